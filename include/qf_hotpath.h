@@ -1,0 +1,233 @@
+/*
+ * qf_hotpath.h -- C ABI of libqf_hotpath.so: the decode-step attention hot path
+ * of Qwen-frence (fused RoPE + paged KV-cache write, GQA paged decode attention
+ * with split-K partial softmax and combine, optional FP8-e4m3 KV cache) as
+ * hand-written sm_100a CUDA kernels.
+ *
+ * Conventions
+ *   - Every pointer marked "device" is a CUDA device pointer owned by the
+ *     caller.  The library allocates no device memory, ever.  It keeps one
+ *     host-side cache of TMA tensor maps keyed by pool address and geometry.
+ *   - `stream` is a cudaStream_t passed as void*.  Every call only enqueues
+ *     work on that stream: no host synchronisation, no device->host read, so
+ *     every call may be recorded into a CUDA graph.
+ *   - Strides are in ELEMENTS of the tensor's dtype, like torch's.
+ *   - Return value: 0 on success, a negative QF_E* code otherwise;
+ *     qf_last_error() then returns a message for the calling thread.
+ *   - All functions are thread-safe; a single host thread drives the
+ *     reference engine (engine/cpp/include/iteration_loop.hpp:157-161).
+ *
+ * Each entry point cites the reference interface it replaces, by path inside
+ * the benjaminW2025/qwen-frence tree.
+ */
+#ifndef QF_HOTPATH_H_
+#define QF_HOTPATH_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QF_ABI_VERSION 1
+
+/* element types of Q/K/V and the pools */
+#define QF_DTYPE_F16 0
+#define QF_DTYPE_BF16 1
+/* element types of metadata tensors (positions, slots, block table, lengths) */
+#define QF_INDEX_I32 0
+#define QF_INDEX_I64 1
+#define QF_INDEX_F32 2 /* positions only */
+
+#define QF_OK 0
+#define QF_EINVAL (-1)   /* bad argument (shape, dtype, alignment, null) */
+#define QF_ECUDA (-2)    /* a CUDA runtime/driver call failed */
+#define QF_EUNSUPPORTED (-3)
+
+/* Fixed geometry of the fast kernels (baseline/naive_forward.py:17-26). */
+#define QF_HEAD_DIM 128
+#define QF_PAGE_SIZE 16
+#define QF_GQA_GROUP 6
+
+int qf_abi_version(void);
+const char* qf_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Fused RoPE + paged KV-cache write.
+ *
+ * One generic entry point; the three reference functions differ only in the
+ * strides they pass:
+ *   rope_kv_write                 custom_kernels/rope_kv_write.py:89-162
+ *       q (1,Hq,T,D): row stride = stride(2), head stride = stride(1)
+ *   native_decode_rope_kv_write   custom_kernels/rope_kv_write.py:223-276
+ *       q (B,Hq,1,D): row stride = stride(0), head stride = stride(1)
+ *   packed_qkv_rope_cache         custom_kernels/packed_qkv_rope_cache.py:91-133
+ *       packed (rows,2048): q = packed, k = packed+1536*sd, v = packed+1792*sd,
+ *       head stride = 128*sd, row stride = stride(0), d stride = sd = stride(1)
+ *
+ * For every row r < rows and every rotary pair (i, i+D/2):
+ *   inv_freq[i] = expf(i * (-(float)log(base) / (D/2)))      (host, fp32)
+ *   angle = (float)positions[r] * inv_freq[i];  c = cosf(angle); s = sinf(angle)
+ *   out[i] = x[i]*c - x[i+D/2]*s;  out[i+D/2] = x[i+D/2]*c + x[i]*s   (fp32,
+ *   one rounding to the element type on store)
+ * Q heads go to q_out (skipped when rotate_q == 0); K heads (rotated) and V
+ * heads (bit-exact copy) go to pool row `slot_mapping[r]` of the flat
+ * [slots, kv_heads, D] view of k_pool / v_pool.
+ * `valid_tokens` (device int32 scalar, may be NULL): rows >= *valid_tokens
+ * write zeros to q_out and do not touch the pools.
+ * ------------------------------------------------------------------------ */
+typedef struct qf_rope_kv_write_args {
+  const void* q;  /* device, may be NULL when rotate_q == 0 */
+  const void* k;  /* device */
+  const void* v;  /* device */
+  void* q_out;    /* device, may be NULL when rotate_q == 0 */
+  int64_t q_stride_row, q_stride_head, q_stride_d;
+  int64_t k_stride_row, k_stride_head, k_stride_d;
+  int64_t v_stride_row, v_stride_head, v_stride_d;
+  int64_t o_stride_row, o_stride_head, o_stride_d;
+  const void* positions;    /* device, [rows] */
+  int32_t positions_dtype;  /* QF_INDEX_* */
+  int64_t positions_stride;
+  const void* slot_mapping; /* device, [rows] */
+  int32_t slot_dtype;       /* QF_INDEX_I32 / I64 */
+  int64_t slot_stride;
+  void* k_pool; /* device, flat [slots, kv_heads, D] view */
+  void* v_pool; /* device */
+  int64_t kp_stride_slot, kp_stride_head, kp_stride_d;
+  int64_t vp_stride_slot, vp_stride_head, vp_stride_d;
+  int64_t num_slots;           /* pool rows; slots outside [0,num_slots) are skipped */
+  const int32_t* valid_tokens; /* device scalar or NULL */
+  int32_t rows, q_heads, kv_heads, head_dim;
+  int32_t dtype;    /* QF_DTYPE_* of q/k/v/q_out/pools */
+  int32_t rotate_q; /* 0: only the kv_heads K/V segments are processed */
+  double base;      /* rope theta */
+} qf_rope_kv_write_args;
+
+int qf_rope_kv_write(const qf_rope_kv_write_args* args, void* stream);
+
+/* Same, but the pools are FP8-e4m3 bytes with one fp32 scale per
+ * (page, kv head): byte = e4m3_rn_satfinite(clamp(x / scale, +-448)) where
+ * scale = {k,v}_scale[(slot / page_size) * kv_heads + head].  The scales are
+ * read, never written (fixed-scale write; nearest reference:
+ * experiments/quant/kernels/staged_cache.py:39-55, codec
+ * experiments/quant/attention.py:27-50).  The reference has no per-page-scale
+ * paged cache; this layout is defined here.  k_pool/v_pool strides are in
+ * bytes == elements. */
+int qf_rope_kv_write_fp8(const qf_rope_kv_write_args* args, const float* k_scale,
+                         const float* v_scale, int32_t page_size, void* stream);
+
+/* Quantise whole fp16/bf16 pools [pages, page_size, kv_heads, D] (contiguous)
+ * to e4m3 pools of the same shape plus scales [pages, kv_heads]:
+ * scale = max(amax(page, head)/448, 1e-12)
+ * (experiments/quant/attention.py:27-41, page granularity instead of token). */
+int qf_quantize_kv_pages_e4m3(const void* pool, int32_t dtype, int64_t num_pages,
+                              int32_t page_size, int32_t kv_heads, int32_t head_dim,
+                              void* pool8, float* scales, void* stream);
+
+/* ------------------------------------------------------------------------
+ * GQA paged decode attention, split-K partial pass.
+ * Replaces grouped_gqa_splitk_partial_out
+ * (custom_kernels/native_grouped_decode/native_grouped_decode.cu:329-403) and
+ * _grouped_splitk_kernel (custom_kernels/paged_decode_grouped_splitk.py:28-158).
+ *
+ * Partition `s` of sequence `b` covers logical pages
+ * [s*P/split_k, (s+1)*P/split_k), P = ceil(seq_lens[b]/page_size).
+ * Outputs (fp32, contiguous):
+ *   partial_out [batch, split_k, q_heads, D]  un-normalised sum of p*V
+ *   partial_max [batch, split_k, q_heads]     exponent offset m (natural-log
+ *                                             units of score*scale); -inf if empty
+ *   partial_sum [batch, split_k, q_heads]     sum of exp(score*scale - m); 0 if empty
+ * with p = exp(score*scale - m).  m is an upper-bounded running offset, not
+ * necessarily the exact maximum: (out, m, sum) is self-consistent, which is
+ * all the combine needs.
+ * When split_k == 1 and out != NULL the kernel also writes the normalised
+ * result to `out` in the q dtype (rows with seq_len 0 give zeros) and the
+ * partial pointers may be NULL.
+ * k_scale/v_scale: NULL for 16-bit pools; for FP8-e4m3 pools (kv_fp8 != 0)
+ * device fp32 [num_pages, kv_heads].
+ * ------------------------------------------------------------------------ */
+typedef struct qf_decode_attention_args {
+  const void* q; /* device [batch, q_heads, D] */
+  int64_t q_stride_b, q_stride_h, q_stride_d;
+  const void* k_pool; /* device [num_pages, page_size, kv_heads, D] */
+  const void* v_pool;
+  int64_t k_stride_page, k_stride_tok, k_stride_head, k_stride_d;
+  int64_t v_stride_page, v_stride_tok, v_stride_head, v_stride_d;
+  const void* block_table; /* device [batch, table_width] */
+  int32_t table_dtype;     /* QF_INDEX_I32 / I64 */
+  int64_t table_stride_b, table_stride_p;
+  int64_t table_width;
+  const void* seq_lens; /* device [batch] */
+  int32_t lens_dtype;
+  int64_t lens_stride;
+  const float* k_scale; /* device or NULL */
+  const float* v_scale;
+  float* partial_out; /* device, see above */
+  float* partial_max;
+  float* partial_sum;
+  void* out; /* device [batch, q_heads, D] in q dtype, or NULL */
+  int64_t o_stride_b, o_stride_h, o_stride_d;
+  int64_t num_pages;
+  int32_t batch, q_heads, kv_heads, head_dim, page_size;
+  int32_t split_k;
+  int32_t dtype;  /* QF_DTYPE_* of q/out (and of the pools unless kv_fp8) */
+  int32_t kv_fp8; /* 0: pools in `dtype`; 1: pools are e4m3 bytes */
+  float scale;    /* softmax scale */
+} qf_decode_attention_args;
+
+int qf_grouped_gqa_splitk_partial_out(const qf_decode_attention_args* args, void* stream);
+
+/* Split-K combine.  Replaces _splitk_reduce_kernel
+ * (custom_kernels/paged_decode_grouped_splitk.py:165-226): log-sum-exp merge of
+ * the partitions with partial_sum > 0, out = acc / (sum > 0 ? sum : 1).
+ * Partial strides are in fp32 elements; `out` is in `dtype`. */
+int qf_splitk_reduce(const float* partial_out, const float* partial_max,
+                     const float* partial_sum, int64_t po_stride_b, int64_t po_stride_k,
+                     int64_t po_stride_h, int64_t po_stride_d, int64_t pm_stride_b,
+                     int64_t pm_stride_k, int64_t pm_stride_h, void* out,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_d,
+                     int32_t batch, int32_t q_heads, int32_t head_dim, int32_t split_k,
+                     int32_t dtype, void* stream);
+
+/* Partial pass + combine in one call (two launches; one when split_k == 1).
+ * Replaces grouped_splitk_decode_attention
+ * (custom_kernels/paged_decode_grouped_splitk.py:228-334) and
+ * native_grouped_splitk_decode_attention
+ * (custom_kernels/paged_decode_native_grouped.py:30-88).  `out` is required. */
+int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream);
+
+/* Compiled resources and occupancy of the fast partial kernel for `dtype` /
+ * `kv_fp8` on `device`.  Replaces grouped_gqa_splitk_diagnostics
+ * (native_grouped_decode.cu:310-327).  Fills
+ *   info[0] registers_per_thread   info[1] static_shared_bytes
+ *   info[2] dynamic_shared_bytes   info[3] local_bytes_per_thread
+ *   info[4] max_threads_per_block  info[5] binary_version
+ *   info[6] ptx_version            info[7] threads_per_block
+ *   info[8] active_blocks_per_sm   info[9] max_warps_per_sm
+ *   info[10] pipeline_stages       info[11] multiprocessor_count */
+#define QF_KERNEL_INFO_FIELDS 12
+int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_fp8,
+                                      int64_t* info);
+
+/* Instrumented partial pass.  Replaces grouped_gqa_splitk_profile_out
+ * (native_grouped_decode.cu:405-459): same outputs as the partial pass plus
+ * cycles [batch, kv_heads, split_k, 4] (device int64): clock64() cycles one
+ * consumer warp of each CTA spent {waiting for pages, in QK, in softmax, in PV}. */
+int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
+                                      int64_t* cycles, void* stream);
+
+/* Device-side status word of the fast kernels on the current device: 0, or a
+ * code recorded by a kernel whose bounded wait ran out or that met a page id
+ * outside the pool.  Synchronises the device; for tests and debugging only.
+ * `reset` != 0 clears it after reading. */
+int qf_device_status(int32_t* status, int32_t reset);
+
+/* Choice of pipeline depth / forcing the generic path, for experiments.
+ * stages == 0 restores the default.  force_generic != 0 routes every
+ * attention call through the stride-generic kernel. */
+int qf_set_tuning(int32_t stages, int32_t force_generic);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QF_HOTPATH_H_ */

@@ -1,0 +1,169 @@
+// Shared helpers for the libqf_hotpath.so translation units: error reporting,
+// element-type conversion, metadata loads and the sm_100a PTX wrappers
+// (mbarrier, TMA tiled loads) the kernels use.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/qf_hotpath.h"
+
+namespace qf {
+
+// ---- host side -----------------------------------------------------------
+int fail(int code, const char* fmt, ...);  // records the message, returns code
+int cuda_fail(cudaError_t err, const char* what);
+
+#define QF_REQUIRE(cond, ...)                              \
+  do {                                                     \
+    if (!(cond)) return ::qf::fail(QF_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define QF_CUDA(expr)                                         \
+  do {                                                        \
+    cudaError_t qf_err__ = (expr);                            \
+    if (qf_err__ != cudaSuccess) return ::qf::cuda_fail(qf_err__, #expr); \
+  } while (0)
+
+// Address of the per-device status word (file-scope __device__ int).
+int* device_status_word();
+
+// Status codes kernels may record.
+constexpr int kStatusWaitTimeout = 1;
+constexpr int kStatusBadPageId = 2;
+
+// ---- device side ---------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) {
+  return __float2half_rn(x);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+// Two packed 16-bit elements (one 32-bit register) -> float2.
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t bits);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t bits) {
+  __half2 h = *reinterpret_cast<__half2*>(&bits);
+  return __half22float2(h);
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t bits) {
+  float2 r;
+  r.x = __uint_as_float(bits << 16);
+  r.y = __uint_as_float(bits & 0xffff0000u);
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Two e4m3 bytes (low 16 bits) -> float2 (exact: every e4m3 value is an fp16 value).
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t bits) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(bits, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+__device__ __forceinline__ int64_t load_index(const void* base, int dtype, int64_t offset) {
+  if (dtype == QF_INDEX_I64) return static_cast<const int64_t*>(base)[offset];
+  return static_cast<const int32_t*>(base)[offset];
+}
+
+__device__ __forceinline__ float load_position(const void* base, int dtype, int64_t offset) {
+  if (dtype == QF_INDEX_F32) return static_cast<const float*>(base)[offset];
+  if (dtype == QF_INDEX_I64) return static_cast<float>(static_cast<const int64_t*>(base)[offset]);
+  return static_cast<float>(static_cast<const int32_t*>(base)[offset]);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+// Makes the initialised barriers visible to the async (TMA) proxy.
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Upper bound on any wait inside a kernel, in SM clock cycles (about two
+// seconds).  A wait that runs out records kStatusWaitTimeout and gives up.
+constexpr long long kWaitCycleLimit = 4000000000LL;
+
+// Returns false when the wait ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > kWaitCycleLimit) return false;
+  }
+  return true;
+}
+
+// 4-D tiled TMA load of one box into this CTA's shared memory; completion is
+// counted in bytes on `bar`.  Coordinates are innermost first.  The innermost
+// coordinate is always 0 here, which satisfies the 16-byte start rule.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+#endif  // __CUDACC__
+}  // namespace qf

@@ -1,0 +1,1029 @@
+// GQA paged decode attention over block tables: split-K partial pass, combine,
+// and the host entry points.
+//
+// Fast partial kernel (sm_100a), geometry D=128, page=16, 6 query heads per KV
+// head (baseline/naive_forward.py:17-26):
+//
+//   * one CTA per (sequence, KV head, split): the six query heads of the GQA
+//     group share every K/V page load
+//     (same work split as native_grouped_decode.cu:62-67);
+//   * pages stream through a ring of shared memory stages guarded by
+//     full/empty mbarriers, filled by 4-D tiled TMA loads ([pages,16,kv,128]
+//     tensor map, box [1,16,1,128]) that lane 0 of warp 0 issues `stages - 2`
+//     pages ahead of the math; page ids are fetched 32 at a time, one batch
+//     ahead.  The CTA is exactly eight warps (no extra producer warp), which
+//     keeps two CTAs of 128 registers per thread resident per SM;
+//   * all 256 threads consume: thread (t, c) owns token slot t (0..15) of every
+//     page and the 8 head dimensions [8c, 8c+8).  It reads its 16 bytes of K and
+//     V from shared memory once and reuses them from registers for all six
+//     heads (packed fp32x2 FMAs), so shared memory is read exactly once per
+//     element, not once per head;
+//   * the six per-thread partial dot products are reduce-scattered across the
+//     16 lanes of a token with 7 shuffles; each lane then owns one head's score,
+//     keeps that head's running (offset, sum) for its token slot, and the
+//     probabilities are gathered back with 6 shuffles.  The running offset only
+//     moves when a score exceeds it by more than 2^8, so the accumulator
+//     rescale is off the common path;
+//   * the 16 token slots are merged once per CTA, through shared memory.
+//
+// No tensor-core MMA: with M=6 the op is a bandwidth-bound GEMV.  No load in
+// this file names a cluster-multicast qualifier.
+//
+// A stride-generic kernel covers every other layout and geometry the
+// reference accepts (custom_kernels/paged_decode_grouped_splitk.py:228-334):
+// arbitrary strides, other page sizes, head dims and group sizes.
+#include <cmath>
+#include <mutex>
+#include <unordered_map>
+
+#include "qf_common.cuh"
+
+namespace qf {
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kFastThreads = kConsumerThreads;  // warp 0 also issues the TMA loads
+constexpr int kMaxStages = 12;
+constexpr int kDefaultStagesF16 = 6;
+constexpr int kDefaultStagesFp8 = 8;
+constexpr int kMergeFloats = kConsumerWarps * QF_GQA_GROUP * QF_HEAD_DIM;  // 24 KB
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+// The exponent offset follows the running maximum only when a score exceeds it
+// by more than this many powers of two; probabilities stay below 2^kOffsetSlack.
+constexpr float kOffsetSlack = 8.f;
+
+int g_tuned_stages = 0;
+int g_force_generic = 0;
+
+struct FastParams {
+  const void* q;
+  int64_t q_sb, q_sh;
+  const void* block_table;
+  int64_t bt_sb, bt_sp;
+  const void* seq_lens;
+  int64_t lens_stride;
+  const float* k_scale;
+  const float* v_scale;
+  float* partial_out;
+  float* partial_max;
+  float* partial_sum;
+  void* out;
+  int64_t o_sb, o_sh, o_sd;
+  int64_t num_pages;
+  long long* cycles;
+  int* status;
+  int table_dtype, lens_dtype;
+  int batch, q_heads, kv_heads, split_k, stages;
+  float scale_log2;  // softmax scale * log2(e)
+};
+
+// ---------------------------------------------------------------------------
+// Consumer-side state of one thread: token slot t = tid/16, dims [8c, 8c+8).
+// ---------------------------------------------------------------------------
+struct SlotState {
+  float2 acc[QF_GQA_GROUP][4];  // un-normalised sum of p*V for the 8 dims
+  float offset;                 // exponent offset of the head this lane owns (log2 units)
+  float sum;                    // sum of p for that head
+};
+
+// Reduce six per-thread partial dots over the 16 lanes of a token slot so that
+// each lane ends with the full dot product of ONE head:
+//   lanes 0,1 -> head 0   lanes 4,5 -> head 1   lanes 2,3,6,7 -> head 2
+//   lanes 8,9 -> head 3   lanes 12,13 -> head 4  lanes 10,11,14,15 -> head 5
+__device__ __forceinline__ float reduce_scatter6(const float (&v)[QF_GQA_GROUP], int sub) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const bool b3 = sub & 8, b2 = sub & 4, b1 = sub & 2;
+  float k0 = b3 ? v[3] : v[0], s0 = b3 ? v[0] : v[3];
+  float k1 = b3 ? v[4] : v[1], s1 = b3 ? v[1] : v[4];
+  float k2 = b3 ? v[5] : v[2], s2 = b3 ? v[2] : v[5];
+  k0 += __shfl_xor_sync(kFull, s0, 8);
+  k1 += __shfl_xor_sync(kFull, s1, 8);
+  k2 += __shfl_xor_sync(kFull, s2, 8);
+  float a = b2 ? k1 : k0, sa = b2 ? k0 : k1;
+  a += __shfl_xor_sync(kFull, sa, 4);
+  const float c = k2 + __shfl_xor_sync(kFull, k2, 4);
+  float x = b1 ? c : a, sx = b1 ? a : c;
+  x += __shfl_xor_sync(kFull, sx, 2);
+  x += __shfl_xor_sync(kFull, x, 1);
+  return x;
+}
+
+// Index (within a KV group) of the head a lane owns after reduce_scatter6.
+__device__ __forceinline__ int owned_head(int sub) {
+  const int b3 = (sub >> 3) & 1, b2 = (sub >> 2) & 1, b1 = (sub >> 1) & 1;
+  return b1 ? 3 * b3 + 2 : 3 * b3 + b2;
+}
+
+// Lane (within the 16-lane token group) that holds head h after reduce_scatter6.
+__device__ __forceinline__ constexpr int source_lane(int h) {
+  return h == 0 ? 0 : h == 1 ? 4 : h == 2 ? 2 : h == 3 ? 8 : h == 4 ? 12 : 10;
+}
+
+// One page for one thread.  kreg/vreg: this thread's 8 K and 8 V elements
+// already converted to fp32 pairs.  `valid`: the thread's token is < seq_len.
+// k_mul/v_mul: per-page FP8 dequantisation scales (1 for 16-bit pools).
+template <bool TAIL>
+__device__ __forceinline__ void consume_page(SlotState& st, const float2 (&q2)[QF_GQA_GROUP][4],
+                                             const float2 (&kreg)[4], const float2 (&vreg)[4],
+                                             bool valid, float k_mul, float v_mul, int sub) {
+  constexpr unsigned kFull = 0xffffffffu;
+  float dots[QF_GQA_GROUP];
+#pragma unroll
+  for (int h = 0; h < QF_GQA_GROUP; ++h) {
+    float2 d = __fmul2_rn(q2[h][0], kreg[0]);
+#pragma unroll
+    for (int j = 1; j < 4; ++j) d = __ffma2_rn(q2[h][j], kreg[j], d);
+    dots[h] = d.x + d.y;
+  }
+  float score = reduce_scatter6(dots, sub) * k_mul;
+  if (TAIL && !valid) score = -INFINITY;
+
+  // Move the offset only when the score outgrows it (or on the first page).
+  const bool grow = score > st.offset + kOffsetSlack;
+  if (__any_sync(kFull, grow)) {
+    float corr = 1.f;
+    if (grow) {
+      corr = st.offset == -INFINITY ? 0.f : fast_exp2(st.offset - score);
+      st.offset = score;
+      st.sum *= corr;
+    }
+#pragma unroll
+    for (int h = 0; h < QF_GQA_GROUP; ++h) {
+      const float ch = __shfl_sync(kFull, corr, source_lane(h), 16);
+      const float2 c2 = make_float2(ch, ch);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) st.acc[h][j] = __fmul2_rn(st.acc[h][j], c2);
+    }
+  }
+  float p = fast_exp2(score - st.offset);
+  if (TAIL && !valid) p = 0.f;  // also covers offset == -inf (NaN from inf - inf)
+  st.sum += p;
+  p *= v_mul;
+
+  float ph[QF_GQA_GROUP];
+#pragma unroll
+  for (int h = 0; h < QF_GQA_GROUP; ++h) ph[h] = __shfl_sync(kFull, p, source_lane(h), 16);
+  if (!TAIL || valid) {
+#pragma unroll
+    for (int h = 0; h < QF_GQA_GROUP; ++h) {
+      const float2 p2 = make_float2(ph[h], ph[h]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) st.acc[h][j] = __ffma2_rn(p2, vreg[j], st.acc[h][j]);
+    }
+  }
+}
+
+template <typename T, bool FP8>
+struct TileTraits {
+  static constexpr int kTileBytes = FP8 ? QF_PAGE_SIZE * QF_HEAD_DIM : QF_PAGE_SIZE * QF_HEAD_DIM * 2;
+  static constexpr int kStageBytes = 2 * kTileBytes;  // K tile + V tile
+};
+
+// Loads this thread's 8 elements of a tile and converts them to fp32 pairs.
+template <typename T, bool FP8>
+__device__ __forceinline__ void load_tile_regs(const unsigned char* tile, int tid, float2 (&r)[4]) {
+  if constexpr (FP8) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(tile + tid * 8);
+    r[0] = e4m3x2_to_float2(static_cast<uint16_t>(raw.x & 0xffffu));
+    r[1] = e4m3x2_to_float2(static_cast<uint16_t>(raw.x >> 16));
+    r[2] = e4m3x2_to_float2(static_cast<uint16_t>(raw.y & 0xffffu));
+    r[3] = e4m3x2_to_float2(static_cast<uint16_t>(raw.y >> 16));
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(tile + tid * 16);
+    r[0] = unpack2<T>(raw.x);
+    r[1] = unpack2<T>(raw.y);
+    r[2] = unpack2<T>(raw.z);
+    r[3] = unpack2<T>(raw.w);
+  }
+}
+
+template <typename T, bool FP8, bool PROFILE>
+__global__ void __launch_bounds__(kFastThreads, 2)
+    decode_partial_tma_kernel(const __grid_constant__ CUtensorMap k_map,
+                              const __grid_constant__ CUtensorMap v_map, const FastParams p) {
+  using Traits = TileTraits<T, FP8>;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ uint64_t full_bar[kMaxStages];
+  __shared__ uint64_t empty_bar[kMaxStages];
+  __shared__ float stage_scale[kMaxStages][2];
+  __shared__ int batch_ids[32];
+  __shared__ float batch_scale[32][2];
+  __shared__ float slot_offset[QF_PAGE_SIZE][QF_GQA_GROUP];
+  __shared__ float slot_sum[QF_PAGE_SIZE][QF_GQA_GROUP];
+  __shared__ float cta_offset[QF_GQA_GROUP];
+  __shared__ float cta_sum[QF_GQA_GROUP];
+
+  constexpr unsigned kFull = 0xffffffffu;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int token = tid >> 4;  // token slot in every page
+  const int sub = tid & 15;    // dim chunk / lane in the token group
+  const int stages = p.stages;
+  const int lookahead = stages > 2 ? stages - 2 : 1;  // pages in flight ahead of the consumers
+
+  // blockIdx.x = (sequence * kv_heads + kv_head) * split_k + split
+  const int split = blockIdx.x % p.split_k;
+  const int kv_head = (blockIdx.x / p.split_k) % p.kv_heads;
+  const int sequence = blockIdx.x / (p.split_k * p.kv_heads);
+
+  int seq_len;
+  {
+    int64_t raw = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
+    raw = raw < 0 ? 0 : raw;
+    seq_len = static_cast<int>(raw > 0x7ffffff0 ? 0x7ffffff0 : raw);
+  }
+  const int total_pages = (seq_len + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE;
+  const int start_page = static_cast<int>(static_cast<int64_t>(split) * total_pages / p.split_k);
+  const int end_page = static_cast<int>((static_cast<int64_t>(split) + 1) * total_pages / p.split_k);
+  const int num_iters = end_page - start_page;
+  // Iterations before `full_iters` read complete pages; at most one partial page follows.
+  const int full_end = min(end_page, seq_len / QF_PAGE_SIZE);
+  const int full_iters = max(full_end - start_page, 0);
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    fence_barrier_init();
+    if (num_iters > 0) {
+      tma_prefetch_descriptor(&k_map);
+      tma_prefetch_descriptor(&v_map);
+    }
+  }
+  __syncthreads();
+
+  // ---- producer role (warp 0 only; every lane runs it, lane 0 issues) ----
+  // Page ids (and FP8 scales) are fetched 32 at a time into registers, one batch
+  // ahead, and parked in shared memory when their batch becomes current.
+  const int num_pages = static_cast<int>(p.num_pages);
+  int ids_next = -1;
+  int issued = 0;  // iterations whose loads have been issued (meaningful in warp 0)
+  float ks_next = 1.f, vs_next = 1.f;
+  auto fetch_batch = [&](int first_iter) {
+    const int idx = start_page + first_iter + lane;
+    ids_next = -1;
+    if (idx < end_page) {
+      const int64_t raw = load_index(p.block_table, p.table_dtype,
+                                     sequence * p.bt_sb + static_cast<int64_t>(idx) * p.bt_sp);
+      ids_next = raw >= 0 && raw < num_pages ? static_cast<int>(raw) : -1;  // -1: outside the pool
+    }
+    if (FP8) {
+      ks_next = ids_next >= 0 ? p.k_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
+      vs_next = ids_next >= 0 ? p.v_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
+    }
+  };
+  // Issues the loads of iteration `index` into stage `pstage` (free once its
+  // empty barrier completes phase `pparity`).  False when that wait ran out.
+  auto produce = [&](int index, int pstage, uint32_t pparity) -> bool {
+    if ((index & 31) == 0) {
+      if (index == 0) fetch_batch(0);
+      __syncwarp();
+      batch_ids[lane] = ids_next;
+      if (FP8) batch_scale[lane][0] = ks_next, batch_scale[lane][1] = vs_next;
+      __syncwarp();
+      if (index + 32 < num_iters) fetch_batch(index + 32);
+    }
+    int ok = 1;
+    if (lane == 0) {
+      if (!mbar_wait_bounded(&empty_bar[pstage], pparity)) {
+        atomicExch(p.status, kStatusWaitTimeout);
+        ok = 0;
+      } else {
+        const int page_id = batch_ids[index & 31];
+        if (page_id < 0) atomicExch(p.status, kStatusBadPageId);
+        if (FP8) {
+          stage_scale[pstage][0] = batch_scale[index & 31][0];
+          stage_scale[pstage][1] = batch_scale[index & 31][1];
+        }
+        unsigned char* dst = smem + pstage * Traits::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[pstage], Traits::kStageBytes);
+        // A page id outside the pool reads as zeros (TMA out-of-bounds fill).
+        tma_load_4d(dst, &k_map, &full_bar[pstage], 0, kv_head, 0, page_id);
+        tma_load_4d(dst + Traits::kTileBytes, &v_map, &full_bar[pstage], 0, kv_head, 0, page_id);
+        issued = index + 1;
+      }
+    }
+    return __shfl_sync(kFull, ok, 0) != 0;
+  };
+
+  SlotState st;
+#pragma unroll
+  for (int h = 0; h < QF_GQA_GROUP; ++h)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) st.acc[h][j] = make_float2(0.f, 0.f);
+  st.offset = -INFINITY;
+  st.sum = 0.f;
+
+  bool aborted = false;
+  if (warp == 0) {
+    // The first `lookahead` stages are free: their empty barriers start out in
+    // the phase that a wait on parity 1 passes.
+    for (int i = 0; i < lookahead && i < num_iters && !aborted; ++i) aborted = !produce(i, i, 1u);
+  }
+
+  float2 q2[QF_GQA_GROUP][4];
+  if (num_iters > 0) {
+    const T* qbase = static_cast<const T*>(p.q) + sequence * p.q_sb +
+                     static_cast<int64_t>(kv_head) * QF_GQA_GROUP * p.q_sh + sub * 8;
+    const float2 s2 = make_float2(p.scale_log2, p.scale_log2);
+#pragma unroll
+    for (int h = 0; h < QF_GQA_GROUP; ++h) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(qbase + h * p.q_sh);
+      q2[h][0] = __fmul2_rn(unpack2<T>(raw.x), s2);
+      q2[h][1] = __fmul2_rn(unpack2<T>(raw.y), s2);
+      q2[h][2] = __fmul2_rn(unpack2<T>(raw.z), s2);
+      q2[h][3] = __fmul2_rn(unpack2<T>(raw.w), s2);
+    }
+  }
+
+  // ------------------------------ main loop -------------------------------
+  long long t_wait = 0, t_math = 0, t_mark = 0;
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int it = 0; it < num_iters && !aborted; ++it) {
+    if (warp == 0 && it + lookahead < num_iters) {
+      // Iteration it+lookahead lands `lookahead` stages ahead of this one.
+      int pstage = stage + lookahead;
+      uint32_t pparity = phase ^ 1u;
+      if (pstage >= stages) pstage -= stages, pparity ^= 1u;
+      if (!produce(it + lookahead, pstage, pparity)) {
+        aborted = true;
+        break;
+      }
+    }
+    if (PROFILE) t_mark = clock64();
+    const bool arrived = mbar_wait_bounded(&full_bar[stage], phase);
+    if (!__all_sync(kFull, arrived)) {
+      if (lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+      aborted = true;
+      break;
+    }
+    if (PROFILE) t_wait += clock64() - t_mark, t_mark = clock64();
+    const unsigned char* tile = smem + stage * Traits::kStageBytes;
+    float2 kreg[4], vreg[4];
+    load_tile_regs<T, FP8>(tile, tid, kreg);
+    load_tile_regs<T, FP8>(tile + Traits::kTileBytes, tid, vreg);
+    float k_mul = 1.f, v_mul = 1.f;
+    if (FP8) k_mul = stage_scale[stage][0], v_mul = stage_scale[stage][1];
+    // The stage is in registers: hand it back to the producer.
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    if (++stage == stages) stage = 0, phase ^= 1u;
+
+    if (it < full_iters) {
+      consume_page<false>(st, q2, kreg, vreg, true, k_mul, v_mul, sub);
+    } else {
+      const bool valid = (start_page + it) * QF_PAGE_SIZE + token < seq_len;
+      consume_page<true>(st, q2, kreg, vreg, valid, k_mul, v_mul, sub);
+    }
+    if (PROFILE) t_math += clock64() - t_mark;
+  }
+  if (PROFILE && p.cycles != nullptr && tid == 32) {
+    // One pure-consumer warp per CTA reports: {waiting for pages, QK + softmax + PV, 0, 0}.
+    long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;
+    dst[0] = t_wait, dst[1] = t_math, dst[2] = 0, dst[3] = 0;
+  }
+  // Barrier: every stage has been read, so the ring is free for the merge.
+  if (__syncthreads_or(aborted)) {
+    // A wait ran out somewhere in this CTA.  Give the loads already issued a
+    // bounded chance to land before their shared memory is reused or released.
+    if (tid == 0) {
+      for (int s = 0; s < stages && s < issued; ++s) {
+        const int last = ((issued - 1 - s) / stages) * stages + s;  // last iteration on stage s
+        mbar_wait_bounded(&full_bar[s], static_cast<uint32_t>(last / stages) & 1u);
+      }
+    }
+    __syncthreads();
+  }
+  float* merge = reinterpret_cast<float*>(smem);  // [8 warps][6 heads][128]
+  {
+    const int h = owned_head(sub);
+    if (sub == source_lane(h)) {
+      slot_offset[token][h] = st.offset;
+      slot_sum[token][h] = st.sum;
+    }
+  }
+  __syncthreads();
+  if (tid < QF_GQA_GROUP) {
+    float m = -INFINITY;
+    for (int g = 0; g < QF_PAGE_SIZE; ++g) m = fmaxf(m, slot_offset[g][tid]);
+    float total = 0.f;
+    for (int g = 0; g < QF_PAGE_SIZE; ++g) {
+      const float mg = slot_offset[g][tid];
+      if (mg != -INFINITY) total += slot_sum[g][tid] * fast_exp2(mg - m);
+    }
+    cta_offset[tid] = m;
+    cta_sum[tid] = total;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < QF_GQA_GROUP; ++h) {
+    const float mg = slot_offset[token][h];
+    const float f = mg == -INFINITY ? 0.f : fast_exp2(mg - cta_offset[h]);
+    const float2 f2 = make_float2(f, f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = __fmul2_rn(st.acc[h][j], f2);
+      a.x += __shfl_xor_sync(kFull, a.x, 16);
+      a.y += __shfl_xor_sync(kFull, a.y, 16);
+      st.acc[h][j] = a;
+    }
+    if (lane < 16) {
+      float4* dst =
+          reinterpret_cast<float4*>(merge + (warp * QF_GQA_GROUP + h) * QF_HEAD_DIM + sub * 8);
+      dst[0] = make_float4(st.acc[h][0].x, st.acc[h][0].y, st.acc[h][1].x, st.acc[h][1].y);
+      dst[1] = make_float4(st.acc[h][2].x, st.acc[h][2].y, st.acc[h][3].x, st.acc[h][3].y);
+    }
+  }
+  __syncthreads();
+  const int64_t head0 = static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
+  const int64_t partial_row =
+      (static_cast<int64_t>(sequence) * p.split_k + split) * p.q_heads + head0;
+#pragma unroll
+  for (int i = 0; i < (QF_GQA_GROUP * QF_HEAD_DIM) / kConsumerThreads; ++i) {
+    const int e = tid + i * kConsumerThreads;  // (head, dim) flattened
+    float value = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) value += merge[w * QF_GQA_GROUP * QF_HEAD_DIM + e];
+    const int h = e >> 7, d = e & 127;
+    if (p.partial_out != nullptr) p.partial_out[partial_row * QF_HEAD_DIM + e] = value;
+    if (p.out != nullptr) {
+      const float total = cta_sum[h];
+      const float norm = value / (total > 0.f ? total : 1.f);
+      static_cast<T*>(p.out)[sequence * p.o_sb + (head0 + h) * p.o_sh + d * p.o_sd] =
+          from_float<T>(norm);
+    }
+  }
+  if (tid < QF_GQA_GROUP && p.partial_max != nullptr) {
+    // natural-log units, as the combine and the reference's reduce expect
+    p.partial_max[partial_row + tid] = cta_offset[tid] * kLn2;
+    p.partial_sum[partial_row + tid] = cta_sum[tid];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Stride-generic partial kernel: any strides, page size, head dim <= 256 and
+// group size.  One CTA of four warps per (sequence, query head, split); warp w
+// takes tokens w, w+4, ... of the partition; a lane holds dims lane + 32*i.
+// Exact running maximum, natural-log units (expf), as the reference kernels.
+// ---------------------------------------------------------------------------
+struct GenericParams {
+  const void* q;
+  int64_t q_sb, q_sh, q_sd;
+  const void* k_pool;
+  const void* v_pool;
+  int64_t k_sp, k_st, k_sh, k_sd;
+  int64_t v_sp, v_st, v_sh, v_sd;
+  const void* block_table;
+  int64_t bt_sb, bt_sp;
+  const void* seq_lens;
+  int64_t lens_stride;
+  const float* k_scale;
+  const float* v_scale;
+  float* partial_out;
+  float* partial_max;
+  float* partial_sum;
+  void* out;
+  int64_t o_sb, o_sh, o_sd;
+  int64_t num_pages;
+  int* status;
+  int table_dtype, lens_dtype;
+  int batch, q_heads, kv_heads, head_dim, page_size, split_k;
+  float scale;
+};
+
+template <typename KV>
+__device__ __forceinline__ float kv_to_float(KV x) {
+  return to_float(x);
+}
+template <>
+__device__ __forceinline__ float kv_to_float<uint8_t>(uint8_t x) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(x, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+constexpr int kGenericWarps = 4;
+constexpr int kGenericMaxPerLane = 8;  // head_dim <= 256
+
+template <typename T, typename KV>
+__global__ void __launch_bounds__(kGenericWarps * 32)
+    decode_partial_generic_kernel(const GenericParams p) {
+  __shared__ float s_max[kGenericWarps];
+  __shared__ float s_sum[kGenericWarps];
+  __shared__ float s_acc[kGenericWarps][256];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x % p.split_k;
+  const int head = (blockIdx.x / p.split_k) % p.q_heads;
+  const int sequence = blockIdx.x / (p.split_k * p.q_heads);
+  const int group = p.q_heads / p.kv_heads;
+  const int kv_head = head / group;
+
+  int64_t seq_len = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
+  if (seq_len < 0) seq_len = 0;
+  const int64_t total_pages = (seq_len + p.page_size - 1) / p.page_size;
+  const int64_t start_page = split * total_pages / p.split_k;
+  const int64_t end_page = (static_cast<int64_t>(split) + 1) * total_pages / p.split_k;
+  const int64_t tok_begin = start_page * p.page_size;
+  int64_t tok_end = end_page * p.page_size;
+  if (tok_end > seq_len) tok_end = seq_len;
+
+  float q[kGenericMaxPerLane], acc[kGenericMaxPerLane];
+  const T* qrow = static_cast<const T*>(p.q) + sequence * p.q_sb + head * p.q_sh;
+#pragma unroll
+  for (int i = 0; i < kGenericMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    q[i] = d < p.head_dim ? to_float(qrow[d * p.q_sd]) : 0.f;
+    acc[i] = 0.f;
+  }
+  float run_max = -INFINITY, run_sum = 0.f;
+
+  for (int64_t tok = tok_begin + warp; tok < tok_end; tok += kGenericWarps) {
+    const int64_t logical = tok / p.page_size;
+    const int in_page = static_cast<int>(tok - logical * p.page_size);
+    const int64_t page_id =
+        load_index(p.block_table, p.table_dtype, sequence * p.bt_sb + logical * p.bt_sp);
+    if (page_id < 0 || page_id >= p.num_pages) {
+      if (lane == 0) atomicExch(p.status, kStatusBadPageId);
+      continue;
+    }
+    const KV* krow = static_cast<const KV*>(p.k_pool) + page_id * p.k_sp + in_page * p.k_st +
+                     kv_head * p.k_sh;
+    const KV* vrow = static_cast<const KV*>(p.v_pool) + page_id * p.v_sp + in_page * p.v_st +
+                     kv_head * p.v_sh;
+    float k_mul = 1.f, v_mul = 1.f;
+    if (p.k_scale != nullptr) {
+      k_mul = p.k_scale[page_id * p.kv_heads + kv_head];
+      v_mul = p.v_scale[page_id * p.kv_heads + kv_head];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGenericMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < p.head_dim) dot += q[i] * (kv_to_float<KV>(krow[d * p.k_sd]) * k_mul);
+    }
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    const float score = dot * p.scale;
+    const float new_max = fmaxf(run_max, score);
+    const float corr = run_max == -INFINITY ? 0.f : expf(run_max - new_max);
+    const float prob = expf(score - new_max);
+    run_sum = run_sum * corr + prob;
+#pragma unroll
+    for (int i = 0; i < kGenericMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < p.head_dim) acc[i] = acc[i] * corr + prob * (kv_to_float<KV>(vrow[d * p.v_sd]) * v_mul);
+    }
+    run_max = new_max;
+  }
+
+  if (lane == 0) s_max[warp] = run_max, s_sum[warp] = run_sum;
+  __syncthreads();
+  float cta_max = -INFINITY;
+  for (int w = 0; w < kGenericWarps; ++w) cta_max = fmaxf(cta_max, s_max[w]);
+  const float factor = run_max == -INFINITY ? 0.f : expf(run_max - cta_max);
+#pragma unroll
+  for (int i = 0; i < kGenericMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    if (d < p.head_dim) s_acc[warp][d] = acc[i] * factor;
+  }
+  __syncthreads();
+  float cta_total = 0.f;
+  for (int w = 0; w < kGenericWarps; ++w) {
+    if (s_max[w] != -INFINITY) cta_total += s_sum[w] * expf(s_max[w] - cta_max);
+  }
+  const int64_t partial_row = (static_cast<int64_t>(sequence) * p.split_k + split) * p.q_heads + head;
+  for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) {
+    float value = 0.f;
+    for (int w = 0; w < kGenericWarps; ++w) value += s_acc[w][d];
+    if (p.partial_out != nullptr) p.partial_out[partial_row * p.head_dim + d] = value;
+    if (p.out != nullptr) {
+      static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + d * p.o_sd] =
+          from_float<T>(value / (cta_total > 0.f ? cta_total : 1.f));
+    }
+  }
+  if (threadIdx.x == 0 && p.partial_max != nullptr) {
+    p.partial_max[partial_row] = cta_max;
+    p.partial_sum[partial_row] = cta_total;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Combine: one CTA per (sequence, query head); a thread per head dimension.
+// Partitions whose sum is zero are skipped, so an empty first partition is
+// harmless (custom_kernels/paged_decode_grouped_splitk.py:210-218).
+// ---------------------------------------------------------------------------
+struct ReduceParams {
+  const float* po;
+  const float* pm;
+  const float* ps;
+  int64_t po_sb, po_sk, po_sh, po_sd;
+  int64_t pm_sb, pm_sk, pm_sh;
+  void* out;
+  int64_t o_sb, o_sh, o_sd;
+  int q_heads, head_dim, split_k;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
+  const int sequence = blockIdx.x / p.q_heads;
+  const int head = blockIdx.x - sequence * p.q_heads;
+  const int d = threadIdx.x;
+  if (d >= p.head_dim) return;
+  const float* pm = p.pm + sequence * p.pm_sb + head * p.pm_sh;
+  const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
+  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + d * p.po_sd;
+
+  // Pass 1: the largest offset among non-empty partitions (broadcast loads).
+  float top = -INFINITY;
+  for (int k = 0; k < p.split_k; ++k) {
+    if (ps[k * p.pm_sk] > 0.f) top = fmaxf(top, pm[k * p.pm_sk]);
+  }
+  // Pass 2: independent loads, one exp per partition.
+  float acc = 0.f, total = 0.f;
+#pragma unroll 4
+  for (int k = 0; k < p.split_k; ++k) {
+    const float sum = ps[k * p.pm_sk];
+    if (sum > 0.f) {
+      const float w = expf(pm[k * p.pm_sk] - top);
+      acc += po[k * p.po_sk] * w;
+      total += sum * w;
+    }
+  }
+  const float result = acc / (total > 0.f ? total : 1.f);
+  static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + d * p.o_sd] = from_float<T>(result);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiledFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int64_t pages, s_page, s_tok, s_head;
+  int kv_heads, elem_code;  // 0 f16, 1 bf16, 2 e4m3 bytes
+  bool operator==(const MapKey& o) const {
+    return base == o.base && pages == o.pages && s_page == o.s_page && s_tok == o.s_tok &&
+           s_head == o.s_head && kv_heads == o.kv_heads && elem_code == o.elem_code;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    auto mix = [&h](size_t v) { h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
+    mix(static_cast<size_t>(k.pages));
+    mix(static_cast<size_t>(k.s_page));
+    mix(static_cast<size_t>(k.s_tok));
+    mix(static_cast<size_t>(k.s_head));
+    mix(static_cast<size_t>(k.kv_heads * 4 + k.elem_code));
+    return h;
+  }
+};
+
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// Tensor map over a pool [pages, 16, kv_heads, 128] with a box of one page of
+// one KV head: [1, 16, 1, 128].  Host-side only; cached by address and layout.
+int pool_tensor_map(const void* base, int elem_code, int64_t pages, int kv_heads, int64_t s_page,
+                    int64_t s_tok, int64_t s_head, CUtensorMap* out) {
+  const MapKey key{base, pages, s_page, s_tok, s_head, kv_heads, elem_code};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *out = it->second;
+      return QF_OK;
+    }
+  }
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return fail(QF_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const int elem_bytes = elem_code == 2 ? 1 : 2;
+  const CUtensorMapDataType type = elem_code == 0   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : elem_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const cuuint64_t dims[4] = {QF_HEAD_DIM, static_cast<cuuint64_t>(kv_heads), QF_PAGE_SIZE,
+                              static_cast<cuuint64_t>(pages)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s_head) * elem_bytes,
+                                 static_cast<cuuint64_t>(s_tok) * elem_bytes,
+                                 static_cast<cuuint64_t>(s_page) * elem_bytes};
+  const cuuint32_t box[4] = {QF_HEAD_DIM, 1, QF_PAGE_SIZE, 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, type, 4, const_cast<void*>(base), dims, strides, box,
+                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return fail(QF_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(rc));
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_maps.size() > 4096) g_maps.clear();  // pools were reallocated many times
+    g_maps.emplace(key, map);
+  }
+  *out = map;
+  return QF_OK;
+}
+
+int* status_word_for_current_device() {
+  static std::mutex mutex;
+  static int* cache[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cache[device] == nullptr) cache[device] = device_status_word();
+  return cache[device];
+}
+
+int stages_for(bool fp8) {
+  int stages = g_tuned_stages > 0 ? g_tuned_stages : (fp8 ? kDefaultStagesFp8 : kDefaultStagesF16);
+  if (stages < 2) stages = 2;
+  if (stages > kMaxStages) stages = kMaxStages;
+  return stages;
+}
+
+size_t fast_smem_bytes(bool fp8, int stages) {
+  const size_t ring = static_cast<size_t>(stages) * (fp8 ? 4096 : 8192);
+  const size_t merge = kMergeFloats * sizeof(float);
+  return ring > merge ? ring : merge;
+}
+
+template <typename T, bool FP8, bool PROFILE>
+int launch_fast(const CUtensorMap& kmap, const CUtensorMap& vmap, const FastParams& p,
+                cudaStream_t stream) {
+  auto kernel = decode_partial_tma_kernel<T, FP8, PROFILE>;
+  const size_t smem = fast_smem_bytes(FP8, p.stages);
+  QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  const int64_t blocks = static_cast<int64_t>(p.batch) * p.kv_heads * p.split_k;
+  kernel<<<static_cast<unsigned>(blocks), kFastThreads, smem, stream>>>(kmap, vmap, p);
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+int validate(const qf_decode_attention_args* a, bool need_out) {
+  QF_REQUIRE(a != nullptr, "args must not be null");
+  QF_REQUIRE(a->batch >= 0 && a->q_heads >= 1 && a->kv_heads >= 1, "invalid batch or head counts");
+  QF_REQUIRE(a->q_heads % a->kv_heads == 0, "query heads must be divisible by KV heads");
+  QF_REQUIRE(a->head_dim >= 1 && a->head_dim <= 256 && (a->head_dim & (a->head_dim - 1)) == 0 &&
+                 a->page_size >= 1 && (a->page_size & (a->page_size - 1)) == 0,
+             "head dimension and page size must be powers of two (head_dim <= 256)");
+  QF_REQUIRE(a->dtype == QF_DTYPE_F16 || a->dtype == QF_DTYPE_BF16,
+             "Q/K/V must be float16 or bfloat16");
+  QF_REQUIRE(a->table_dtype == QF_INDEX_I32 || a->table_dtype == QF_INDEX_I64,
+             "page table must use an integer dtype");
+  QF_REQUIRE(a->lens_dtype == QF_INDEX_I32 || a->lens_dtype == QF_INDEX_I64,
+             "sequence lengths must use an integer dtype");
+  QF_REQUIRE(a->split_k >= 1 && a->split_k <= 65535, "split_k must be in [1, 65535]");
+  QF_REQUIRE(a->num_pages >= 0 && a->num_pages < (1LL << 31), "num_pages out of range");
+  if (a->batch == 0) return QF_OK;
+  QF_REQUIRE(a->q && a->seq_lens, "q and seq_lens must not be null");
+  QF_REQUIRE(a->table_width == 0 || a->block_table, "block_table must not be null");
+  QF_REQUIRE(a->num_pages == 0 || (a->k_pool && a->v_pool), "K/V pools must not be null");
+  if (a->kv_fp8) QF_REQUIRE(a->k_scale && a->v_scale, "fp8 pools need k_scale and v_scale");
+  if (need_out) QF_REQUIRE(a->out != nullptr, "out must not be null");
+  if (a->split_k > 1 || a->out == nullptr) {
+    QF_REQUIRE(a->partial_out && a->partial_max && a->partial_sum,
+               "partial buffers must not be null");
+  }
+  const int64_t blocks = static_cast<int64_t>(a->batch) * a->q_heads * a->split_k;
+  QF_REQUIRE(blocks < (1LL << 31), "batch * heads * split_k exceeds the grid limit");
+  return QF_OK;
+}
+
+bool fast_path_ok(const qf_decode_attention_args* a) {
+  if (g_force_generic) return false;
+  if (a->head_dim != QF_HEAD_DIM || a->page_size != QF_PAGE_SIZE) return false;
+  if (a->q_heads != a->kv_heads * QF_GQA_GROUP) return false;
+  if (a->num_pages < 1 || a->kv_heads > 65535) return false;
+  if (a->q_stride_d != 1 || !aligned16(a->q) || (a->q_stride_b & 7) || (a->q_stride_h & 7)) return false;
+  if (a->k_stride_d != 1 || a->v_stride_d != 1) return false;
+  if (!aligned16(a->k_pool) || !aligned16(a->v_pool)) return false;
+  const int64_t unit = a->kv_fp8 ? 16 : 8;  // elements per 16 bytes
+  const int64_t strides[6] = {a->k_stride_page, a->k_stride_tok, a->k_stride_head,
+                              a->v_stride_page, a->v_stride_tok, a->v_stride_head};
+  for (int64_t s : strides) {
+    if (s <= 0 || (s % unit) != 0) return false;
+  }
+  return true;
+}
+
+template <bool PROFILE>
+int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long* cycles,
+                   cudaStream_t stream) {
+  if (a->batch == 0) return QF_OK;
+  int* status = status_word_for_current_device();
+  QF_REQUIRE(status != nullptr, "could not resolve the device status word");
+  void* out = direct_out ? a->out : nullptr;
+
+  if (fast_path_ok(a)) {
+    const int elem_code = a->kv_fp8 ? 2 : (a->dtype == QF_DTYPE_F16 ? 0 : 1);
+    CUtensorMap kmap, vmap;
+    int rc = pool_tensor_map(a->k_pool, elem_code, a->num_pages, a->kv_heads, a->k_stride_page,
+                             a->k_stride_tok, a->k_stride_head, &kmap);
+    if (rc != QF_OK) return rc;
+    rc = pool_tensor_map(a->v_pool, elem_code, a->num_pages, a->kv_heads, a->v_stride_page,
+                         a->v_stride_tok, a->v_stride_head, &vmap);
+    if (rc != QF_OK) return rc;
+    FastParams p{};
+    p.q = a->q, p.q_sb = a->q_stride_b, p.q_sh = a->q_stride_h;
+    p.block_table = a->block_table, p.bt_sb = a->table_stride_b, p.bt_sp = a->table_stride_p;
+    p.seq_lens = a->seq_lens, p.lens_stride = a->lens_stride;
+    p.k_scale = a->k_scale, p.v_scale = a->v_scale;
+    p.partial_out = a->partial_out, p.partial_max = a->partial_max, p.partial_sum = a->partial_sum;
+    p.out = out, p.o_sb = a->o_stride_b, p.o_sh = a->o_stride_h, p.o_sd = a->o_stride_d;
+    p.num_pages = a->num_pages;
+    p.cycles = cycles;
+    p.status = status;
+    p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
+    p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
+    p.stages = stages_for(a->kv_fp8 != 0);
+    p.scale_log2 = a->scale * kLog2e;
+    if (a->kv_fp8) {
+      return a->dtype == QF_DTYPE_F16
+                 ? launch_fast<__half, true, PROFILE>(kmap, vmap, p, stream)
+                 : launch_fast<__nv_bfloat16, true, PROFILE>(kmap, vmap, p, stream);
+    }
+    return a->dtype == QF_DTYPE_F16
+               ? launch_fast<__half, false, PROFILE>(kmap, vmap, p, stream)
+               : launch_fast<__nv_bfloat16, false, PROFILE>(kmap, vmap, p, stream);
+  }
+
+  QF_REQUIRE(!PROFILE, "stage profiling requires the native grouped-decode layout");
+  GenericParams g{};
+  g.q = a->q, g.q_sb = a->q_stride_b, g.q_sh = a->q_stride_h, g.q_sd = a->q_stride_d;
+  g.k_pool = a->k_pool, g.v_pool = a->v_pool;
+  g.k_sp = a->k_stride_page, g.k_st = a->k_stride_tok, g.k_sh = a->k_stride_head, g.k_sd = a->k_stride_d;
+  g.v_sp = a->v_stride_page, g.v_st = a->v_stride_tok, g.v_sh = a->v_stride_head, g.v_sd = a->v_stride_d;
+  g.block_table = a->block_table, g.bt_sb = a->table_stride_b, g.bt_sp = a->table_stride_p;
+  g.seq_lens = a->seq_lens, g.lens_stride = a->lens_stride;
+  g.k_scale = a->kv_fp8 ? a->k_scale : nullptr, g.v_scale = a->kv_fp8 ? a->v_scale : nullptr;
+  g.partial_out = a->partial_out, g.partial_max = a->partial_max, g.partial_sum = a->partial_sum;
+  g.out = out, g.o_sb = a->o_stride_b, g.o_sh = a->o_stride_h, g.o_sd = a->o_stride_d;
+  g.num_pages = a->num_pages;
+  g.status = status;
+  g.table_dtype = a->table_dtype, g.lens_dtype = a->lens_dtype;
+  g.batch = a->batch, g.q_heads = a->q_heads, g.kv_heads = a->kv_heads, g.head_dim = a->head_dim;
+  g.page_size = a->page_size, g.split_k = a->split_k;
+  g.scale = a->scale;
+  const unsigned blocks = static_cast<unsigned>(static_cast<int64_t>(a->batch) * a->q_heads * a->split_k);
+  const int threads = kGenericWarps * 32;
+  if (a->kv_fp8) {
+    if (a->dtype == QF_DTYPE_F16)
+      decode_partial_generic_kernel<__half, uint8_t><<<blocks, threads, 0, stream>>>(g);
+    else
+      decode_partial_generic_kernel<__nv_bfloat16, uint8_t><<<blocks, threads, 0, stream>>>(g);
+  } else if (a->dtype == QF_DTYPE_F16) {
+    decode_partial_generic_kernel<__half, __half><<<blocks, threads, 0, stream>>>(g);
+  } else {
+    decode_partial_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, threads, 0, stream>>>(g);
+  }
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
+int launch_reduce(const ReduceParams& r, int batch, int dtype, cudaStream_t stream) {
+  if (batch == 0) return QF_OK;
+  const unsigned blocks = static_cast<unsigned>(static_cast<int64_t>(batch) * r.q_heads);
+  const int threads = ((r.head_dim + 31) / 32) * 32;
+  if (dtype == QF_DTYPE_F16)
+    splitk_reduce_kernel<__half><<<blocks, threads, 0, stream>>>(r);
+  else
+    splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(r);
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
+}  // namespace
+}  // namespace qf
+
+extern "C" {
+
+int qf_grouped_gqa_splitk_partial_out(const qf_decode_attention_args* args, void* stream) {
+  const int rc = qf::validate(args, false);
+  if (rc != QF_OK) return rc;
+  const bool direct = args->split_k == 1 && args->out != nullptr;
+  return qf::launch_partial<false>(args, direct, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args, int64_t* cycles,
+                                      void* stream) {
+  const int rc = qf::validate(args, false);
+  if (rc != QF_OK) return rc;
+  QF_REQUIRE(cycles != nullptr, "cycles must not be null");
+  const bool direct = args->split_k == 1 && args->out != nullptr;
+  return qf::launch_partial<true>(args, direct, reinterpret_cast<long long*>(cycles),
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int qf_splitk_reduce(const float* partial_out, const float* partial_max, const float* partial_sum,
+                     int64_t po_stride_b, int64_t po_stride_k, int64_t po_stride_h,
+                     int64_t po_stride_d, int64_t pm_stride_b, int64_t pm_stride_k,
+                     int64_t pm_stride_h, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                     int64_t o_stride_d, int32_t batch, int32_t q_heads, int32_t head_dim,
+                     int32_t split_k, int32_t dtype, void* stream) {
+  QF_REQUIRE(batch >= 0 && q_heads >= 1 && split_k >= 1, "invalid batch, head or split count");
+  QF_REQUIRE(head_dim >= 1 && head_dim <= 256, "head_dim must be in [1, 256]");
+  QF_REQUIRE(dtype == QF_DTYPE_F16 || dtype == QF_DTYPE_BF16, "out must be float16 or bfloat16");
+  if (batch == 0) return QF_OK;
+  QF_REQUIRE(partial_out && partial_max && partial_sum && out, "buffers must not be null");
+  qf::ReduceParams r{};
+  r.po = partial_out, r.pm = partial_max, r.ps = partial_sum;
+  r.po_sb = po_stride_b, r.po_sk = po_stride_k, r.po_sh = po_stride_h, r.po_sd = po_stride_d;
+  r.pm_sb = pm_stride_b, r.pm_sk = pm_stride_k, r.pm_sh = pm_stride_h;
+  r.out = out, r.o_sb = o_stride_b, r.o_sh = o_stride_h, r.o_sd = o_stride_d;
+  r.q_heads = q_heads, r.head_dim = head_dim, r.split_k = split_k;
+  return qf::launch_reduce(r, batch, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {
+  int rc = qf::validate(args, true);
+  if (rc != QF_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (args->split_k == 1) return qf::launch_partial<false>(args, true, nullptr, s);
+  rc = qf::launch_partial<false>(args, false, nullptr, s);
+  if (rc != QF_OK) return rc;
+  qf::ReduceParams r{};
+  r.po = args->partial_out, r.pm = args->partial_max, r.ps = args->partial_sum;
+  const int64_t hq = args->q_heads, d = args->head_dim, k = args->split_k;
+  r.po_sb = k * hq * d, r.po_sk = hq * d, r.po_sh = d, r.po_sd = 1;
+  r.pm_sb = k * hq, r.pm_sk = hq, r.pm_sh = 1;
+  r.out = args->out, r.o_sb = args->o_stride_b, r.o_sh = args->o_stride_h, r.o_sd = args->o_stride_d;
+  r.q_heads = args->q_heads, r.head_dim = args->head_dim, r.split_k = args->split_k;
+  return qf::launch_reduce(r, args->batch, args->dtype, s);
+}
+
+int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_fp8, int64_t* info) {
+  QF_REQUIRE(info != nullptr, "info must not be null");
+  QF_REQUIRE(dtype == QF_DTYPE_F16 || dtype == QF_DTYPE_BF16, "dtype must be float16 or bfloat16");
+  const void* kernel;
+  if (kv_fp8) {
+    kernel = dtype == QF_DTYPE_F16
+                 ? reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__half, true, false>)
+                 : reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__nv_bfloat16, true, false>);
+  } else {
+    kernel = dtype == QF_DTYPE_F16
+                 ? reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__half, false, false>)
+                 : reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__nv_bfloat16, false, false>);
+  }
+  int previous = 0;
+  QF_CUDA(cudaGetDevice(&previous));
+  QF_CUDA(cudaSetDevice(device));
+  const int stages = qf::stages_for(kv_fp8 != 0);
+  const size_t smem = qf::fast_smem_bytes(kv_fp8 != 0, stages);
+  cudaFuncAttributes attr{};
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+  if (err == cudaSuccess) err = cudaFuncGetAttributes(&attr, kernel);
+  int active = 0;
+  if (err == cudaSuccess) {
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&active, kernel, qf::kFastThreads, smem);
+  }
+  cudaDeviceProp prop{};
+  if (err == cudaSuccess) err = cudaGetDeviceProperties(&prop, device);
+  cudaSetDevice(previous);
+  if (err != cudaSuccess) return qf::cuda_fail(err, "kernel diagnostics");
+  info[0] = attr.numRegs;
+  info[1] = static_cast<int64_t>(attr.sharedSizeBytes);
+  info[2] = static_cast<int64_t>(smem);
+  info[3] = static_cast<int64_t>(attr.localSizeBytes);
+  info[4] = attr.maxThreadsPerBlock;
+  info[5] = attr.binaryVersion;
+  info[6] = attr.ptxVersion;
+  info[7] = qf::kFastThreads;
+  info[8] = active;
+  info[9] = prop.maxThreadsPerMultiProcessor / 32;
+  info[10] = stages;
+  info[11] = prop.multiProcessorCount;
+  return QF_OK;
+}
+
+int qf_set_tuning(int32_t stages, int32_t force_generic) {
+  QF_REQUIRE(stages >= 0 && stages <= qf::kMaxStages, "stages must be in [0, %d]", qf::kMaxStages);
+  qf::g_tuned_stages = stages;
+  qf::g_force_generic = force_generic ? 1 : 0;
+  return QF_OK;
+}
+
+}  // extern "C"
