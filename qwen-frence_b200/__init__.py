@@ -22,6 +22,7 @@ current torch stream; none has a CPU fallback):
 
 from __future__ import annotations
 
+import importlib
 import importlib.util
 import sys
 from pathlib import Path
@@ -66,9 +67,11 @@ def kernel_module(name):
 def __getattr__(name):
     if name in _EXPORTS:
         return getattr(kernel_module(_EXPORTS[name]), name)
+    if name == "cabi":
+        # one shared instance with the drop-in modules, which load it by path
+        return _load("qf_hotpath_cabi", PACKAGE_DIR / "_cabi.py")
     if name in _LOCAL:
-        stem = _LOCAL[name]
-        return _load(f"qf_hotpath_{stem.lstrip('_')}", PACKAGE_DIR / f"{stem}.py")
+        return importlib.import_module(f"{__name__}.{_LOCAL[name]}")
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 

@@ -1,0 +1,201 @@
+"""One decode step of the hot path over all layers: for every layer, the packed-QKV
+RoPE + paged KV write, then GQA paged decode attention over the block tables.
+
+This is the loop body of the reference's graph decoder restricted to the two
+stages this package owns (engine/graph/paged_graph_decoder.py:234-289):
+the write for position p precedes, on the same stream, the attention that
+reads seq_len = p + 1 tokens.  The projections around it (QKV GEMM, o_proj,
+MLP) are outside the path; the packed QKV rows arrive as an input.
+
+`DecodeStep` owns the device state of one rank (per-layer pools, static
+metadata buffers at fixed addresses, partial buffers), can capture the whole
+step in a CUDA graph as the reference engine does
+(engine/graph/paged_graph_decoder.py:124-142), and offers `run_from_host`,
+the end-to-end call that takes pinned host buffers, copies them in, replays
+and copies the result out.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import kv_layout
+
+
+class DecodeStep:
+    def __init__(self, workload, device, *, split_k=None, dtype=torch.float16,
+                 fill_pools=True, package=None):
+        import sys
+
+        self.package = package if package is not None else sys.modules[__package__]
+        self.workload = workload
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.fp8 = workload.fp8
+        self.layers = workload.layers
+        self.batch = workload.batch
+        self.split_k = int(split_k) if split_k else kv_layout.plan_split_k(
+            max(self.batch, 1), workload.max_context,
+            sm_count=torch.cuda.get_device_properties(self.device).multi_processor_count)
+        self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 else 3)
+
+        shape = (workload.num_pages, kv_layout.PAGE_SIZE, kv_layout.KV_HEADS, kv_layout.HEAD_DIM)
+        pool_dtype = torch.uint8 if self.fp8 else dtype
+        self.k_pools = [torch.empty(shape, dtype=pool_dtype, device=self.device) for _ in range(self.layers)]
+        self.v_pools = [torch.empty(shape, dtype=pool_dtype, device=self.device) for _ in range(self.layers)]
+        self.k_scales = self.v_scales = None
+        if self.fp8:
+            scale_shape = (workload.num_pages, kv_layout.KV_HEADS)
+            self.k_scales = [torch.ones(scale_shape, dtype=torch.float32, device=self.device) for _ in range(self.layers)]
+            self.v_scales = [torch.ones(scale_shape, dtype=torch.float32, device=self.device) for _ in range(self.layers)]
+        if fill_pools:
+            self._fill_pools()
+
+        # Static buffers: a captured graph reads these addresses on every replay.
+        b = self.batch
+        self.packed = torch.zeros((self.layers, b, 2048), dtype=dtype, device=self.device)
+        self.positions = workload.positions.to(self.device)
+        self.seq_lens = workload.seq_lens.to(self.device)
+        self.slot_mapping = workload.slot_mapping.to(self.device)
+        self.block_table = workload.block_table.to(self.device)
+        # attention output of the last layer (what the step hands on); under capture
+        # it lives at a fixed address in the graph's private pool
+        self.result = torch.zeros((b, kv_layout.Q_HEADS, kv_layout.HEAD_DIM), dtype=dtype, device=self.device)
+        k = self.split_k
+        self.partials = None
+        if k > 1:
+            self.partials = (
+                torch.empty((b, k, kv_layout.Q_HEADS, kv_layout.HEAD_DIM), dtype=torch.float32, device=self.device),
+                torch.empty((b, k, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
+                torch.empty((b, k, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
+            )
+        self.graph = None
+        self._host = None
+
+    # ------------------------------------------------------------------ setup
+    def _fill_pools(self):
+        """Random N(0,1)*0.5 K/V in the live pages (the rest of the pool is never
+        read); FP8 pools are quantised page by page with the library's quantiser."""
+        w = self.workload
+        live = w.live_pages.to(self.device)
+        generator = torch.Generator(device=self.device).manual_seed(4000 + w.seed)
+        chunk = 4096
+        for layer in range(self.layers):
+            for pool, scales in ((self.k_pools[layer], self.k_scales), (self.v_pools[layer], self.v_scales)):
+                for start in range(0, live.numel(), chunk):
+                    index = live[start:start + chunk]
+                    values = torch.randn((index.numel(), *pool.shape[1:]), generator=generator,
+                                         device=self.device, dtype=torch.float32).mul_(0.5).to(self.dtype)
+                    if self.fp8:
+                        bits, scale = self.package.quantize_kv_pool_e4m3(values)
+                        pool[index] = bits
+                        scales[layer][index] = scale
+                    else:
+                        pool[index] = values
+
+    def load_packed_rows(self):
+        """Setup: fill the static packed-QKV buffer of every layer (untimed)."""
+        from . import workloads
+
+        for layer in range(self.layers):
+            self.packed[layer].copy_(workloads.packed_qkv_rows(self.workload, layer, self.device, self.dtype))
+
+    # ------------------------------------------------------------------- step
+    def layer(self, index):
+        """RoPE + KV write, then attention, for one layer, on the current stream."""
+        pkg = self.package
+        if self.fp8:
+            q = pkg.packed_qkv_rope_cache_fp8(
+                self.packed[index], self.positions, self.slot_mapping, self.k_pools[index],
+                self.v_pools[index], self.k_scales[index], self.v_scales[index])
+            out = pkg.grouped_splitk_decode_attention_fp8(
+                q, self.k_pools[index], self.v_pools[index], self.k_scales[index], self.v_scales[index],
+                self.block_table, self.seq_lens, split_k=self.split_k,
+                partials=self._fp8_partials())
+        else:
+            q = pkg.packed_qkv_rope_cache(
+                self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index])
+            out = pkg.grouped_splitk_decode_attention(
+                q, self.k_pools[index], self.v_pools[index], self.block_table, self.seq_lens,
+                split_k=self.split_k, partials=self.partials)
+        return out
+
+    def _fp8_partials(self):
+        if self.partials is not None:
+            return self.partials
+        b = self.batch
+        self.partials = (
+            torch.empty((b, 1, kv_layout.Q_HEADS, kv_layout.HEAD_DIM), dtype=torch.float32, device=self.device),
+            torch.empty((b, 1, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
+            torch.empty((b, 1, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
+        )
+        return self.partials
+
+    def step(self):
+        """All layers, eagerly, on the current stream."""
+        if self.batch == 0:
+            return self.result
+        for index in range(self.layers):
+            out = self.layer(index)
+        self.result = out
+        return out
+
+    def capture(self, warmup=3):
+        """Warm up on a side stream, then record the whole step into one CUDA graph."""
+        if self.batch == 0:
+            return None
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                self.step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            self.step()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.graph = graph
+        return graph
+
+    def replay(self):
+        if self.batch == 0 or self.graph is None:
+            return self.step()
+        self.graph.replay()
+        return self.result
+
+    # ------------------------------------------------------------- end to end
+    def host_buffers(self):
+        """Pinned host staging: the step's inputs and its result."""
+        if self._host is None:
+            pin = dict(pin_memory=True)
+            self._host = dict(
+                packed=torch.empty(self.packed.shape, dtype=self.dtype, **pin),
+                positions=torch.empty(self.positions.shape, dtype=self.positions.dtype, **pin),
+                seq_lens=torch.empty(self.seq_lens.shape, dtype=self.seq_lens.dtype, **pin),
+                slot_mapping=torch.empty(self.slot_mapping.shape, dtype=self.slot_mapping.dtype, **pin),
+                block_table=torch.empty(self.block_table.shape, dtype=self.block_table.dtype, **pin),
+                out=torch.empty(self.result.shape, dtype=self.dtype, **pin),
+            )
+            for key in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"):
+                self._host[key].copy_(getattr(self, key))
+        return self._host
+
+    def h2d_bytes(self):
+        host = self.host_buffers()
+        return sum(host[k].numel() * host[k].element_size()
+                   for k in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"))
+
+    def d2h_bytes(self):
+        host = self.host_buffers()
+        return host["out"].numel() * host["out"].element_size()
+
+    def run_from_host(self):
+        """Host inputs in, result out: H2D copies of the step's inputs from pinned
+        memory, the step (graph replay when captured), D2H of the last layer's
+        attention output.  Asynchronous on the current stream; the caller synchronises."""
+        host = self.host_buffers()
+        for key in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"):
+            getattr(self, key).copy_(host[key], non_blocking=True)
+        result = self.replay()
+        host["out"].copy_(result, non_blocking=True)
+        return host["out"]

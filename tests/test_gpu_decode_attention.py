@@ -1,0 +1,256 @@
+"""GPU parity of GQA paged decode attention (split-K partial pass + combine) against
+the CPU oracle and the committed reference outputs.  Every call goes through the
+C ABI via the drop-in modules.
+
+Bar: max-abs 2e-3 and rel 1e-2 against an fp32-accumulated reference for fp16
+(the reference's own gate atol = rtol = 2e-3 is applied; 2e-2 for bf16)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import (assert_attention_close, attention_case_tensors, make_paged_inputs, with_gaps)
+
+pytestmark = pytest.mark.gpu
+
+
+def _to(device, *tensors):
+    return tuple(t.to(device) for t in tensors)
+
+
+def _fast_path_inputs(device, lengths, **kwargs):
+    """Contiguous Qwen-geometry inputs (the TMA kernel's layout) on the device."""
+    q, k, v, table, lens = make_paged_inputs(lengths, **kwargs)
+    return (q, k, v, table, lens), _to(device, q, k, v, table, lens)
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 7, 22])
+def test_golden_cases_every_split(package, attention_golden, cuda_device, split_k):
+    """Reference outputs for ragged / strided / NaN-poisoned / boundary / adversarial
+    inputs.  Strided cases are re-strided on the device (generic kernel); the
+    contiguous ones take the TMA kernel."""
+    for name in attention_golden.names:
+        fields = attention_golden.case(name)
+        q, k, v, table, lens, scale, expected = attention_case_tensors(fields)
+        dq, dk, dv, dtable, dlens = _to(cuda_device, q, k, v, table, lens)
+        if tuple(fields["q_stride"]) != tuple(q.stride()):
+            dq, dv, dtable, dlens = map(with_gaps, (dq, dv, dtable, dlens))
+        out = package.grouped_splitk_decode_attention(dq, dk, dv, dtable, dlens, split_k=split_k, scale=scale)
+        assert_attention_close(out, expected)
+        assert torch.isfinite(out.float()).all(), name
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("split_k", [1, 3, 8])
+def test_fast_kernel_ragged_poisoned(package, oracle, cuda_device, dtype, split_k):
+    """Contiguous layout -> TMA kernel.  Lengths straddle page boundaries, the tail
+    of every last page is NaN, the table is padded with -1."""
+    lengths = [0, 1, 15, 16, 17, 31, 32, 33, 81, 100, 129, 513, 1000]
+    host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=42, poison=True)
+    expected = oracle.paged_attention(*host)
+    out = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+    assert_attention_close(out, expected)
+    if split_k >= 2:
+        native = package.native_grouped_splitk_decode_attention(*dev, split_k=split_k)
+        assert torch.equal(native, out)
+
+
+def test_fast_and_generic_kernels_agree(package, oracle, cuda_device):
+    lengths = [5, 64, 257, 2048]
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=3, value_scale=0.5)
+    fast = package.grouped_splitk_decode_attention(*dev, split_k=4)
+    package.cabi.set_tuning(force_generic=True)
+    try:
+        generic = package.grouped_splitk_decode_attention(*dev, split_k=4)
+    finally:
+        package.cabi.set_tuning()
+    expected = oracle.paged_attention(*host)
+    assert_attention_close(fast, expected)
+    assert_attention_close(generic, expected)
+
+
+@pytest.mark.parametrize("stages", [2, 3, 4, 12])
+def test_pipeline_depths(package, oracle, cuda_device, stages):
+    """Ring depths from the minimum to the maximum give the same answer; partitions
+    longer than 32 pages cross the page-id batch boundary."""
+    lengths = [16 * 70 + 5, 16 * 33, 16 * 32, 40]
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=8)
+    expected = oracle.paged_attention(*host)
+    package.cabi.set_tuning(stages=stages)
+    try:
+        for split_k in (1, 2):
+            out = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+            assert_attention_close(out, expected)
+    finally:
+        package.cabi.set_tuning()
+
+
+def test_partials_match_oracle_partition_by_partition(package, oracle, cuda_device):
+    """The fp32 partial buffers, partition by partition: out/sum rescaled to a
+    common offset equal the oracle's; empty partitions are (0, -inf, 0)."""
+    lengths = [0, 1, 17, 100, 700]
+    split_k = 5
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=11, value_scale=0.5)
+    batch = len(lengths)
+    partials = (torch.full((batch, split_k, 12, 128), float("nan"), device=cuda_device),
+                torch.full((batch, split_k, 12), float("nan"), device=cuda_device),
+                torch.full((batch, split_k, 12), float("nan"), device=cuda_device))
+    out = package.native_grouped_splitk_decode_attention(*dev, split_k=split_k, partials=partials)
+    po, pm, ps = (t.cpu() for t in partials)
+    ro, rm, rs = oracle.splitk_partial(*host, split_k=split_k)
+    empty = rs == 0
+    assert torch.equal(ps == 0, empty)
+    assert torch.isinf(pm[empty]).all() and (pm[empty] < 0).all()
+    assert (po[empty] == 0).all()
+    # common offset: oracle's exact maximum
+    factor = torch.where(empty, torch.zeros_like(pm), torch.exp(pm - rm))
+    torch.testing.assert_close(ps * factor, rs, atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(po * factor[..., None], ro, atol=2e-3, rtol=2e-3)
+    assert_attention_close(out, oracle.splitk_reduce(ro, rm, rs))
+    # the standalone combine entry point on the kernel's own partials
+    again = package.splitk_reduce(*partials, torch.empty_like(out))
+    assert torch.equal(again, out)
+
+
+def test_known_answers(package, cuda_device):
+    """experiments/tests/test_grouped_splitk_pipelined.py:40-66, :112-119."""
+    dev = cuda_device
+    q, k, v, table, lens = make_paged_inputs([0, 1, 17], poison=True)
+    q.zero_()
+    v[:, :, 0] = 3
+    v[:, :, 1] = 9
+    expected = torch.zeros_like(q)
+    expected[1:, :6] = 3
+    expected[1:, 6:] = 9
+    for split_k in (1, 2, 7):
+        out = package.grouped_splitk_decode_attention(*_to(dev, q, k, v, table, lens), split_k=split_k)
+        assert torch.equal(out.cpu(), expected)
+
+    q, k, v, table, lens = make_paged_inputs([1024])
+    q.zero_(), k.zero_(), v.fill_(128)
+    for split_k in (1, 2, 8):
+        out = package.grouped_splitk_decode_attention(*_to(dev, q, k, v, table, lens), split_k=split_k)
+        assert torch.equal(out.cpu(), torch.full_like(q, 128))  # fp32 partials: no fp16 overflow
+
+    q, k, v, table, lens = make_paged_inputs([0, 0])
+    for split_k in (1, 7):
+        out = package.grouped_splitk_decode_attention(
+            *_to(dev, q, k, v), table[:, :0].to(dev), lens.to(dev), split_k=split_k)
+        assert torch.equal(out.cpu(), torch.zeros_like(q))
+
+
+def test_large_scores_move_the_offset(package, oracle, cuda_device):
+    """Scores that grow along the sequence force the running offset to move many
+    times (the lazy-rescale branch), and scores far apart underflow cleanly."""
+    lengths = [300, 45]
+    q, k, v, table, lens = make_paged_inputs(lengths, seed=5)
+    ramp = torch.linspace(0.0, 6.0, 16)[None, :, None, None]
+    k.mul_(ramp.half())  # later rows of every page dominate
+    host = (q, k, v, table, lens)
+    expected = oracle.paged_attention(*host, scale=1.0)
+    for split_k in (1, 3):
+        out = package.grouped_splitk_decode_attention(*_to(cuda_device, *host), split_k=split_k, scale=1.0)
+        assert_attention_close(out, expected)
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int32, torch.int64])
+def test_index_dtypes_and_q_view(package, oracle, cuda_device, index_dtype):
+    """int32/int64 metadata; q as the (B, 12, 1, 128)[:, :, 0, :] view the graph
+    decoder passes (engine/graph/paged_graph_decoder.py:283-284)."""
+    host, dev = _fast_path_inputs(cuda_device, [33, 130, 7], seed=2)
+    dq, dk, dv, dtable, dlens = dev
+    q4 = dq[:, :, None, :].contiguous()
+    out = package.grouped_splitk_decode_attention(
+        q4[:, :, 0, :], dk, dv, dtable.to(index_dtype), dlens.to(index_dtype), split_k=2)
+    assert_attention_close(out, oracle.paged_attention(*host))
+
+
+def test_other_geometries_use_generic_kernel(package, oracle, cuda_device):
+    """Page 32, head_dim 64, group 4 / 3 KV heads: what the reference's Triton kernel
+    accepts beyond the Qwen geometry."""
+    host = make_paged_inputs([31, 32, 33, 129], page_size=32, kv_heads=3, group=4, head_dim=64, seed=6)
+    expected = oracle.paged_attention(*host)
+    for split_k in (1, 3):
+        out = package.grouped_splitk_decode_attention(*_to(cuda_device, *host), split_k=split_k)
+        assert_attention_close(out, expected)
+
+
+def test_graph_replay_reads_updated_inputs(package, oracle, cuda_device):
+    """Capture once, mutate q and seq_lens in place, replay
+    (experiments/tests/test_grouped_splitk_pipelined.py:121-137)."""
+    host, dev = _fast_path_inputs(cuda_device, [70, 70], seed=0)
+    dq, dk, dv, dtable, dlens = dev
+    for split_k in (1, 7):
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            package.grouped_splitk_decode_attention(dq, dk, dv, dtable, dlens, split_k=split_k)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            actual = package.grouped_splitk_decode_attention(dq, dk, dv, dtable, dlens, split_k=split_k)
+        torch.cuda.current_stream().wait_stream(stream)
+        dq.mul_(0.5)
+        dlens.copy_(torch.tensor([0, 17], device=cuda_device, dtype=torch.int32))
+        graph.replay()
+        torch.cuda.synchronize()
+        expected = oracle.paged_attention(dq.cpu(), host[1], host[2], host[3], dlens.cpu())
+        assert_attention_close(actual, expected)
+        dq.mul_(2.0)
+        dlens.copy_(host[4].to(cuda_device))
+
+
+def test_preallocated_partials_and_k1_contract(package, oracle, cuda_device):
+    """K=1 returns partial_out.squeeze(1) in the q dtype; preallocated buffers are used."""
+    host, dev = _fast_path_inputs(cuda_device, [1, 17, 81], seed=1)
+    expected = oracle.paged_attention(*host)
+    out = package.grouped_splitk_decode_attention(*dev, split_k=1)
+    assert out.dtype == torch.float16 and out.shape == (3, 12, 128)
+    assert_attention_close(out, expected)
+    partials = (torch.empty(3, 4, 12, 128, device=cuda_device), torch.empty(3, 4, 12, device=cuda_device),
+                torch.empty(3, 4, 12, device=cuda_device))
+    out = package.grouped_splitk_decode_attention(*dev, split_k=4, partials=partials)
+    assert_attention_close(out, expected)
+    with pytest.raises(ValueError, match="do not match this launch shape"):
+        package.grouped_splitk_decode_attention(*dev, split_k=5, partials=partials)
+
+
+def test_validation_errors(package, cuda_device):
+    (_, dev) = _fast_path_inputs(cuda_device, [17, 81])
+    q, k, v, table, lens = dev
+    for bad in (0, -1, 1.5):
+        with pytest.raises(ValueError, match="positive integer"):
+            package.grouped_splitk_decode_attention(q, k, v, table, lens, split_k=bad)
+    with pytest.raises(ValueError, match="divisible"):
+        package.grouped_splitk_decode_attention(q[:, :11], k, v, table, lens, split_k=2)
+    with pytest.raises(ValueError, match="heads_per_program"):
+        package.grouped_splitk_decode_attention(q, k, v, table, lens, split_k=2, heads_per_program=4)
+    with pytest.raises(ValueError, match="split_k >= 2"):
+        package.native_grouped_splitk_decode_attention(q, k, v, table, lens, split_k=1)
+    with pytest.raises(ValueError, match="integer tensors"):
+        package.grouped_splitk_decode_attention(q, k, v, table.float(), lens, split_k=2)
+
+
+def test_diagnostics_and_stage_cycles(package, cuda_device):
+    (_, dev) = _fast_path_inputs(cuda_device, [400, 90])
+    q, k, v, table, lens = dev
+    info = package.native_grouped_decode_diagnostics(q, table)
+    assert info["threads_per_block"] == 256 and info["binary_version"] >= 100
+    assert info["active_blocks_per_sm"] >= 1 and info["registers_per_thread"] <= 128
+    cycles = package.native_grouped_stage_cycles(q, k, v, table, lens, split_k=2)
+    assert cycles.shape == (2, 2, 2, 4) and cycles.dtype == torch.int64
+    assert (cycles[..., 1] > 0).all()
+
+
+def test_bad_page_id_is_reported_not_dereferenced(package, cuda_device):
+    """A page id outside the pool reads as zeros and raises the status word; no fault."""
+    (_, dev) = _fast_path_inputs(cuda_device, [40])
+    q, k, v, table, lens = dev
+    table = table.clone()
+    table[0, 1] = 10_000
+    out = package.grouped_splitk_decode_attention(q, k, v, table, lens, split_k=1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert package.cabi.device_status() == 2
+    assert package.cabi.device_status() == 0

@@ -1,0 +1,156 @@
+"""GPU tests of the whole decode step (RoPE + KV write, then attention, per layer)
+on the benchmark configurations, through the public operators, eagerly, under CUDA
+graph capture and through the host-buffer entry; plus the plugin boundary: the
+drop-in files loaded the way the reference's kernel_dispatch loads them."""
+
+from __future__ import annotations
+
+import importlib.util
+
+import pytest
+import torch
+
+from conftest import assert_attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_step(oracle, workload, packed, k_pool, v_pool):
+    """One layer on the CPU oracle; mutates the CPU pools, returns (q, out)."""
+    q = oracle.packed_qkv_rope_cache(packed, workload.positions, workload.slot_mapping, k_pool, v_pool)
+    out = oracle.paged_attention(q, k_pool, v_pool, workload.block_table, workload.seq_lens)
+    return q, out
+
+
+def _check_layer(oracle, step, layer, out_dev):
+    w = step.workload
+    k_cpu, v_cpu = step.k_pools[layer].cpu(), step.v_pools[layer].cpu()
+    slots = w.slot_mapping
+    # rebuild the pre-step pool: the written rows are the only difference
+    packed = step.packed[layer].cpu()
+    k_ref, v_ref = k_cpu.clone(), v_cpu.clone()
+    _, out_ref = _oracle_step(oracle, w, packed, k_ref, v_ref)
+    assert torch.equal(v_cpu.view(-1, 2, 128)[slots], packed[:, 1792:].view(-1, 2, 128))
+    ulp = oracle.ulp_distance_fp16(k_cpu.view(-1, 2, 128)[slots], k_ref.view(-1, 2, 128)[slots],
+                                   packed[:, 1536:1792].view(-1, 2, 128))
+    assert ulp.max().item() <= 1.0
+    assert_attention_close(out_dev, out_ref)
+
+
+def test_cpu_runnable_configuration(package, oracle, cuda_device):
+    """Batch 8, context 512, one layer, 512-page permuted pool: eager, captured and
+    host-buffer runs agree with the oracle and with each other."""
+    workload = package.workloads.build_workload("cpu_single_layer_b8")
+    for split_k in (1, 4):
+        step = package.decode_step.DecodeStep(workload, cuda_device, split_k=split_k, package=package)
+        step.load_packed_rows()
+        eager = step.step().clone()
+        _check_layer(oracle, step, 0, eager)
+        step.capture()
+        replayed = step.replay().clone()
+        assert torch.equal(replayed, eager)
+        host_out = step.run_from_host()
+        torch.cuda.synchronize()
+        assert torch.equal(host_out.to(cuda_device), eager)
+        assert step.h2d_bytes() == 8 * 2048 * 2 + 8 * (4 + 4 + 8) + 8 * 33 * 4
+        assert step.d2h_bytes() == 8 * 12 * 128 * 2
+
+
+@pytest.mark.parametrize("name,kwargs", [
+    ("decode_b64", dict()),
+    ("long_skew_b4", dict()),
+    ("sweep_b256", dict(pool_pages=40000)),
+])
+def test_full_size_single_layer(package, oracle, cuda_device, name, kwargs):
+    """Full batch and context lengths of the large configurations, one layer:
+    checked against the oracle row by row, and split-count invariance."""
+    workload = package.workloads.build_workload(name, layers=1, **kwargs)
+    step = package.decode_step.DecodeStep(workload, cuda_device, package=package)
+    step.load_packed_rows()
+    out = step.step().clone()
+    _check_layer(oracle, step, 0, out)
+    other = package.decode_step.DecodeStep(workload, cuda_device, split_k=max(1, step.split_k // 2),
+                                           fill_pools=False, package=package)
+    other.k_pools, other.v_pools, other.packed = step.k_pools, step.v_pools, step.packed
+    assert_attention_close(other.step(), out)
+
+
+def test_page_placement_invariance(package, cuda_device):
+    """Moving every page somewhere else (pool and table permuted together) leaves the
+    result bit-identical: only slot arithmetic changed."""
+    workload = package.workloads.build_workload("decode_b64", layers=1, batch=16)
+    step = package.decode_step.DecodeStep(workload, cuda_device, split_k=3, package=package)
+    step.load_packed_rows()
+    before = step.step().clone()
+    generator = torch.Generator().manual_seed(77)
+    perm = torch.randperm(workload.num_pages, generator=generator).to(cuda_device)  # new id of old page
+    inverse = torch.empty_like(perm)
+    inverse[perm] = torch.arange(workload.num_pages, device=cuda_device)
+    step.k_pools[0] = step.k_pools[0][inverse].contiguous()
+    step.v_pools[0] = step.v_pools[0][inverse].contiguous()
+    step.block_table = perm[step.block_table.long()].int()
+    step.slot_mapping = perm[(step.slot_mapping // 16)] * 16 + step.slot_mapping % 16
+    assert torch.equal(step.step(), before)
+
+
+def test_multi_layer_fp8_configuration(package, oracle, cuda_device):
+    """Two layers of the FP8 configuration (batch 128, context 2048) against the
+    fp16 kernels and the oracle on the dequantised cache."""
+    workload = package.workloads.build_workload("fp8_b128", layers=2, batch=32)
+    step = package.decode_step.DecodeStep(workload, cuda_device, package=package)
+    step.load_packed_rows()
+    out = step.step()
+    layer = 1
+    k_hat = package.dequantize_kv_pool_e4m3(step.k_pools[layer], step.k_scales[layer])
+    v_hat = package.dequantize_kv_pool_e4m3(step.v_pools[layer], step.v_scales[layer])
+    q = oracle.rope(step.packed[layer].cpu()[:, :1536].view(-1, 12, 128), workload.positions)
+    expected = oracle.paged_attention(q, k_hat.cpu(), v_hat.cpu(), workload.block_table, workload.seq_lens)
+    assert_attention_close(out, expected)
+    step.capture()
+    assert torch.equal(step.replay(), out)
+
+
+def test_files_load_the_way_kernel_dispatch_loads_them(package, oracle, cuda_device):
+    """baseline/kernel_dispatch.py:13-23 imports custom_kernels/<name>.py by file path
+    under a private module name; the drop-in directory must work the same way."""
+    def load(name):
+        path = package.KERNEL_DIR / f"{name}.py"
+        spec = importlib.util.spec_from_file_location(f"_inference_engine_{name}", path)
+        module = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(module)
+        return module
+
+    names = {
+        "rope_kv_write": ("rope_kv_write", "native_decode_rope_kv_write"),
+        "packed_qkv_rope_cache": ("packed_qkv_rope_cache",),
+        "paged_decode_grouped_splitk": ("grouped_splitk_decode_attention",),
+        "paged_decode_native_grouped": ("native_grouped_splitk_decode_attention",
+                                        "native_grouped_decode_diagnostics", "native_grouped_stage_cycles"),
+    }
+    modules = {name: load(name) for name in names}
+    for name, functions in names.items():
+        for function in functions:
+            assert callable(getattr(modules[name], function))
+
+    workload = package.workloads.build_workload("cpu_single_layer_b8")
+    step = package.decode_step.DecodeStep(workload, cuda_device, split_k=8, package=package)
+    step.load_packed_rows()
+    # the accepted decode variant: (B, H, 1, D) views + native_decode_rope_kv_write,
+    # then the dispatch call with the engine's frozen config
+    packed = step.packed[0]
+    batch = packed.shape[0]
+    q = packed[:, :1536].view(batch, 1, 12, 128).transpose(1, 2)
+    k = packed[:, 1536:1792].view(batch, 1, 2, 128).transpose(1, 2)
+    v = packed[:, 1792:].view(batch, 1, 2, 128).transpose(1, 2)
+    q_rot = modules["rope_kv_write"].native_decode_rope_kv_write(
+        q, k, v, step.positions, step.slot_mapping, step.k_pools[0], step.v_pools[0],
+        base=1_000_000.0, rotate_q=True)
+    config = package.kv_layout.select_splitk_config(workload.max_context)
+    out = modules["paged_decode_grouped_splitk"].grouped_splitk_decode_attention(
+        q_rot[:, :, 0, :], step.k_pools[0], step.v_pools[0], step.block_table, step.seq_lens,
+        scale=None, partials=None, **config)
+    native = modules["paged_decode_native_grouped"].native_grouped_splitk_decode_attention(
+        q_rot[:, :, 0, :], step.k_pools[0], step.v_pools[0], step.block_table, step.seq_lens,
+        scale=None, partials=None, split_k=config["split_k"])
+    _check_layer(oracle, step, 0, out)
+    assert torch.equal(native, out)

@@ -1,0 +1,110 @@
+"""GPU parity of the FP8-e4m3 KV-cache variant (per-page scales, in-kernel
+dequantisation).  No reference kernel exists for this layout, so parity is pinned
+as: codec bytes equal the reference codec's (through the oracle, which is pinned to
+it), and attention over the FP8 cache equals the fp16 path run on the dequantised
+cache, within the attention tolerance."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import assert_attention_close, make_paged_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def test_page_quantizer_is_byte_exact(package, oracle, cuda_device):
+    generator = torch.Generator().manual_seed(5)
+    pool = (torch.randn(40, 16, 2, 128, generator=generator) * 0.5).half()
+    pool[3] = 0
+    pool[4, :, 1] = 1000.0
+    pool8, scales = package.quantize_kv_pool_e4m3(pool.to(cuda_device))
+    ref8, ref_scales = oracle.quantize_pages(pool)
+    assert torch.equal(scales.cpu(), ref_scales)
+    assert torch.equal(pool8.cpu(), ref8)
+    restored = package.dequantize_kv_pool_e4m3(pool8, scales)
+    assert torch.equal(restored.cpu(), oracle.dequantize_pages(ref8, ref_scales))
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 8])
+def test_fp8_attention_equals_fp16_on_dequantised_cache(package, oracle, cuda_device, split_k):
+    lengths = [0, 1, 16, 17, 100, 513, 2048]
+    q, k, v, table, lens = make_paged_inputs(lengths, seed=21, value_scale=0.5)
+    dev = cuda_device
+    k8, ks = package.quantize_kv_pool_e4m3(k.to(dev))
+    v8, vs = package.quantize_kv_pool_e4m3(v.to(dev))
+    out8 = package.grouped_splitk_decode_attention_fp8(
+        q.to(dev), k8, v8, ks, vs, table.to(dev), lens.to(dev), split_k=split_k)
+    # (a) the fp16 kernels on the dequantised cache
+    k_hat = package.dequantize_kv_pool_e4m3(k8, ks)
+    v_hat = package.dequantize_kv_pool_e4m3(v8, vs)
+    out16 = package.grouped_splitk_decode_attention(q.to(dev), k_hat, v_hat, table.to(dev), lens.to(dev),
+                                                    split_k=split_k)
+    assert_attention_close(out8, out16)
+    # (b) the CPU oracle on the dequantised cache
+    expected = oracle.paged_attention(q, oracle.dequantize_pages(k8.cpu(), ks.cpu()),
+                                      oracle.dequantize_pages(v8.cpu(), vs.cpu()), table, lens)
+    assert_attention_close(out8, expected)
+    # (c) quantisation error itself stays small against the unquantised cache
+    exact = oracle.paged_attention(q, k, v, table, lens)
+    assert (out8.cpu().float() - exact.float()).abs().max().item() < 5e-2
+
+
+def test_fp8_generic_path_and_view_as_float8(package, oracle, cuda_device):
+    """float8_e4m3fn-typed pools are accepted; the stride-generic kernel gives the same answer."""
+    q, k, v, table, lens = make_paged_inputs([33, 200], seed=2, value_scale=0.5)
+    dev = cuda_device
+    k8, ks = package.quantize_kv_pool_e4m3(k.to(dev))
+    v8, vs = package.quantize_kv_pool_e4m3(v.to(dev))
+    args = (q.to(dev), k8.view(torch.float8_e4m3fn), v8.view(torch.float8_e4m3fn), ks, vs,
+            table.to(dev), lens.to(dev))
+    fast = package.grouped_splitk_decode_attention_fp8(*args, split_k=2)
+    package.cabi.set_tuning(force_generic=True)
+    try:
+        generic = package.grouped_splitk_decode_attention_fp8(*args, split_k=2)
+    finally:
+        package.cabi.set_tuning()
+    assert_attention_close(fast, generic)
+
+
+def test_fp8_fixed_scale_write(package, oracle, cuda_device):
+    """New token rows are quantised with the page's existing scale: V bytes equal the
+    oracle's byte for byte (no rotation involved); K bytes may differ by one code
+    where the fp32 rotation lands on a rounding boundary."""
+    generator = torch.Generator().manual_seed(13)
+    batch, pages = 24, 6
+    packed = (torch.randn(batch, 2048, generator=generator) * 0.5).half()
+    positions = torch.arange(batch, dtype=torch.int32) * 97 + 5
+    slots = torch.randperm(pages * 16, generator=generator)[:batch]
+    k_scale = torch.rand(pages, 2, generator=generator) * 0.004 + 0.002
+    v_scale = torch.rand(pages, 2, generator=generator) * 0.004 + 0.002
+    k8 = torch.full((pages, 16, 2, 128), 0x11, dtype=torch.uint8)
+    v8 = torch.full((pages, 16, 2, 128), 0x22, dtype=torch.uint8)
+    dev = cuda_device
+    k8_dev, v8_dev = k8.to(dev), v8.to(dev)
+    q = package.packed_qkv_rope_cache_fp8(packed.to(dev), positions.to(dev), slots.to(dev), k8_dev, v8_dev,
+                                          k_scale.to(dev), v_scale.to(dev))
+    k_rows = oracle.rope_f32(packed[:, 1536:1792].view(batch, 2, 128), positions)
+    v_rows = packed[:, 1792:].view(batch, 2, 128).float()
+    oracle.write_fixed_scale(k_rows, slots, k8, k_scale)
+    oracle.write_fixed_scale(v_rows, slots, v8, v_scale)
+    assert torch.equal(v8_dev.cpu(), v8)
+    table = oracle.e4m3_decode_table()
+    got, want = table[k8_dev.cpu().long()], table[k8.long()]
+    mismatched = (k8_dev.cpu() != k8)
+    assert mismatched.float().mean().item() < 1e-3
+    # a differing byte is an adjacent code: at most one e4m3 step (<= 2^-3 relative)
+    assert ((got - want).abs() <= want.abs() / 8 + 2.0 ** -9)[mismatched].all()
+    q_ref = oracle.rope(packed[:, :1536].view(batch, 12, 128), positions)
+    assert oracle.ulp_distance_fp16(q.cpu(), q_ref, packed[:, :1536].view(batch, 12, 128)).max().item() <= 1.0
+
+    # decode layout entry point writes the same bytes
+    k8_b, v8_b = torch.full_like(k8_dev, 0x11), torch.full_like(v8_dev, 0x22)
+    p = packed.to(dev)[:, None, :]
+    package.native_decode_rope_kv_write_fp8(
+        p[..., :1536].view(batch, 1, 12, 128).transpose(1, 2),
+        p[..., 1536:1792].view(batch, 1, 2, 128).transpose(1, 2),
+        p[..., 1792:].view(batch, 1, 2, 128).transpose(1, 2),
+        positions.to(dev), slots.to(dev), k8_b, v8_b, k_scale.to(dev), v_scale.to(dev))
+    assert torch.equal(k8_b, k8_dev) and torch.equal(v8_b, v8_dev)

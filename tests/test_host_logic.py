@@ -1,0 +1,273 @@
+"""CPU tests of everything around the kernels: the C ABI loads and exports what the
+header declares, the ctypes structs match the C layout, wrapper validation fires
+before any device work, and the host-side integer logic (allocator, metadata,
+split policy, sharding, workloads) reproduces the reference's."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+import shutil
+import subprocess
+from unittest import mock
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_DIR, REPO_ROOT
+
+
+# ------------------------------------------------------------------- C ABI
+
+def test_library_exports_every_declared_symbol(package):
+    header = (REPO_ROOT / "include" / "qf_hotpath.h").read_text()
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(qf_\w+)\s*\(", header, flags=re.M))
+    assert declared == set(package.cabi.EXPORTED_SYMBOLS)
+    lib = package.cabi.library()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.qf_abi_version() == package.cabi.ABI_VERSION == 1
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
+def test_ctypes_structs_match_c_layout(package, tmp_path):
+    fields = {"qf_rope_kv_write_args": package.cabi.RopeKvWriteArgs,
+              "qf_decode_attention_args": package.cabi.DecodeAttentionArgs}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "qf_hotpath.h"', "int main(void) {"]
+    for struct, cls in fields.items():
+        lines.append(f'printf("{struct} %zu\\n", sizeof({struct}));')
+        for name, _ in cls._fields_:
+            lines.append(f'printf("{struct}.{name} %zu\\n", offsetof({struct}, {name}));')
+    lines.append("return 0; }")
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(REPO_ROOT / "include"), str(source), "-o", str(binary)], check=True)
+    reported = dict(line.split() for line in subprocess.run(
+        [str(binary)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for struct, cls in fields.items():
+        assert int(reported[struct]) == ctypes.sizeof(cls)
+        for name, _ in cls._fields_:
+            assert int(reported[f"{struct}.{name}"]) == getattr(cls, name).offset, (struct, name)
+
+
+def test_c_side_validation_without_a_gpu(package):
+    """Argument errors come back as a negative status and a message; nothing is launched."""
+    cabi = package.cabi
+    lib = cabi.library()
+    args = cabi.DecodeAttentionArgs()
+    args.batch, args.q_heads, args.kv_heads, args.head_dim, args.page_size = 2, 12, 5, 128, 16
+    args.split_k = 1
+    assert lib.qf_grouped_splitk_decode_attention(ctypes.byref(args), None) == -1
+    assert b"divisible" in lib.qf_last_error()
+    args.kv_heads, args.split_k = 2, 0
+    assert lib.qf_grouped_gqa_splitk_partial_out(ctypes.byref(args), None) == -1
+    assert b"split_k" in lib.qf_last_error()
+    rope = cabi.RopeKvWriteArgs()
+    rope.rows, rope.q_heads, rope.kv_heads, rope.head_dim, rope.dtype = 1, 12, 2, 100, 0
+    assert lib.qf_rope_kv_write(ctypes.byref(rope), None) == -1
+    assert b"head dimension" in lib.qf_last_error()
+    with pytest.raises(RuntimeError, match="libqf_hotpath"):
+        cabi.check(-1)
+    assert lib.qf_set_tuning(99, 0) == -1
+    assert lib.qf_set_tuning(0, 0) == 0
+
+
+def test_missing_library_fails_loudly_with_one_build_command(package):
+    cabi = package.cabi
+    native = package.kernel_module("paged_decode_native_grouped")
+    with mock.patch.object(cabi, "_library", None), \
+            mock.patch.object(cabi, "LIBRARY_PATH", REPO_ROOT / "does-not-exist.so"):
+        with pytest.raises(RuntimeError, match=r"python qwen-frence_b200/build\.py"):
+            cabi.library()
+        with pytest.raises(RuntimeError, match=r"not built; run: python qwen-frence_b200/build\.py"):
+            native._extension()
+
+
+def test_product_never_touches_the_oracle():
+    """No file of the package imports, opens or names the oracle."""
+    for path in (REPO_ROOT / "qwen-frence_b200").rglob("*"):
+        if path.suffix in (".py", ".cu", ".cuh", ".h") and "build" not in path.parts[-2:-1]:
+            assert "oracle" not in path.read_text().lower(), path
+
+
+# ------------------------------------------------- wrapper contracts (fakes)
+
+class FakeTensor:
+    """Shape/ndim/dtype only, like the reference's CPU contract tests
+    (experiments/tests/test_native_grouped_decode.py:18-24)."""
+
+    def __init__(self, shape, *, dtype="fp16", device="cuda"):
+        self.shape = tuple(shape)
+        self.ndim = len(shape)
+        self.dtype = dtype
+        self.device = device
+
+
+def _fake_inputs(group=6, head_dim=128, page_size=16):
+    return (FakeTensor((8, 2 * group, head_dim)), FakeTensor((2048, page_size, 2, head_dim)),
+            FakeTensor((2048, page_size, 2, head_dim)), FakeTensor((8, 256), dtype="int32"),
+            FakeTensor((8,), dtype="int32"))
+
+
+def test_native_wrapper_rejects_unsupported_layouts(package):
+    """experiments/tests/test_native_grouped_decode.py:43-60."""
+    fn = package.native_grouped_splitk_decode_attention
+    with pytest.raises(ValueError, match="six query heads"):
+        fn(*_fake_inputs(group=4), split_k=8)
+    with pytest.raises(ValueError, match="head_dim=128"):
+        fn(*_fake_inputs(head_dim=64), split_k=8)
+    with pytest.raises(ValueError, match="head_dim=128"):
+        fn(*_fake_inputs(page_size=32), split_k=8)
+    with pytest.raises(ValueError, match="split_k >= 2"):
+        fn(*_fake_inputs(), split_k=1)
+    with pytest.raises(ValueError, match="split_k >= 2"):
+        fn(*_fake_inputs(), split_k=2.0)
+
+
+def test_cpu_tensors_are_rejected_not_computed(package):
+    """There is no CPU path: CPU tensors are a ValueError, never a fallback."""
+    q = torch.zeros(2, 12, 128, dtype=torch.float16)
+    pool = torch.zeros(4, 16, 2, 128, dtype=torch.float16)
+    table = torch.zeros(2, 2, dtype=torch.int32)
+    lens = torch.ones(2, dtype=torch.int32)
+    with pytest.raises(ValueError, match="CUDA device"):
+        package.grouped_splitk_decode_attention(q, pool, pool, table, lens, split_k=1)
+    with pytest.raises(ValueError, match="share a device"):
+        package.native_grouped_splitk_decode_attention(q, pool, pool, table, lens, split_k=2)
+    with pytest.raises(ValueError, match="CUDA"):
+        package.packed_qkv_rope_cache(torch.zeros(2, 2048, dtype=torch.float16), lens, lens, pool, pool)
+    with pytest.raises(ValueError, match="CUDA"):
+        package.rope_kv_write(q[None].transpose(1, 2)[:, :, :, :], pool[:1, :2].transpose(1, 2)[:, :, :2],
+                              pool[:1, :2].transpose(1, 2)[:, :, :2], lens, lens, pool, pool)
+
+
+# ------------------------------------------------------ allocator + metadata
+
+def test_page_pool_replays_reference_allocator(package):
+    """Golden: the reference PagedKVCache driven through allocate / free / truncate."""
+    data = np.load(GOLDEN_DIR / "metadata_case.npz")
+    pool = package.kv_layout.PagePool(4, 64)
+    pool.allocate([5, 16, 17, 1])
+    pool.allocate([1, 1, 0, 40])
+    pool.free(1)
+    pool.allocate([0, 33, 1, 0])
+    pool.truncate(3, 20)
+    pool.allocate([1, 1, 1, 1])
+    assert pool.cur_lens == data["cur_lens"].tolist()
+    assert pool.free_pages == data["free_blocks"].tolist()
+    tables = [[int(p) for p in row if p >= 0] for row in data["tables"]]
+    assert pool.block_tables == tables
+    positions, seq_lens, table, slots = package.kv_layout.decode_step_inputs(
+        pool.cur_lens, pool.block_tables, int(data["max_blocks"]))
+    for actual, key in ((positions, "positions"), (seq_lens, "seq_lens"), (table, "block_table"),
+                        (slots, "slot_mapping")):
+        assert actual.dtype == data[key].dtype and np.array_equal(actual, data[key]), key
+
+
+def test_page_pool_is_atomic_on_exhaustion(package):
+    layout = package.kv_layout
+    pool = layout.PagePool(2, 3)
+    pool.allocate([16, 16])
+    before = (list(pool.free_pages), [list(t) for t in pool.block_tables], list(pool.cur_lens))
+    with pytest.raises(layout.CacheFullError):
+        pool.allocate([1, 17])  # needs 1 + 2 pages, 1 free
+    assert (pool.free_pages, pool.block_tables, pool.cur_lens) == before
+    with pytest.raises(ValueError, match="max_seq_len"):
+        layout.PagePool(1, 4, max_seq_len=32).allocate([33])
+    with pytest.raises(ValueError, match="cannot truncate"):
+        pool.truncate(0, 17)
+    pool.reset()
+    assert pool.free_pages == [0, 1, 2] and pool.cur_lens == [0, 0]
+
+
+def test_split_policy_matches_reference_table(package):
+    data = np.load(GOLDEN_DIR / "splitk_policy.npz")
+    for context, split_k, stages in zip(data["contexts"], data["split_k"], data["num_stages"]):
+        config = package.kv_layout.select_splitk_config(int(context))
+        assert (config["split_k"], config["num_stages"]) == (int(split_k), int(stages))
+        assert config["heads_per_program"] == 1 and config["num_warps"] == 4
+    with pytest.raises(ValueError):
+        package.kv_layout.select_splitk_config(0)
+
+
+def test_plan_split_k_uses_host_bounds_only(package):
+    plan = package.kv_layout.plan_split_k
+    assert plan(256, 8193) == 3          # enough (sequence, head) pairs already
+    assert plan(64, 4097) == 10
+    assert plan(4, 32769) == 148         # long, tiny batch: fill the machine
+    assert plan(1, 64) == 1              # never shorter than 8 pages per split
+    assert plan(8, 513) == 4
+    for batch, context in ((1, 1), (3, 100000), (1024, 16)):
+        assert 1 <= plan(batch, context) <= 65535
+
+
+def test_algorithmic_bytes(package):
+    layout = package.kv_layout
+    assert layout.kv_bytes_per_layer([4096] * 64) == 64 * 2 * 4096 * 128 * 2 * 2  # reference's unique_bytes
+    one = layout.algorithmic_bytes_per_layer([17], split_k=1)
+    assert one == 17 * 1024 + 2 * 4 + 2 * 3072 + (4096 + 3072 + 1024 + 12)
+    assert layout.algorithmic_bytes_per_layer([17], split_k=2) - one == 2 * 2 * 12 * 130 * 4
+    assert layout.algorithmic_bytes_per_layer([32], split_k=1, fp8=True) == \
+        32 * 512 + 2 * 4 + 2 * 16 + 2 * 3072 + (4096 + 3072 + 512 + 12)
+
+
+# ----------------------------------------------------------------- workloads
+
+def test_workloads_have_the_configured_shapes(package):
+    build = package.workloads.build_workload
+    w = build("cpu_single_layer_b8")
+    assert (w.layers, w.batch, w.num_pages, w.block_table.shape) == (1, 8, 512, (8, 33))
+    assert w.seq_lens.tolist() == [513] * 8 and w.positions.tolist() == [512] * 8
+    pages = w.block_table.flatten().tolist()
+    assert len(set(pages)) == len(pages) and pages != sorted(pages)  # permuted, disjoint
+    rows = torch.arange(8)
+    expected_slots = w.block_table[rows, 32].long() * 16 + 0
+    assert torch.equal(w.slot_mapping, expected_slots)
+
+    w = build("decode_b64")
+    assert w.layers == 28 and w.batch == 64
+    assert 128 <= min(w.contexts) and max(w.contexts) <= 4096
+    w2 = build("decode_b64")
+    assert w2.contexts == w.contexts and torch.equal(w2.block_table, w.block_table)  # seeded
+    assert build("decode_b64", rank=1, world_size=2).contexts != w.contexts          # weak: own batch
+
+    w = build("long_skew_b4")
+    assert sorted(w.contexts) == [512, 4096, 16384, 32768] and w.block_table.shape[1] == 2049
+    w = build("fp8_b128", layers=2)
+    assert w.fp8 and w.batch == 128 and set(w.contexts) == {2048}
+
+
+def test_strong_scaling_shards_cover_the_batch_once(package):
+    build = package.workloads.build_workload
+    everyone = package.workloads.context_lengths("sweep_b256")
+    assert len(everyone) == 256 and 64 <= min(everyone) and max(everyone) <= 8192
+    seen = []
+    loads = []
+    for rank in range(8):
+        w = build("sweep_b256", rank=rank, world_size=8, scaling="strong", layers=1)
+        assert w.num_pages == 131072 // 8
+        assert [everyone[i] for i in w.global_indices] == w.contexts
+        used = int((w.block_table > 0).sum()) + 1
+        assert used <= w.num_pages and w.meta["filler_pages"] > 0
+        seen += w.global_indices
+        loads.append(sum(w.contexts))
+    assert sorted(seen) == list(range(256))
+    assert max(loads) / (sum(loads) / 8) < 1.02  # snake dealing balances the ranks
+
+
+def test_partition_policies(package):
+    sharding = package.sharding
+    lengths = [100, 5, 80, 7, 60, 9, 40, 11]
+    snake = sharding.partition_sequences(lengths, 2)
+    assert sorted(snake[0] + snake[1]) == list(range(8))
+    assert snake[0] == [0, 6, 7, 1] and snake[1] == [2, 4, 5, 3]
+    assert sharding.imbalance(lengths, snake) < sharding.imbalance(
+        lengths, sharding.partition_sequences(lengths, 2, "block")) + 1e-9
+    block = sharding.partition_sequences(lengths, 3, "block")
+    assert block == [[0, 1, 2], [3, 4, 5], [6, 7]]
+    assert sharding.partition_sequences([], 4) == [[], [], [], []]
+    assert sharding.shard_pages([17, 16, 1], [[0, 1], [2]]) == [3, 1]
+    with pytest.raises(ValueError):
+        sharding.partition_sequences(lengths, 0)
