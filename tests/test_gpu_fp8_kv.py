@@ -46,9 +46,11 @@ def test_fp8_attention_equals_fp16_on_dequantised_cache(package, oracle, cuda_de
     expected = oracle.paged_attention(q, oracle.dequantize_pages(k8.cpu(), ks.cpu()),
                                       oracle.dequantize_pages(v8.cpu(), vs.cpu()), table, lens)
     assert_attention_close(out8, expected)
-    # (c) quantisation error itself stays small against the unquantised cache
+    # (c) quantisation error itself stays small against the unquantised cache: e4m3
+    # keeps three mantissa bits, so a single value is off by at most 1/16 of itself
+    # (a one-token sequence returns V itself); values here stay below 2.5
     exact = oracle.paged_attention(q, k, v, table, lens)
-    assert (out8.cpu().float() - exact.float()).abs().max().item() < 5e-2
+    assert (out8.cpu().float() - exact.float()).abs().max().item() <= 2.5 / 16
 
 
 def test_fp8_generic_path_and_view_as_float8(package, oracle, cuda_device):
