@@ -70,10 +70,11 @@ def test_fast_and_generic_kernels_agree(package, oracle, cuda_device):
     assert_attention_close(generic, expected)
 
 
-@pytest.mark.parametrize("stages", [2, 3, 4, 12])
+@pytest.mark.parametrize("stages", [1, 3, 4, 12])
 def test_pipeline_depths(package, oracle, cuda_device, stages):
-    """Ring depths from the minimum to the maximum give the same answer; partitions
-    longer than 32 pages cross the page-id batch boundary."""
+    """Ring depths from the minimum (requests below three are raised to three) to the
+    maximum give the same answer; partitions longer than 32 pages cross the page-id
+    batch boundary."""
     lengths = [16 * 70 + 5, 16 * 33, 16 * 32, 40]
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=8)
     expected = oracle.paged_attention(*host)
