@@ -48,6 +48,10 @@ UNIT = "tokens/s"
 LAYERS = 28
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the
+# ncu capture summarised in profiles/ (same per-launch workload as a full-size launch: one
+# layer of the named workload at seed 0).  Workloads without a capture report null.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {("decode_b64", 0): 137.93e6 + 5.79e6}
 
 
 def parse_args():
@@ -349,7 +353,9 @@ def main():
         roofline = {
             "bound": "hbm", "kernel": "decode_partial_tma_kernel", "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-            "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": None,
+            "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed))
+            if world == 1 and step.split_k == 10 else None,  # the captured launch used split_k 10
             "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,
             "kv_bytes_per_launch": package.kv_layout.kv_bytes_per_layer(
                 workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2),
