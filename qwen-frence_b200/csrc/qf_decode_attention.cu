@@ -1,33 +1,8 @@
 // GQA paged decode attention over block tables: split-K partial pass, combine,
 // and the host entry points.
 //
-// Fast partial kernel (sm_100a), geometry D=128, page=16, 6 query heads per KV
-// head (baseline/naive_forward.py:17-26):
-//
-//   * one CTA per (sequence, KV head, split): the six query heads of the GQA
-//     group share every K/V page load
-//     (same work split as native_grouped_decode.cu:62-67);
-//   * pages stream through a ring of shared memory stages guarded by
-//     full/empty mbarriers, filled by 4-D tiled TMA loads ([pages,16,kv,128]
-//     tensor map, box [1,16,1,128]) that lane 0 of warp 0 issues `stages - 2`
-//     pages ahead of the math; page ids are fetched 32 at a time, one batch
-//     ahead.  The CTA is exactly eight warps (no extra producer warp), which
-//     keeps two CTAs of 128 registers per thread resident per SM;
-//   * all 256 threads consume: thread (t, c) owns token slot t (0..15) of every
-//     page and the 8 head dimensions [8c, 8c+8).  It reads its 16 bytes of K and
-//     V from shared memory once and reuses them from registers for all six
-//     heads (packed fp32x2 FMAs), so shared memory is read exactly once per
-//     element, not once per head;
-//   * the six per-thread partial dot products are reduce-scattered across the
-//     16 lanes of a token with 7 shuffles; each lane then owns one head's score,
-//     keeps that head's running (offset, sum) for its token slot, and the
-//     probabilities are gathered back with 6 shuffles.  The running offset only
-//     moves when a score exceeds it by more than 2^8, so the accumulator
-//     rescale is off the common path;
-//   * the 16 token slots are merged once per CTA, through shared memory.
-//
-// No tensor-core MMA: with M=6 the op is a bandwidth-bound GEMV.  No load in
-// this file names a cluster-multicast qualifier.
+// The fast partial kernel (sm_100a, TMA ring, Qwen geometry) lives in
+// qf_decode_partial.cuh.
 //
 // A stride-generic kernel covers every other layout and geometry the
 // reference accepts (custom_kernels/paged_decode_grouped_splitk.py:228-334):
@@ -37,433 +12,13 @@
 #include <unordered_map>
 
 #include "qf_common.cuh"
+#include "qf_decode_partial.cuh"
 
 namespace qf {
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kFastThreads = kConsumerThreads;  // warp 0 also issues the TMA loads
-constexpr int kMaxStages = 12;
-constexpr int kDefaultStagesF16 = 6;
-constexpr int kDefaultStagesFp8 = 8;
-constexpr int kMergeFloats = kConsumerWarps * QF_GQA_GROUP * QF_HEAD_DIM;  // 24 KB
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-// The exponent offset follows the running maximum only when a score exceeds it
-// by more than this many powers of two; probabilities stay below 2^kOffsetSlack.
-constexpr float kOffsetSlack = 8.f;
-
 int g_tuned_stages = 0;
 int g_force_generic = 0;
-
-struct FastParams {
-  const void* q;
-  int64_t q_sb, q_sh;
-  const void* block_table;
-  int64_t bt_sb, bt_sp;
-  const void* seq_lens;
-  int64_t lens_stride;
-  const float* k_scale;
-  const float* v_scale;
-  float* partial_out;
-  float* partial_max;
-  float* partial_sum;
-  void* out;
-  int64_t o_sb, o_sh, o_sd;
-  int64_t num_pages;
-  long long* cycles;
-  int* status;
-  int table_dtype, lens_dtype;
-  int batch, q_heads, kv_heads, split_k, stages;
-  float scale_log2;  // softmax scale * log2(e)
-};
-
-// ---------------------------------------------------------------------------
-// Consumer-side state of one thread: token slot t = tid/16, dims [8c, 8c+8).
-// ---------------------------------------------------------------------------
-struct SlotState {
-  float2 acc[QF_GQA_GROUP][4];  // un-normalised sum of p*V for the 8 dims
-  float offset;                 // exponent offset of the head this lane owns (log2 units)
-  float sum;                    // sum of p for that head
-};
-
-// Reduce six per-thread partial dots over the 16 lanes of a token slot so that
-// each lane ends with the full dot product of ONE head:
-//   lanes 0,1 -> head 0   lanes 4,5 -> head 1   lanes 2,3,6,7 -> head 2
-//   lanes 8,9 -> head 3   lanes 12,13 -> head 4  lanes 10,11,14,15 -> head 5
-__device__ __forceinline__ float reduce_scatter6(const float (&v)[QF_GQA_GROUP], int sub) {
-  constexpr unsigned kFull = 0xffffffffu;
-  const bool b3 = sub & 8, b2 = sub & 4, b1 = sub & 2;
-  float k0 = b3 ? v[3] : v[0], s0 = b3 ? v[0] : v[3];
-  float k1 = b3 ? v[4] : v[1], s1 = b3 ? v[1] : v[4];
-  float k2 = b3 ? v[5] : v[2], s2 = b3 ? v[2] : v[5];
-  k0 += __shfl_xor_sync(kFull, s0, 8);
-  k1 += __shfl_xor_sync(kFull, s1, 8);
-  k2 += __shfl_xor_sync(kFull, s2, 8);
-  float a = b2 ? k1 : k0, sa = b2 ? k0 : k1;
-  a += __shfl_xor_sync(kFull, sa, 4);
-  const float c = k2 + __shfl_xor_sync(kFull, k2, 4);
-  float x = b1 ? c : a, sx = b1 ? a : c;
-  x += __shfl_xor_sync(kFull, sx, 2);
-  x += __shfl_xor_sync(kFull, x, 1);
-  return x;
-}
-
-// Index (within a KV group) of the head a lane owns after reduce_scatter6.
-__device__ __forceinline__ int owned_head(int sub) {
-  const int b3 = (sub >> 3) & 1, b2 = (sub >> 2) & 1, b1 = (sub >> 1) & 1;
-  return b1 ? 3 * b3 + 2 : 3 * b3 + b2;
-}
-
-// Lane (within the 16-lane token group) that holds head h after reduce_scatter6.
-__device__ __forceinline__ constexpr int source_lane(int h) {
-  return h == 0 ? 0 : h == 1 ? 4 : h == 2 ? 2 : h == 3 ? 8 : h == 4 ? 12 : 10;
-}
-
-// One page for one thread.  kreg/vreg: this thread's 8 K and 8 V elements
-// already converted to fp32 pairs.  `valid`: the thread's token is < seq_len.
-// k_mul/v_mul: per-page FP8 dequantisation scales (1 for 16-bit pools).
-template <bool TAIL>
-__device__ __forceinline__ void consume_page(SlotState& st, const float2 (&q2)[QF_GQA_GROUP][4],
-                                             const float2 (&kreg)[4], const float2 (&vreg)[4],
-                                             bool valid, float k_mul, float v_mul, int sub) {
-  constexpr unsigned kFull = 0xffffffffu;
-  float dots[QF_GQA_GROUP];
-#pragma unroll
-  for (int h = 0; h < QF_GQA_GROUP; ++h) {
-    float2 d = __fmul2_rn(q2[h][0], kreg[0]);
-#pragma unroll
-    for (int j = 1; j < 4; ++j) d = __ffma2_rn(q2[h][j], kreg[j], d);
-    dots[h] = d.x + d.y;
-  }
-  float score = reduce_scatter6(dots, sub) * k_mul;
-  if (TAIL && !valid) score = -INFINITY;
-
-  // Move the offset only when the score outgrows it (or on the first page).
-  const bool grow = score > st.offset + kOffsetSlack;
-  if (__any_sync(kFull, grow)) {
-    float corr = 1.f;
-    if (grow) {
-      corr = st.offset == -INFINITY ? 0.f : fast_exp2(st.offset - score);
-      st.offset = score;
-      st.sum *= corr;
-    }
-#pragma unroll
-    for (int h = 0; h < QF_GQA_GROUP; ++h) {
-      const float ch = __shfl_sync(kFull, corr, source_lane(h), 16);
-      const float2 c2 = make_float2(ch, ch);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) st.acc[h][j] = __fmul2_rn(st.acc[h][j], c2);
-    }
-  }
-  float p = fast_exp2(score - st.offset);
-  if (TAIL && !valid) p = 0.f;  // also covers offset == -inf (NaN from inf - inf)
-  st.sum += p;
-  p *= v_mul;
-
-  float ph[QF_GQA_GROUP];
-#pragma unroll
-  for (int h = 0; h < QF_GQA_GROUP; ++h) ph[h] = __shfl_sync(kFull, p, source_lane(h), 16);
-  if (!TAIL || valid) {
-#pragma unroll
-    for (int h = 0; h < QF_GQA_GROUP; ++h) {
-      const float2 p2 = make_float2(ph[h], ph[h]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) st.acc[h][j] = __ffma2_rn(p2, vreg[j], st.acc[h][j]);
-    }
-  }
-}
-
-template <typename T, bool FP8>
-struct TileTraits {
-  static constexpr int kTileBytes = FP8 ? QF_PAGE_SIZE * QF_HEAD_DIM : QF_PAGE_SIZE * QF_HEAD_DIM * 2;
-  static constexpr int kStageBytes = 2 * kTileBytes;  // K tile + V tile
-};
-
-// Loads this thread's 8 elements of a tile and converts them to fp32 pairs.
-template <typename T, bool FP8>
-__device__ __forceinline__ void load_tile_regs(const unsigned char* tile, int tid, float2 (&r)[4]) {
-  if constexpr (FP8) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(tile + tid * 8);
-    r[0] = e4m3x2_to_float2(static_cast<uint16_t>(raw.x & 0xffffu));
-    r[1] = e4m3x2_to_float2(static_cast<uint16_t>(raw.x >> 16));
-    r[2] = e4m3x2_to_float2(static_cast<uint16_t>(raw.y & 0xffffu));
-    r[3] = e4m3x2_to_float2(static_cast<uint16_t>(raw.y >> 16));
-  } else {
-    const uint4 raw = *reinterpret_cast<const uint4*>(tile + tid * 16);
-    r[0] = unpack2<T>(raw.x);
-    r[1] = unpack2<T>(raw.y);
-    r[2] = unpack2<T>(raw.z);
-    r[3] = unpack2<T>(raw.w);
-  }
-}
-
-template <typename T, bool FP8, bool PROFILE>
-__global__ void __launch_bounds__(kFastThreads, 2)
-    decode_partial_tma_kernel(const __grid_constant__ CUtensorMap k_map,
-                              const __grid_constant__ CUtensorMap v_map, const FastParams p) {
-  using Traits = TileTraits<T, FP8>;
-  extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ uint64_t full_bar[kMaxStages];
-  __shared__ uint64_t empty_bar[kMaxStages];
-  __shared__ float stage_scale[kMaxStages][2];
-  __shared__ int batch_ids[32];
-  __shared__ float batch_scale[32][2];
-  __shared__ float slot_offset[QF_PAGE_SIZE][QF_GQA_GROUP];
-  __shared__ float slot_sum[QF_PAGE_SIZE][QF_GQA_GROUP];
-  __shared__ float cta_offset[QF_GQA_GROUP];
-  __shared__ float cta_sum[QF_GQA_GROUP];
-
-  constexpr unsigned kFull = 0xffffffffu;
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5;
-  const int lane = tid & 31;
-  const int token = tid >> 4;  // token slot in every page
-  const int sub = tid & 15;    // dim chunk / lane in the token group
-  const int stages = p.stages;
-  const int lookahead = stages > 2 ? stages - 2 : 1;  // pages in flight ahead of the consumers
-
-  // blockIdx.x = (sequence * kv_heads + kv_head) * split_k + split
-  const int split = blockIdx.x % p.split_k;
-  const int kv_head = (blockIdx.x / p.split_k) % p.kv_heads;
-  const int sequence = blockIdx.x / (p.split_k * p.kv_heads);
-
-  int seq_len;
-  {
-    int64_t raw = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
-    raw = raw < 0 ? 0 : raw;
-    seq_len = static_cast<int>(raw > 0x7ffffff0 ? 0x7ffffff0 : raw);
-  }
-  const int total_pages = (seq_len + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE;
-  const int start_page = static_cast<int>(static_cast<int64_t>(split) * total_pages / p.split_k);
-  const int end_page = static_cast<int>((static_cast<int64_t>(split) + 1) * total_pages / p.split_k);
-  const int num_iters = end_page - start_page;
-  // Iterations before `full_iters` read complete pages; at most one partial page follows.
-  const int full_end = min(end_page, seq_len / QF_PAGE_SIZE);
-  const int full_iters = max(full_end - start_page, 0);
-
-  if (tid == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kConsumerWarps);
-    }
-    fence_barrier_init();
-    if (num_iters > 0) {
-      tma_prefetch_descriptor(&k_map);
-      tma_prefetch_descriptor(&v_map);
-    }
-  }
-  __syncthreads();
-
-  // ---- producer role (warp 0 only; every lane runs it, lane 0 issues) ----
-  // Page ids (and FP8 scales) are fetched 32 at a time into registers, one batch
-  // ahead, and parked in shared memory when their batch becomes current.
-  const int num_pages = static_cast<int>(p.num_pages);
-  int ids_next = -1;
-  int issued = 0;  // iterations whose loads have been issued (meaningful in warp 0)
-  float ks_next = 1.f, vs_next = 1.f;
-  auto fetch_batch = [&](int first_iter) {
-    const int idx = start_page + first_iter + lane;
-    ids_next = -1;
-    if (idx < end_page) {
-      const int64_t raw = load_index(p.block_table, p.table_dtype,
-                                     sequence * p.bt_sb + static_cast<int64_t>(idx) * p.bt_sp);
-      ids_next = raw >= 0 && raw < num_pages ? static_cast<int>(raw) : -1;  // -1: outside the pool
-    }
-    if (FP8) {
-      ks_next = ids_next >= 0 ? p.k_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
-      vs_next = ids_next >= 0 ? p.v_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
-    }
-  };
-  // Issues the loads of iteration `index` into stage `pstage` (free once its
-  // empty barrier completes phase `pparity`).  False when that wait ran out.
-  auto produce = [&](int index, int pstage, uint32_t pparity) -> bool {
-    if ((index & 31) == 0) {
-      if (index == 0) fetch_batch(0);
-      __syncwarp();
-      batch_ids[lane] = ids_next;
-      if (FP8) batch_scale[lane][0] = ks_next, batch_scale[lane][1] = vs_next;
-      __syncwarp();
-      if (index + 32 < num_iters) fetch_batch(index + 32);
-    }
-    int ok = 1;
-    if (lane == 0) {
-      if (!mbar_wait_bounded(&empty_bar[pstage], pparity)) {
-        atomicExch(p.status, kStatusWaitTimeout);
-        ok = 0;
-      } else {
-        const int page_id = batch_ids[index & 31];
-        if (page_id < 0) atomicExch(p.status, kStatusBadPageId);
-        if (FP8) {
-          stage_scale[pstage][0] = batch_scale[index & 31][0];
-          stage_scale[pstage][1] = batch_scale[index & 31][1];
-        }
-        unsigned char* dst = smem + pstage * Traits::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[pstage], Traits::kStageBytes);
-        // A page id outside the pool reads as zeros (TMA out-of-bounds fill).
-        tma_load_4d(dst, &k_map, &full_bar[pstage], 0, kv_head, 0, page_id);
-        tma_load_4d(dst + Traits::kTileBytes, &v_map, &full_bar[pstage], 0, kv_head, 0, page_id);
-        issued = index + 1;
-      }
-    }
-    return __shfl_sync(kFull, ok, 0) != 0;
-  };
-
-  SlotState st;
-#pragma unroll
-  for (int h = 0; h < QF_GQA_GROUP; ++h)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) st.acc[h][j] = make_float2(0.f, 0.f);
-  st.offset = -INFINITY;
-  st.sum = 0.f;
-
-  bool aborted = false;
-  if (warp == 0) {
-    // The first `lookahead` stages are free: their empty barriers start out in
-    // the phase that a wait on parity 1 passes.
-    for (int i = 0; i < lookahead && i < num_iters && !aborted; ++i) aborted = !produce(i, i, 1u);
-  }
-
-  float2 q2[QF_GQA_GROUP][4];
-  if (num_iters > 0) {
-    const T* qbase = static_cast<const T*>(p.q) + sequence * p.q_sb +
-                     static_cast<int64_t>(kv_head) * QF_GQA_GROUP * p.q_sh + sub * 8;
-    const float2 s2 = make_float2(p.scale_log2, p.scale_log2);
-#pragma unroll
-    for (int h = 0; h < QF_GQA_GROUP; ++h) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(qbase + h * p.q_sh);
-      q2[h][0] = __fmul2_rn(unpack2<T>(raw.x), s2);
-      q2[h][1] = __fmul2_rn(unpack2<T>(raw.y), s2);
-      q2[h][2] = __fmul2_rn(unpack2<T>(raw.z), s2);
-      q2[h][3] = __fmul2_rn(unpack2<T>(raw.w), s2);
-    }
-  }
-
-  // ------------------------------ main loop -------------------------------
-  long long t_wait = 0, t_math = 0, t_mark = 0;
-  int stage = 0;
-  uint32_t phase = 0;
-  for (int it = 0; it < num_iters && !aborted; ++it) {
-    if (warp == 0 && it + lookahead < num_iters) {
-      // Iteration it+lookahead lands `lookahead` stages ahead of this one.
-      int pstage = stage + lookahead;
-      uint32_t pparity = phase ^ 1u;
-      if (pstage >= stages) pstage -= stages, pparity ^= 1u;
-      if (!produce(it + lookahead, pstage, pparity)) {
-        aborted = true;
-        break;
-      }
-    }
-    if (PROFILE) t_mark = clock64();
-    const bool arrived = mbar_wait_bounded(&full_bar[stage], phase);
-    if (!__all_sync(kFull, arrived)) {
-      if (lane == 0) atomicExch(p.status, kStatusWaitTimeout);
-      aborted = true;
-      break;
-    }
-    if (PROFILE) t_wait += clock64() - t_mark, t_mark = clock64();
-    const unsigned char* tile = smem + stage * Traits::kStageBytes;
-    float2 kreg[4], vreg[4];
-    load_tile_regs<T, FP8>(tile, tid, kreg);
-    load_tile_regs<T, FP8>(tile + Traits::kTileBytes, tid, vreg);
-    float k_mul = 1.f, v_mul = 1.f;
-    if (FP8) k_mul = stage_scale[stage][0], v_mul = stage_scale[stage][1];
-    // The stage is in registers: hand it back to the producer.
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[stage]);
-    if (++stage == stages) stage = 0, phase ^= 1u;
-
-    if (it < full_iters) {
-      consume_page<false>(st, q2, kreg, vreg, true, k_mul, v_mul, sub);
-    } else {
-      const bool valid = (start_page + it) * QF_PAGE_SIZE + token < seq_len;
-      consume_page<true>(st, q2, kreg, vreg, valid, k_mul, v_mul, sub);
-    }
-    if (PROFILE) t_math += clock64() - t_mark;
-  }
-  if (PROFILE && p.cycles != nullptr && tid == 32) {
-    // One pure-consumer warp per CTA reports: {waiting for pages, QK + softmax + PV, 0, 0}.
-    long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;
-    dst[0] = t_wait, dst[1] = t_math, dst[2] = 0, dst[3] = 0;
-  }
-  // Barrier: every stage has been read, so the ring is free for the merge.
-  if (__syncthreads_or(aborted)) {
-    // A wait ran out somewhere in this CTA.  Give the loads already issued a
-    // bounded chance to land before their shared memory is reused or released.
-    if (tid == 0) {
-      for (int s = 0; s < stages && s < issued; ++s) {
-        const int last = ((issued - 1 - s) / stages) * stages + s;  // last iteration on stage s
-        mbar_wait_bounded(&full_bar[s], static_cast<uint32_t>(last / stages) & 1u);
-      }
-    }
-    __syncthreads();
-  }
-  float* merge = reinterpret_cast<float*>(smem);  // [8 warps][6 heads][128]
-  {
-    const int h = owned_head(sub);
-    if (sub == source_lane(h)) {
-      slot_offset[token][h] = st.offset;
-      slot_sum[token][h] = st.sum;
-    }
-  }
-  __syncthreads();
-  if (tid < QF_GQA_GROUP) {
-    float m = -INFINITY;
-    for (int g = 0; g < QF_PAGE_SIZE; ++g) m = fmaxf(m, slot_offset[g][tid]);
-    float total = 0.f;
-    for (int g = 0; g < QF_PAGE_SIZE; ++g) {
-      const float mg = slot_offset[g][tid];
-      if (mg != -INFINITY) total += slot_sum[g][tid] * fast_exp2(mg - m);
-    }
-    cta_offset[tid] = m;
-    cta_sum[tid] = total;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < QF_GQA_GROUP; ++h) {
-    const float mg = slot_offset[token][h];
-    const float f = mg == -INFINITY ? 0.f : fast_exp2(mg - cta_offset[h]);
-    const float2 f2 = make_float2(f, f);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 a = __fmul2_rn(st.acc[h][j], f2);
-      a.x += __shfl_xor_sync(kFull, a.x, 16);
-      a.y += __shfl_xor_sync(kFull, a.y, 16);
-      st.acc[h][j] = a;
-    }
-    if (lane < 16) {
-      float4* dst =
-          reinterpret_cast<float4*>(merge + (warp * QF_GQA_GROUP + h) * QF_HEAD_DIM + sub * 8);
-      dst[0] = make_float4(st.acc[h][0].x, st.acc[h][0].y, st.acc[h][1].x, st.acc[h][1].y);
-      dst[1] = make_float4(st.acc[h][2].x, st.acc[h][2].y, st.acc[h][3].x, st.acc[h][3].y);
-    }
-  }
-  __syncthreads();
-  const int64_t head0 = static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
-  const int64_t partial_row =
-      (static_cast<int64_t>(sequence) * p.split_k + split) * p.q_heads + head0;
-#pragma unroll
-  for (int i = 0; i < (QF_GQA_GROUP * QF_HEAD_DIM) / kConsumerThreads; ++i) {
-    const int e = tid + i * kConsumerThreads;  // (head, dim) flattened
-    float value = 0.f;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) value += merge[w * QF_GQA_GROUP * QF_HEAD_DIM + e];
-    const int h = e >> 7, d = e & 127;
-    if (p.partial_out != nullptr) p.partial_out[partial_row * QF_HEAD_DIM + e] = value;
-    if (p.out != nullptr) {
-      const float total = cta_sum[h];
-      const float norm = value / (total > 0.f ? total : 1.f);
-      static_cast<T*>(p.out)[sequence * p.o_sb + (head0 + h) * p.o_sh + d * p.o_sd] =
-          from_float<T>(norm);
-    }
-  }
-  if (tid < QF_GQA_GROUP && p.partial_max != nullptr) {
-    // natural-log units, as the combine and the reference's reduce expect
-    p.partial_max[partial_row + tid] = cta_offset[tid] * kLn2;
-    p.partial_sum[partial_row + tid] = cta_sum[tid];
-  }
-}
 
 // ---------------------------------------------------------------------------
 // Stride-generic partial kernel: any strides, page size, head dim <= 256 and
@@ -756,7 +311,7 @@ int* status_word_for_current_device() {
 
 int stages_for(bool fp8) {
   int stages = g_tuned_stages > 0 ? g_tuned_stages : (fp8 ? kDefaultStagesFp8 : kDefaultStagesF16);
-  if (stages < 2) stages = 2;
+  if (stages < kMinStages) stages = kMinStages;  // two pages in use + one being filled
   if (stages > kMaxStages) stages = kMaxStages;
   return stages;
 }
