@@ -6,8 +6,8 @@
  *
  * Conventions
  *   - Every pointer marked "device" is a CUDA device pointer owned by the
- *     caller.  The library allocates no device memory, ever.  It keeps one
- *     host-side cache of TMA tensor maps keyed by pool address and geometry.
+ *     caller.  The library allocates no device memory, ever, and keeps no
+ *     per-pool state.
  *   - `stream` is a cudaStream_t passed as void*.  Every call only enqueues
  *     work on that stream: no host synchronisation, no device->host read, so
  *     every call may be recorded into a CUDA graph.
@@ -216,15 +216,17 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
                                       int64_t* cycles, void* stream);
 
-/* Device-side status word of the fast kernels on the current device: 0, or a
- * code recorded by a kernel whose bounded wait ran out or that met a page id
- * outside the pool.  Synchronises the device; for tests and debugging only.
- * `reset` != 0 clears it after reading. */
+/* Device-side status word of the kernels on the current device: 0, or 2 when a
+ * kernel met a page id outside the pool (such a page is never dereferenced; it
+ * reads as zeros).  The kernels contain no spin wait.  Synchronises the device;
+ * for tests and debugging only.  `reset` != 0 clears it after reading. */
 int qf_device_status(int32_t* status, int32_t reset);
 
 /* Choice of pipeline depth / forcing the generic path, for experiments.
- * stages == 0 restores the default.  force_generic != 0 routes every
- * attention call through the stride-generic kernel. */
+ * `stages` is the number of pages resident in the fast kernel's shared-memory
+ * ring (rounded to whole page pairs, clamped to 4..10); 0 restores the default
+ * of 8.  force_generic != 0 routes every attention call through the
+ * stride-generic kernel. */
 int qf_set_tuning(int32_t stages, int32_t force_generic);
 
 #ifdef __cplusplus

@@ -189,7 +189,7 @@ class device_of:
 
 
 def device_status(reset=True):
-    """Status word written by kernels whose bounded wait ran out (0 = clean)."""
+    """Status word of the kernels on the current device (0 = clean, 2 = bad page id)."""
     value = c_int32(0)
     check(library().qf_device_status(ctypes.byref(value), 1 if reset else 0))
     return value.value

@@ -1,5 +1,5 @@
 // Library-wide plumbing of libqf_hotpath.so: ABI version, per-thread error
-// text, the per-device status word kernels write when a bounded wait runs out,
+// text, the per-device status word kernels write when they meet a bad page id,
 // and the tuning switches.
 #include <cstdarg>
 #include <cstdio>

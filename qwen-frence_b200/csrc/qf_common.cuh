@@ -1,9 +1,7 @@
 // Shared helpers for the libqf_hotpath.so translation units: error reporting,
-// element-type conversion, metadata loads and the sm_100a PTX wrappers
-// (mbarrier, TMA tiled loads) the kernels use.
+// element-type conversion and metadata loads.
 #pragma once
 
-#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -32,8 +30,7 @@ int cuda_fail(cudaError_t err, const char* what);
 // Address of the per-device status word (file-scope __device__ int).
 int* device_status_word();
 
-// Status codes kernels may record.
-constexpr int kStatusWaitTimeout = 1;
+// Status codes kernels may record (1 is reserved).
 constexpr int kStatusBadPageId = 2;
 
 // ---- device side ---------------------------------------------------------
@@ -100,63 +97,6 @@ __device__ __forceinline__ float load_position(const void* base, int dtype, int6
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-// Makes the initialised barriers visible to the async (TMA) proxy.
-__device__ __forceinline__ void fence_barrier_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
-// Upper bound on any wait inside a kernel, in SM clock cycles (about two
-// seconds).  A wait that runs out records kStatusWaitTimeout and gives up.
-constexpr long long kWaitCycleLimit = 4000000000LL;
-
-// Returns false when the wait ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > kWaitCycleLimit) return false;
-  }
-  return true;
-}
-
-// 4-D tiled TMA load of one box into this CTA's shared memory; completion is
-// counted in bytes on `bar`.  Coordinates are innermost first.  The innermost
-// coordinate is always 0 here, which satisfies the 16-byte start rule.
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
-                                            int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(smem_u32(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

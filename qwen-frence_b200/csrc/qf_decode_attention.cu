@@ -1,7 +1,7 @@
 // GQA paged decode attention over block tables: split-K partial pass, combine,
 // and the host entry points.
 //
-// The fast partial kernel (sm_100a, TMA ring, Qwen geometry) lives in
+// The fast partial kernel (sm_100a, cp.async ring, Qwen geometry) lives in
 // qf_decode_partial.cuh.
 //
 // A stride-generic kernel covers every other layout and geometry the
@@ -9,7 +9,6 @@
 // arbitrary strides, other page sizes, head dims and group sizes.
 #include <cmath>
 #include <mutex>
-#include <unordered_map>
 
 #include "qf_common.cuh"
 #include "qf_decode_partial.cuh"
@@ -215,90 +214,6 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
-            cudaSuccess ||
-        result != cudaDriverEntryPointSuccess) {
-      return static_cast<EncodeTiledFn>(nullptr);
-    }
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
-struct MapKey {
-  const void* base;
-  int64_t pages, s_page, s_tok, s_head;
-  int kv_heads, elem_code;  // 0 f16, 1 bf16, 2 e4m3 bytes
-  bool operator==(const MapKey& o) const {
-    return base == o.base && pages == o.pages && s_page == o.s_page && s_tok == o.s_tok &&
-           s_head == o.s_head && kv_heads == o.kv_heads && elem_code == o.elem_code;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = reinterpret_cast<size_t>(k.base);
-    auto mix = [&h](size_t v) { h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
-    mix(static_cast<size_t>(k.pages));
-    mix(static_cast<size_t>(k.s_page));
-    mix(static_cast<size_t>(k.s_tok));
-    mix(static_cast<size_t>(k.s_head));
-    mix(static_cast<size_t>(k.kv_heads * 4 + k.elem_code));
-    return h;
-  }
-};
-
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-
-// Tensor map over a pool [pages, 16, kv_heads, 128] with a box of one page of
-// one KV head: [1, 16, 1, 128].  Host-side only; cached by address and layout.
-int pool_tensor_map(const void* base, int elem_code, int64_t pages, int kv_heads, int64_t s_page,
-                    int64_t s_tok, int64_t s_head, CUtensorMap* out) {
-  const MapKey key{base, pages, s_page, s_tok, s_head, kv_heads, elem_code};
-  {
-    std::lock_guard<std::mutex> lock(g_map_mutex);
-    auto it = g_maps.find(key);
-    if (it != g_maps.end()) {
-      *out = it->second;
-      return QF_OK;
-    }
-  }
-  EncodeTiledFn encode = encode_tiled();
-  if (encode == nullptr) return fail(QF_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const int elem_bytes = elem_code == 2 ? 1 : 2;
-  const CUtensorMapDataType type = elem_code == 0   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                   : elem_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                    : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  const cuuint64_t dims[4] = {QF_HEAD_DIM, static_cast<cuuint64_t>(kv_heads), QF_PAGE_SIZE,
-                              static_cast<cuuint64_t>(pages)};
-  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s_head) * elem_bytes,
-                                 static_cast<cuuint64_t>(s_tok) * elem_bytes,
-                                 static_cast<cuuint64_t>(s_page) * elem_bytes};
-  const cuuint32_t box[4] = {QF_HEAD_DIM, 1, QF_PAGE_SIZE, 1};
-  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
-  CUtensorMap map;
-  const CUresult rc = encode(&map, type, 4, const_cast<void*>(base), dims, strides, box,
-                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return fail(QF_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(rc));
-  {
-    std::lock_guard<std::mutex> lock(g_map_mutex);
-    if (g_maps.size() > 4096) g_maps.clear();  // pools were reallocated many times
-    g_maps.emplace(key, map);
-  }
-  *out = map;
-  return QF_OK;
-}
-
 int* status_word_for_current_device() {
   static std::mutex mutex;
   static int* cache[64] = {};
@@ -309,28 +224,29 @@ int* status_word_for_current_device() {
   return cache[device];
 }
 
-int stages_for(bool fp8) {
-  int stages = g_tuned_stages > 0 ? g_tuned_stages : (fp8 ? kDefaultStagesFp8 : kDefaultStagesF16);
-  if (stages < kMinStages) stages = kMinStages;  // two pages in use + one being filled
-  if (stages > kMaxStages) stages = kMaxStages;
-  return stages;
+// Page pairs kept in flight ahead of the math.  qf_set_tuning speaks in pages
+// ("stages"): two pages per pair, one pair being computed.
+int depth_for() {
+  int depth = g_tuned_stages > 0 ? g_tuned_stages / 2 - 1 : kDefaultDepth;
+  if (depth < 1) depth = 1;
+  if (depth > kMaxDepth) depth = kMaxDepth;
+  return depth;
 }
 
-size_t fast_smem_bytes(bool fp8, int stages) {
-  const size_t ring = static_cast<size_t>(stages) * (fp8 ? 4096 : 8192);
+size_t fast_smem_bytes(bool fp8, int depth) {
+  const size_t ring = static_cast<size_t>(depth + 1) * (fp8 ? 8192 : 16384);
   const size_t merge = kMergeFloats * sizeof(float);
   return ring > merge ? ring : merge;
 }
 
 template <typename T, bool FP8, bool PROFILE>
-int launch_fast(const CUtensorMap& kmap, const CUtensorMap& vmap, const FastParams& p,
-                cudaStream_t stream) {
-  auto kernel = decode_partial_tma_kernel<T, FP8, PROFILE>;
-  const size_t smem = fast_smem_bytes(FP8, p.stages);
+int launch_fast(const FastParams& p, cudaStream_t stream) {
+  auto kernel = decode_partial_kernel<T, FP8, PROFILE>;
+  const size_t smem = fast_smem_bytes(FP8, p.depth);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
   const int64_t blocks = static_cast<int64_t>(p.batch) * p.kv_heads * p.split_k;
-  kernel<<<static_cast<unsigned>(blocks), kFastThreads, smem, stream>>>(kmap, vmap, p);
+  kernel<<<static_cast<unsigned>(blocks), kFastThreads, smem, stream>>>(p);
   QF_CUDA(cudaGetLastError());
   return QF_OK;
 }
@@ -393,16 +309,15 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
   void* out = direct_out ? a->out : nullptr;
 
   if (fast_path_ok(a)) {
-    const int elem_code = a->kv_fp8 ? 2 : (a->dtype == QF_DTYPE_F16 ? 0 : 1);
-    CUtensorMap kmap, vmap;
-    int rc = pool_tensor_map(a->k_pool, elem_code, a->num_pages, a->kv_heads, a->k_stride_page,
-                             a->k_stride_tok, a->k_stride_head, &kmap);
-    if (rc != QF_OK) return rc;
-    rc = pool_tensor_map(a->v_pool, elem_code, a->num_pages, a->kv_heads, a->v_stride_page,
-                         a->v_stride_tok, a->v_stride_head, &vmap);
-    if (rc != QF_OK) return rc;
     FastParams p{};
     p.q = a->q, p.q_sb = a->q_stride_b, p.q_sh = a->q_stride_h;
+    const int64_t elem = a->kv_fp8 ? 1 : 2;
+    p.k_pool = static_cast<const unsigned char*>(a->k_pool);
+    p.v_pool = static_cast<const unsigned char*>(a->v_pool);
+    p.k_page_bytes = a->k_stride_page * elem, p.k_tok_bytes = a->k_stride_tok * elem;
+    p.k_head_bytes = a->k_stride_head * elem;
+    p.v_page_bytes = a->v_stride_page * elem, p.v_tok_bytes = a->v_stride_tok * elem;
+    p.v_head_bytes = a->v_stride_head * elem;
     p.block_table = a->block_table, p.bt_sb = a->table_stride_b, p.bt_sp = a->table_stride_p;
     p.seq_lens = a->seq_lens, p.lens_stride = a->lens_stride;
     p.k_scale = a->k_scale, p.v_scale = a->v_scale;
@@ -413,16 +328,16 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
     p.status = status;
     p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
     p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
-    p.stages = stages_for(a->kv_fp8 != 0);
+    p.depth = depth_for();
     p.scale_log2 = a->scale * kLog2e;
     if (a->kv_fp8) {
       return a->dtype == QF_DTYPE_F16
-                 ? launch_fast<__half, true, PROFILE>(kmap, vmap, p, stream)
-                 : launch_fast<__nv_bfloat16, true, PROFILE>(kmap, vmap, p, stream);
+                 ? launch_fast<__half, true, PROFILE>(p, stream)
+                 : launch_fast<__nv_bfloat16, true, PROFILE>(p, stream);
     }
     return a->dtype == QF_DTYPE_F16
-               ? launch_fast<__half, false, PROFILE>(kmap, vmap, p, stream)
-               : launch_fast<__nv_bfloat16, false, PROFILE>(kmap, vmap, p, stream);
+               ? launch_fast<__half, false, PROFILE>(p, stream)
+               : launch_fast<__nv_bfloat16, false, PROFILE>(p, stream);
   }
 
   QF_REQUIRE(!PROFILE, "stage profiling requires the native grouped-decode layout");
@@ -535,18 +450,18 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
   const void* kernel;
   if (kv_fp8) {
     kernel = dtype == QF_DTYPE_F16
-                 ? reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__half, true, false>)
-                 : reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__nv_bfloat16, true, false>);
+                 ? reinterpret_cast<const void*>(qf::decode_partial_kernel<__half, true, false>)
+                 : reinterpret_cast<const void*>(qf::decode_partial_kernel<__nv_bfloat16, true, false>);
   } else {
     kernel = dtype == QF_DTYPE_F16
-                 ? reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__half, false, false>)
-                 : reinterpret_cast<const void*>(qf::decode_partial_tma_kernel<__nv_bfloat16, false, false>);
+                 ? reinterpret_cast<const void*>(qf::decode_partial_kernel<__half, false, false>)
+                 : reinterpret_cast<const void*>(qf::decode_partial_kernel<__nv_bfloat16, false, false>);
   }
   int previous = 0;
   QF_CUDA(cudaGetDevice(&previous));
   QF_CUDA(cudaSetDevice(device));
-  const int stages = qf::stages_for(kv_fp8 != 0);
-  const size_t smem = qf::fast_smem_bytes(kv_fp8 != 0, stages);
+  const int depth = qf::depth_for();
+  const size_t smem = qf::fast_smem_bytes(kv_fp8 != 0, depth);
   cudaFuncAttributes attr{};
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
@@ -569,13 +484,13 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
   info[7] = qf::kFastThreads;
   info[8] = active;
   info[9] = prop.maxThreadsPerMultiProcessor / 32;
-  info[10] = stages;
+  info[10] = 2 * (depth + 1);  // pages resident in the ring
   info[11] = prop.multiProcessorCount;
   return QF_OK;
 }
 
 int qf_set_tuning(int32_t stages, int32_t force_generic) {
-  QF_REQUIRE(stages >= 0 && stages <= qf::kMaxStages, "stages must be in [0, %d]", qf::kMaxStages);
+  QF_REQUIRE(stages >= 0 && stages <= 64, "stages must be in [0, 64]");
   qf::g_tuned_stages = stages;
   qf::g_force_generic = force_generic ? 1 : 0;
   return QF_OK;

@@ -6,28 +6,32 @@
 //   * one CTA of eight warps per (sequence, KV head, split): the six query heads
 //     of the GQA group share every K/V page load
 //     (same CTA grid as native_grouped_decode.cu:62-67);
-//   * pages stream through a ring of shared-memory stages guarded by full/empty
-//     mbarriers and filled by 4-D tiled TMA loads ([pages,16,kv,128] tensor map,
-//     box [1,16,1,128]) that lane 0 of warp 0 issues `stages - 2` pages ahead of
-//     the math; page ids are fetched 32 at a time, one batch ahead;
 //   * warps 0-3 compute heads 0-2 of the group, warps 4-7 heads 3-5.  Inside a
 //     head group, thread (r, c) owns head dims [8c, 8c+8) of FOUR tokens per
 //     iteration: rows r and r+8 of two consecutive pages.  Q (3 heads x 8 dims)
 //     and the accumulators (3 heads x 8 dims) take 48 registers, so four
 //     independent token chains fit without spilling and the per-iteration costs
-//     (barrier waits, score reduction, softmax, address arithmetic) are spread
-//     over four tokens;
+//     are spread over four tokens;
+//   * loads: 16-byte cp.async (global -> shared, no registers) into a ring of
+//     page-pair slots, `depth` pairs ahead of the math.  A thread and its twin in
+//     the other head group need the same eight chunks; the twin in group 0
+//     copies the four K chunks, the one in group 1 the four V chunks, and the
+//     two warps meet at a 64-thread named barrier once per iteration.  Each
+//     16-byte chunk of a page is fetched exactly once, a warp's copies cover
+//     whole 256-byte rows, and nothing spins: the only waits are
+//     cp.async.wait_group and bar.sync.  (A 4-D tiled TMA box of one KV head is
+//     16 rows of 256 B at a 512 B pitch and streams at 57 % of what these
+//     per-thread copies reach on the same pages: load_path_probe.cu.)
 //   * the twelve per-thread partial dots (4 tokens x 3 heads) are reduce-scattered
 //     over the 16 lanes that share those tokens with 12 shuffles, leaving one
 //     (token, head) score per lane; probabilities go back through shared memory
-//     as ready-made (p, p) operands of the packed FMAs;
+//     as ready-made (p, p) operands of the packed FMAs (fma.rn.f32x2);
 //   * the exponent offset is kept per (16-lane group, head) and only moves when a
 //     score exceeds it by 2^8, so rescaling the accumulators is off the common
 //     path; (out, offset, sum) stays self-consistent for the combine;
 //   * the per-group states merge once per CTA through shared memory.
 //
-// No tensor-core MMA: with M=6 the op is a bandwidth-bound GEMV.  No load here
-// names a cluster-multicast qualifier.  Every wait is bounded.
+// No tensor-core MMA: with M=6 the op is a bandwidth-bound GEMV.
 #pragma once
 
 #include "qf_common.cuh"
@@ -37,13 +41,11 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kFastThreads = kConsumerWarps * 32;
-constexpr int kMaxStages = 12;
-constexpr int kMinStages = 3;
-constexpr int kDefaultStagesF16 = 8;
-constexpr int kDefaultStagesFp8 = 12;
-constexpr int kHeadsPerThread = 3;   // half of the GQA group
-constexpr int kTokensPerThread = 4;  // rows r, r+8 of two pages
-constexpr int kGroupRows = 8;        // 16-lane groups per head group
+constexpr int kMaxDepth = 4;          // page pairs in flight ahead of the math
+constexpr int kDefaultDepth = 3;
+constexpr int kHeadsPerThread = 3;    // half of the GQA group
+constexpr int kTokensPerThread = 4;   // rows r, r+8 of two pages
+constexpr int kGroupRows = 8;         // 16-lane groups per head group
 constexpr int kMergeFloats = kConsumerWarps * kHeadsPerThread * QF_HEAD_DIM;  // 12 KB
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -54,6 +56,10 @@ constexpr float kOffsetSlack = 8.f;
 struct FastParams {
   const void* q;
   int64_t q_sb, q_sh;
+  const unsigned char* k_pool;
+  const unsigned char* v_pool;
+  int64_t k_page_bytes, k_tok_bytes, k_head_bytes;  // pool strides in bytes
+  int64_t v_page_bytes, v_tok_bytes, v_head_bytes;
   const void* block_table;
   int64_t bt_sb, bt_sp;
   const void* seq_lens;
@@ -69,15 +75,15 @@ struct FastParams {
   long long* cycles;
   int* status;
   int table_dtype, lens_dtype;
-  int batch, q_heads, kv_heads, split_k, stages;
+  int batch, q_heads, kv_heads, split_k, depth;
   float scale_log2;  // softmax scale * log2(e)
 };
 
 template <typename T, bool FP8>
 struct TileTraits {
-  static constexpr int kChunkBytes = FP8 ? 8 : 16;  // one thread's 8 elements
+  static constexpr int kChunkBytes = FP8 ? 8 : 16;                    // one thread's 8 elements
   static constexpr int kTileBytes = QF_PAGE_SIZE * 16 * kChunkBytes;  // K or V of a page and KV head
-  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kSlotBytes = 4 * kTileBytes;                   // K(A) K(B) V(A) V(B)
 };
 
 // This thread's 8 elements of one token row, as stored (16 bytes, 8 for FP8).
@@ -112,28 +118,28 @@ __device__ __forceinline__ void to_pairs(const RawChunk<FP8>& raw, float2 (&r)[4
   }
 }
 
-// Slow side of a barrier wait: poll until the phase completes, the cycle limit
-// passes, or another thread of the CTA has already given up.  Giving up raises
-// the CTA's abort flag and the device status word; the caller carries on with
-// whatever is in shared memory, so control flow never diverges and every later
-// wait returns at once.
-__device__ __forceinline__ void wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
-  if (*abort_flag) return;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return;
-    if (clock64() - start > kWaitCycleLimit) {
-      *abort_flag = 1;
-      atomicExch(status, kStatusWaitTimeout);
-      return;
-    }
+// Asynchronous global -> shared copy of one chunk (16 bytes, 8 for FP8), L2 only.
+template <bool FP8>
+__device__ __forceinline__ void copy_chunk_async(unsigned char* smem_dst, const unsigned char* src) {
+  if constexpr (FP8) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+  } else {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
   }
 }
-
-__device__ __forceinline__ void wait_phase(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                           int* status) {
-  if (!mbar_try_wait(bar, parity)) wait_slow(bar, parity, abort_flag, status);
+__device__ __forceinline__ void commit_copies() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Wait until at most `pending` of this thread's committed groups are in flight.
+__device__ __forceinline__ void wait_copies(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+  }
+}
+// Barrier among the 64 threads of a warp and its twin in the other head group.
+__device__ __forceinline__ void twin_barrier(int pair) {
+  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
 }
 
 // Reduce twelve per-thread partial dots v[token*3 + head] over the 16 lanes that
@@ -172,36 +178,30 @@ __device__ __forceinline__ float reduce_scatter12(const float (&v)[12], int sub)
 __device__ __forceinline__ constexpr int head_lane(int h) { return h == 0 ? 0 : h == 1 ? 2 : 1; }
 
 
+#ifndef QF_MIN_CTAS
+#define QF_MIN_CTAS 2
+#endif
 template <typename T, bool FP8, bool PROFILE>
-__global__ void __launch_bounds__(kFastThreads, 2)
-    decode_partial_tma_kernel(const __grid_constant__ CUtensorMap k_map,
-                              const __grid_constant__ CUtensorMap v_map, const FastParams p) {
+__global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
+    decode_partial_kernel(const FastParams p) {
   using Traits = TileTraits<T, FP8>;
-  extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ uint64_t full_bar[kMaxStages];
-  __shared__ uint64_t empty_bar[kMaxStages];
-  __shared__ float stage_scale[kMaxStages][2];
-  __shared__ int batch_ids[32];
-  __shared__ float batch_scale[32][2];
+  extern __shared__ __align__(1024) unsigned char smem[];  // ring of page-pair slots; merge scratch later
   // Probabilities of one iteration as (p, p) operands: [parity][warp][half-warp][token*3 + head]
   __shared__ __align__(16) float2 prob_pairs[2][kConsumerWarps][2][12];
   __shared__ float group_offset[2][kGroupRows][kHeadsPerThread];  // [head group][row][head]
   __shared__ float group_sum[2][kGroupRows][kHeadsPerThread];
   __shared__ float cta_offset[QF_GQA_GROUP];
   __shared__ float cta_sum[QF_GQA_GROUP];
-  __shared__ int abort_word;
-  __shared__ int issued_loads;  // iterations (pages) whose loads have been issued
 
   constexpr unsigned kFull = 0xffffffffu;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int sub = lane & 15;                          // dim chunk, and lane in the 16-lane group
-  const int head_group = warp >> 2;                   // heads 3*head_group .. +2 of the GQA group
-  const int row = ((warp & 3) << 1) | (lane >> 4);    // token rows `row` and `row + 8` of a page
-  const int stages = p.stages;
-  const int lookahead = stages - 2;                   // pages in flight ahead of the math
-  volatile int* abort_flag = &abort_word;
+  const int sub = lane & 15;                        // dim chunk, and lane in the 16-lane group
+  const int head_group = warp >> 2;                 // heads 3*head_group .. +2 of the GQA group
+  const int row = ((warp & 3) << 1) | (lane >> 4);  // token rows `row` and `row + 8` of a page
+  const int depth = p.depth;                        // page pairs in flight ahead of the math
+  const int slots = depth + 1;
 
   // blockIdx.x = (sequence * kv_heads + kv_head) * split_k + split
   const int split = blockIdx.x % p.split_k;
@@ -217,82 +217,72 @@ __global__ void __launch_bounds__(kFastThreads, 2)
   const int total_pages = (seq_len + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE;
   const int start_page = static_cast<int>(static_cast<int64_t>(split) * total_pages / p.split_k);
   const int end_page = static_cast<int>((static_cast<int64_t>(split) + 1) * total_pages / p.split_k);
-  const int num_iters = end_page - start_page;  // pages of this partition
-  // Tokens of this partition that exist, counted from its first page: every token
-  // index below this is inside the sequence.
-  const int tokens_here = min(seq_len - start_page * QF_PAGE_SIZE, num_iters * QF_PAGE_SIZE);
+  const int num_pages_here = end_page - start_page;  // pages of this partition
+  const int num_pairs = (num_pages_here + 1) >> 1;
+  // Tokens of this partition that exist, counted from its first page.
+  const int tokens_here = min(seq_len - start_page * QF_PAGE_SIZE, num_pages_here * QF_PAGE_SIZE);
 
-  if (tid == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kConsumerWarps);
-    }
-    abort_word = 0;
-    issued_loads = 0;
-    fence_barrier_init();
-    if (num_iters > 0) {
-      tma_prefetch_descriptor(&k_map);
-      tma_prefetch_descriptor(&v_map);
-    }
-  }
-  __syncthreads();
+  // ---- loads -------------------------------------------------------------
+  // This thread copies four chunks per page pair: rows `row`, `row+8` of pages A and
+  // B, of K when it is in head group 0 and of V when it is in head group 1.
+  const int pool_pages = static_cast<int>(p.num_pages);
+  const unsigned char* pool = head_group == 0 ? p.k_pool : p.v_pool;
+  const int64_t page_bytes = head_group == 0 ? p.k_page_bytes : p.v_page_bytes;
+  const int64_t tok_bytes = head_group == 0 ? p.k_tok_bytes : p.v_tok_bytes;
+  const unsigned char* pool_row =
+      pool + row * tok_bytes + kv_head * (head_group == 0 ? p.k_head_bytes : p.v_head_bytes) +
+      sub * Traits::kChunkBytes;
+  // Byte offset of this thread's chunk of token row `row` inside a K or V tile.
+  const int chunk_offset = (((warp & 3) << 5) | lane) * Traits::kChunkBytes;
+  constexpr int kRowPlus8 = 8 * 16 * Traits::kChunkBytes;
+  const int fill_offset = head_group * 2 * Traits::kTileBytes + chunk_offset;  // K tiles first, then V tiles
+  const int64_t table_row = sequence * p.bt_sb;
 
-  // ---- producer role (warp 0 only; every lane runs it, lane 0 issues) ----
-  // Page ids (and FP8 scales) are fetched 32 at a time into registers, one batch
-  // ahead, and parked in shared memory when their batch becomes current.
-  const int num_pages = static_cast<int>(p.num_pages);
-  int ids_next = -1;
-  float ks_next = 1.f, vs_next = 1.f;
-  auto fetch_batch = [&](int first_iter) {
-    const int idx = start_page + first_iter + lane;
-    ids_next = -1;
-    if (idx < end_page) {
-      const int64_t raw = load_index(p.block_table, p.table_dtype,
-                                     sequence * p.bt_sb + static_cast<int64_t>(idx) * p.bt_sp);
-      ids_next = raw >= 0 && raw < num_pages ? static_cast<int>(raw) : -1;  // -1: outside the pool
+  // Page id of page `index` of this partition, or -1 when it does not exist or
+  // lies outside the pool (recorded in the status word, never dereferenced).
+  auto page_id_of = [&](int index) -> int {
+    if (index >= num_pages_here) return -1;
+    const int64_t raw = load_index(p.block_table, p.table_dtype,
+                                   table_row + static_cast<int64_t>(start_page + index) * p.bt_sp);
+    if (raw < 0 || raw >= pool_pages) {
+      atomicExch(p.status, kStatusBadPageId);
+      return -1;
     }
-    if (FP8) {
-      ks_next = ids_next >= 0 ? p.k_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
-      vs_next = ids_next >= 0 ? p.v_scale[static_cast<int64_t>(ids_next) * p.kv_heads + kv_head] : 1.f;
-    }
+    return static_cast<int>(raw);
   };
-  // Issues the loads of page `index` (0-based in this partition; called with
-  // index = 0, 1, 2, ...) into the next stage of the ring, once the previous
-  // occupant of that stage has been released.  A fresh barrier reports the phase
-  // of parity 1 complete, so the first lap never waits.
-  int pstage = 0;
-  uint32_t pparity = 1u;
-  auto produce = [&](int index) {
-    if ((index & 31) == 0) {
-      if (index == 0) fetch_batch(0);
-      __syncwarp();
-      batch_ids[lane] = ids_next;
-      if (FP8) batch_scale[lane][0] = ks_next, batch_scale[lane][1] = vs_next;
-      __syncwarp();
-      if (index + 32 < num_iters) fetch_batch(index + 32);
-    }
-    if (lane == 0) {
-      wait_phase(&empty_bar[pstage], pparity, abort_flag, p.status);
-      const int page_id = batch_ids[index & 31];
-      if (page_id < 0) atomicExch(p.status, kStatusBadPageId);
-      if (FP8) {
-        stage_scale[pstage][0] = batch_scale[index & 31][0];
-        stage_scale[pstage][1] = batch_scale[index & 31][1];
+  auto copy_page = [&](unsigned char* dst, int page_id) {
+    if (page_id >= 0) {
+      const unsigned char* src = pool_row + static_cast<int64_t>(page_id) * page_bytes;
+      copy_chunk_async<FP8>(dst, src);
+      copy_chunk_async<FP8>(dst + kRowPlus8, src + 8 * tok_bytes);
+    } else {
+      // no such page: zeros, so that nothing stale or non-finite is ever multiplied
+      if constexpr (FP8) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
+        *reinterpret_cast<uint2*>(dst + kRowPlus8) = make_uint2(0u, 0u);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dst + kRowPlus8) = make_uint4(0u, 0u, 0u, 0u);
       }
-      unsigned char* dst = smem + pstage * Traits::kStageBytes;
-      mbar_arrive_expect_tx(&full_bar[pstage], Traits::kStageBytes);
-      // A page id outside the pool reads as zeros (TMA out-of-bounds fill).
-      tma_load_4d(dst, &k_map, &full_bar[pstage], 0, kv_head, 0, page_id);
-      tma_load_4d(dst + Traits::kTileBytes, &v_map, &full_bar[pstage], 0, kv_head, 0, page_id);
-      issued_loads = index + 1;
     }
-    if (++pstage == stages) pstage = 0, pparity ^= 1u;
-    __syncwarp();
   };
-
-  if (warp == 0) {
-    for (int i = 0; i < lookahead && i < num_iters; ++i) produce(i);
-  }
+  // Page ids of the pair to be issued next; fetched one iteration early.
+  int next_id_a = page_id_of(0), next_id_b = page_id_of(1);
+  int next_pair = 0;  // pair whose copies are issued next
+  int fill_slot = 0;
+  auto issue_pair = [&]() {
+    if (next_pair < num_pairs) {
+      unsigned char* dst = smem + fill_slot * Traits::kSlotBytes + fill_offset;
+      copy_page(dst, next_id_a);
+      copy_page(dst + Traits::kTileBytes, next_id_b);
+      ++next_pair;
+      next_id_a = page_id_of(2 * next_pair);
+      next_id_b = page_id_of(2 * next_pair + 1);
+    }
+    commit_copies();  // always, so that group counting stays uniform
+    if (++fill_slot == slots) fill_slot = 0;
+  };
+  for (int i = 0; i < depth; ++i) issue_pair();
 
   // ---- per-thread state: 3 heads x 8 dims of Q (pre-scaled) and of the output ----
   float2 q2[kHeadsPerThread][4];
@@ -301,7 +291,7 @@ __global__ void __launch_bounds__(kFastThreads, 2)
   for (int h = 0; h < kHeadsPerThread; ++h)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[h][j] = make_float2(0.f, 0.f);
-  if (num_iters > 0) {
+  if (num_pairs > 0) {
     const T* qbase = static_cast<const T*>(p.q) + sequence * p.q_sb +
                      (static_cast<int64_t>(kv_head) * QF_GQA_GROUP + head_group * kHeadsPerThread) * p.q_sh +
                      sub * 8;
@@ -316,40 +306,49 @@ __global__ void __launch_bounds__(kFastThreads, 2)
     }
   }
   // After the reduce-scatter this lane owns one (token, head) of its group:
-  const int my_token = ((sub >> 3) & 1) * 2 + ((sub >> 2) & 1);  // 0: (page A,row) 1: (A,row+8) 2: (B,row) 3: (B,row+8)
+  // token 0: (page A, row)  1: (A, row+8)  2: (B, row)  3: (B, row+8)
+  const int my_token = ((sub >> 3) & 1) * 2 + ((sub >> 2) & 1);
   const int my_head = (sub & 1) ? 2 : ((sub >> 1) & 1);
   float my_offset = -INFINITY;  // exponent offset of my head, shared by the group (log2 units)
   float my_sum = 0.f;           // sum of p over my token stream
-  // Byte offset of this thread's chunk of token row `row` inside a K or V tile.
-  const int chunk_offset = (((warp & 3) << 5) | lane) * Traits::kChunkBytes;
-  constexpr int kRowPlus8 = 8 * 16 * Traits::kChunkBytes;
   float2* prob_slot = &prob_pairs[0][warp][lane >> 4][0];
   constexpr int kProbParityStride = kConsumerWarps * 2 * 12;  // float2 elements
 
   // ------------------------------ main loop -------------------------------
-  // One iteration = two pages (A, B) = four tokens per thread.  A missing page B
+  // One iteration = one page pair (A, B) = four tokens per thread.  A missing page B
   // (odd page count) and the sequence's partial last page are handled by one
   // rule: token t of the partition exists iff t < tokens_here.
   long long t_wait = 0, t_total = 0, t_mark = 0;
   if (PROFILE) t_total = clock64();
-  int stage_a = 0;
-  uint32_t phase_a = 0;
-  int produce_next = lookahead < num_iters ? lookahead : num_iters;  // next page index to issue (warp 0)
-  for (int page_a = 0; page_a < num_iters; page_a += 2) {
-    int stage_b = stage_a + 1;
-    uint32_t phase_b = phase_a;
-    if (stage_b == stages) stage_b = 0, phase_b ^= 1u;
-    const bool has_b = page_a + 1 < num_iters;
-    if (warp == 0) {
-      // keep the ring `lookahead` pages ahead of the pair being computed
-      for (int n = 0; n < 2 && produce_next < num_iters; ++n) produce(produce_next++);
+  // FP8: dequantisation scales of the page that holds this lane's token, fetched an
+  // iteration ahead (the lane that owns a score only needs its own page's scales).
+  float k_mul = 1.f, v_mul = 1.f, k_mul_next = 1.f, v_mul_next = 1.f;
+  auto fetch_scales = [&](int pair) {
+    const int index = 2 * pair + (my_token >> 1);
+    k_mul_next = v_mul_next = 1.f;
+    if (index < num_pages_here) {
+      const int64_t raw = load_index(p.block_table, p.table_dtype,
+                                     table_row + static_cast<int64_t>(start_page + index) * p.bt_sp);
+      if (raw >= 0 && raw < pool_pages) {
+        k_mul_next = p.k_scale[raw * p.kv_heads + kv_head];
+        v_mul_next = p.v_scale[raw * p.kv_heads + kv_head];
+      }
     }
-    const unsigned char* tile_a = smem + stage_a * Traits::kStageBytes + chunk_offset;
-    const unsigned char* tile_b = smem + stage_b * Traits::kStageBytes + chunk_offset;
+  };
+  if (FP8) fetch_scales(0);
+  int read_slot = 0;
+  for (int pair = 0; pair < num_pairs; ++pair) {
     if (PROFILE) t_mark = clock64();
-    wait_phase(&full_bar[stage_a], phase_a, abort_flag, p.status);
-    if (has_b) wait_phase(&full_bar[stage_b], phase_b, abort_flag, p.status);
+    wait_copies(depth - 1);  // this thread's copies of `pair` have landed
+    twin_barrier(warp & 3);  // so have the twin's; and the twin is done with the previous slot
     if (PROFILE) t_wait += clock64() - t_mark;
+    issue_pair();            // refill the slot both twins have just left
+    if (FP8) {
+      k_mul = k_mul_next, v_mul = v_mul_next;
+      fetch_scales(pair + 1);
+    }
+    const unsigned char* slot = smem + read_slot * Traits::kSlotBytes + chunk_offset;
+    if (++read_slot == slots) read_slot = 0;
 
     // ---- scores: q . k for 3 heads x 4 tokens over this thread's 8 dims ----
     float dots[12];
@@ -364,19 +363,14 @@ __global__ void __launch_bounds__(kFastThreads, 2)
         dots[base + h] = d.x + d.y;
       }
     };
-    score_token(tile_a, 0);
-    score_token(tile_a + kRowPlus8, 3);
-    if (has_b) {
-      score_token(tile_b, 6);
-      score_token(tile_b + kRowPlus8, 9);
-    } else {
-#pragma unroll
-      for (int i = 6; i < 12; ++i) dots[i] = 0.f;
-    }
+    score_token(slot, 0);
+    score_token(slot + kRowPlus8, 3);
+    score_token(slot + Traits::kTileBytes, 6);
+    score_token(slot + Traits::kTileBytes + kRowPlus8, 9);
     float score = reduce_scatter12(dots, sub);
-    const int token_base = page_a * QF_PAGE_SIZE + row;  // partition-relative index of token 0
+    const int token_base = pair * 2 * QF_PAGE_SIZE + row;  // partition-relative index of token 0
     const bool my_valid = token_base + (my_token >> 1) * QF_PAGE_SIZE + (my_token & 1) * 8 < tokens_here;
-    if (FP8) score *= stage_scale[(my_token >> 1) ? stage_b : stage_a][0];
+    if (FP8) score *= k_mul;
     if (!my_valid) score = -INFINITY;
 
     // ---- online softmax; the offset of a head is shared by its four token lanes ----
@@ -399,10 +393,10 @@ __global__ void __launch_bounds__(kFastThreads, 2)
     float prob = fast_exp2(score - my_offset);
     if (!my_valid) prob = 0.f;  // also covers offset == -inf (NaN from inf - inf)
     my_sum += prob;
-    if (FP8) prob *= stage_scale[(my_token >> 1) ? stage_b : stage_a][1];
+    if (FP8) prob *= v_mul;
 
     // ---- publish the twelve probabilities of this group as (p, p) pairs ----
-    float2* probs = prob_slot + ((page_a >> 1) & 1) * kProbParityStride;
+    float2* probs = prob_slot + (pair & 1) * kProbParityStride;
     probs[my_token * 3 + my_head] = make_float2(prob, prob);  // head 2 is written twice, same value
     __syncwarp();
     float4 pp[6];
@@ -412,7 +406,7 @@ __global__ void __launch_bounds__(kFastThreads, 2)
     // ---- values: acc[h] += p[token][h] * v[token] ----
     auto add_token = [&](const unsigned char* at, int k) {
       float2 vreg[4];
-      to_pairs<T, FP8>(load_raw<FP8>(at + Traits::kTileBytes), vreg);
+      to_pairs<T, FP8>(load_raw<FP8>(at), vreg);
 #pragma unroll
       for (int h = 0; h < kHeadsPerThread; ++h) {
         const int i = k * 3 + h;  // compile-time after unrolling
@@ -422,50 +416,31 @@ __global__ void __launch_bounds__(kFastThreads, 2)
         for (int j = 0; j < 4; ++j) acc[h][j] = __ffma2_rn(p2, vreg[j], acc[h][j]);
       }
     };
+    const unsigned char* values = slot + 2 * Traits::kTileBytes;
     if (token_base + 8 + QF_PAGE_SIZE < tokens_here) {
       // all four tokens exist (the common case)
-      add_token(tile_a, 0);
-      add_token(tile_a + kRowPlus8, 1);
-      add_token(tile_b, 2);
-      add_token(tile_b + kRowPlus8, 3);
+      add_token(values, 0);
+      add_token(values + kRowPlus8, 1);
+      add_token(values + Traits::kTileBytes, 2);
+      add_token(values + Traits::kTileBytes + kRowPlus8, 3);
     } else {
-      if (token_base < tokens_here) add_token(tile_a, 0);
-      if (token_base + 8 < tokens_here) add_token(tile_a + kRowPlus8, 1);
-      if (token_base + QF_PAGE_SIZE < tokens_here) add_token(tile_b, 2);
-      if (token_base + QF_PAGE_SIZE + 8 < tokens_here) add_token(tile_b + kRowPlus8, 3);
+      // a token that does not exist may hold anything (NaN included): skip it
+      if (token_base < tokens_here) add_token(values, 0);
+      if (token_base + 8 < tokens_here) add_token(values + kRowPlus8, 1);
+      if (token_base + QF_PAGE_SIZE < tokens_here) add_token(values + Traits::kTileBytes, 2);
+      if (token_base + QF_PAGE_SIZE + 8 < tokens_here) add_token(values + Traits::kTileBytes + kRowPlus8, 3);
     }
-
-    // ---- both stages are in registers: hand them back to the producer ----
-    __syncwarp();
-    if (lane == 0) {
-      mbar_arrive(&empty_bar[stage_a]);
-      if (has_b) mbar_arrive(&empty_bar[stage_b]);
-    }
-    stage_a = stage_b + 1, phase_a = phase_b;
-    if (stage_a == stages) stage_a = 0, phase_a ^= 1u;
   }
   if (PROFILE && p.cycles != nullptr && tid == 32) {
-    // One pure-consumer warp per CTA reports {waiting for pages, whole loop, 0, 0}.
+    // One warp per CTA reports {waiting for pages, whole loop, 0, 0}.
     long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;
     dst[0] = t_wait, dst[1] = clock64() - t_total, dst[2] = 0, dst[3] = 0;
   }
 
   // ------------------------------ CTA merge -------------------------------
-  // Barrier: every stage has been read, so the ring is free for the merge.
+  // Barrier: every slot has been read, so the ring is free for the merge.
+  wait_copies(0);
   __syncthreads();
-  if (*abort_flag) {
-    // A wait ran out somewhere in this CTA.  Give the loads already issued a
-    // bounded chance to land before their shared memory is reused or released.
-    if (tid == 0) {
-      abort_word = 0;  // let the waits below poll again
-      const int issued = issued_loads;
-      for (int s = 0; s < stages && s < issued; ++s) {
-        const int last = ((issued - 1 - s) / stages) * stages + s;  // last page that used stage s
-        wait_phase(&full_bar[s], static_cast<uint32_t>(last / stages) & 1u, abort_flag, p.status);
-      }
-    }
-    __syncthreads();
-  }
   float* merge = reinterpret_cast<float*>(smem);  // [8 warps][3 heads][128]
   {
     // sum of a head over the group's four token streams (lanes differing in bits 3, 2)

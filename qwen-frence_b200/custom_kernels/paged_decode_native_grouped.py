@@ -5,7 +5,7 @@ points and signatures, so baseline/kernel_dispatch.py:84-88 and
 engine/kvcache/paged_decode_attention.py:228-234 call it unchanged.
 
 The partial kernel assigns one CTA to a (request, KV head, split); the six
-query heads of the group share every K/V page, which is streamed by TMA into a
+query heads of the group share every K/V page, which is copied once into a
 shared-memory ring; the combine merges the numerically stable fp32 partials.
 Both run inside libqf_hotpath.so (sm_100a); nothing here depends on Triton, on
 a torch C++ extension or on a CPU fallback.
