@@ -351,7 +351,7 @@ def main():
         launch_bytes = partial_kernel_bytes(workload, step.split_k, step.fp8)
         achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
         roofline = {
-            "bound": "hbm", "kernel": "decode_partial_tma_kernel", "achieved": achieved, "peak": peak,
+            "bound": "hbm", "kernel": "decode_partial_kernel", "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed))

@@ -222,11 +222,10 @@ int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
  * for tests and debugging only.  `reset` != 0 clears it after reading. */
 int qf_device_status(int32_t* status, int32_t reset);
 
-/* Choice of pipeline depth / forcing the generic path, for experiments.
- * `stages` is the number of pages resident in the fast kernel's shared-memory
- * ring (rounded to whole page pairs, clamped to 4..10); 0 restores the default
- * of 8.  force_generic != 0 routes every attention call through the
- * stride-generic kernel. */
+/* Switches for experiments.  force_generic != 0 routes every attention call
+ * through the stride-generic kernel.  `stages` is accepted and recorded but the
+ * fast kernel's shared-memory ring has a fixed depth (four page pairs, three in
+ * flight), chosen at compile time. */
 int qf_set_tuning(int32_t stages, int32_t force_generic);
 
 #ifdef __cplusplus

@@ -224,17 +224,8 @@ int* status_word_for_current_device() {
   return cache[device];
 }
 
-// Page pairs kept in flight ahead of the math.  qf_set_tuning speaks in pages
-// ("stages"): two pages per pair, one pair being computed.
-int depth_for() {
-  int depth = g_tuned_stages > 0 ? g_tuned_stages / 2 - 1 : kDefaultDepth;
-  if (depth < 1) depth = 1;
-  if (depth > kMaxDepth) depth = kMaxDepth;
-  return depth;
-}
-
-size_t fast_smem_bytes(bool fp8, int depth) {
-  const size_t ring = static_cast<size_t>(depth + 1) * (fp8 ? 8192 : 16384);
+size_t fast_smem_bytes(bool fp8) {
+  const size_t ring = static_cast<size_t>(kSlots) * (fp8 ? 8192 : 16384);
   const size_t merge = kMergeFloats * sizeof(float);
   return ring > merge ? ring : merge;
 }
@@ -242,7 +233,7 @@ size_t fast_smem_bytes(bool fp8, int depth) {
 template <typename T, bool FP8, bool PROFILE>
 int launch_fast(const FastParams& p, cudaStream_t stream) {
   auto kernel = decode_partial_kernel<T, FP8, PROFILE>;
-  const size_t smem = fast_smem_bytes(FP8, p.depth);
+  const size_t smem = fast_smem_bytes(FP8);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
   const int64_t blocks = static_cast<int64_t>(p.batch) * p.kv_heads * p.split_k;
@@ -328,7 +319,6 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
     p.status = status;
     p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
     p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
-    p.depth = depth_for();
     p.scale_log2 = a->scale * kLog2e;
     if (a->kv_fp8) {
       return a->dtype == QF_DTYPE_F16
@@ -460,8 +450,7 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
   int previous = 0;
   QF_CUDA(cudaGetDevice(&previous));
   QF_CUDA(cudaSetDevice(device));
-  const int depth = qf::depth_for();
-  const size_t smem = qf::fast_smem_bytes(kv_fp8 != 0, depth);
+  const size_t smem = qf::fast_smem_bytes(kv_fp8 != 0);
   cudaFuncAttributes attr{};
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
@@ -484,7 +473,7 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
   info[7] = qf::kFastThreads;
   info[8] = active;
   info[9] = prop.maxThreadsPerMultiProcessor / 32;
-  info[10] = 2 * (depth + 1);  // pages resident in the ring
+  info[10] = 2 * qf::kSlots;  // pages resident in the ring
   info[11] = prop.multiProcessorCount;
   return QF_OK;
 }

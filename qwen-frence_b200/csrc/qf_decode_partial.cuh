@@ -13,7 +13,7 @@
 //     independent token chains fit without spilling and the per-iteration costs
 //     are spread over four tokens;
 //   * loads: 16-byte cp.async (global -> shared, no registers) into a ring of
-//     page-pair slots, `depth` pairs ahead of the math.  A thread and its twin in
+//     page-pair slots, three pairs ahead of the math.  A thread and its twin in
 //     the other head group need the same eight chunks; the twin in group 0
 //     copies the four K chunks, the one in group 1 the four V chunks, and the
 //     two warps meet at a 64-thread named barrier once per iteration.  Each
@@ -41,8 +41,8 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kFastThreads = kConsumerWarps * 32;
-constexpr int kMaxDepth = 4;          // page pairs in flight ahead of the math
-constexpr int kDefaultDepth = 3;
+constexpr int kDepth = 3;             // page pairs in flight ahead of the math
+constexpr int kSlots = kDepth + 1;    // page-pair slots in the ring (a power of two)
 constexpr int kHeadsPerThread = 3;    // half of the GQA group
 constexpr int kTokensPerThread = 4;   // rows r, r+8 of two pages
 constexpr int kGroupRows = 8;         // 16-lane groups per head group
@@ -75,7 +75,7 @@ struct FastParams {
   long long* cycles;
   int* status;
   int table_dtype, lens_dtype;
-  int batch, q_heads, kv_heads, split_k, depth;
+  int batch, q_heads, kv_heads, split_k;
   float scale_log2;  // softmax scale * log2(e)
 };
 
@@ -128,42 +128,35 @@ __device__ __forceinline__ void copy_chunk_async(unsigned char* smem_dst, const 
   }
 }
 __device__ __forceinline__ void commit_copies() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Wait until at most `pending` of this thread's committed groups are in flight.
-__device__ __forceinline__ void wait_copies(int pending) {
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-  }
+// Wait until at most kDepth - 1 of this thread's committed groups are in flight,
+// i.e. until the oldest of the kDepth pairs it keeps in flight has landed.
+__device__ __forceinline__ void wait_oldest_pair() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
 }
+__device__ __forceinline__ void wait_all_copies() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 // Barrier among the 64 threads of a warp and its twin in the other head group.
 __device__ __forceinline__ void twin_barrier(int pair) {
   asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
 }
 
-// Reduce twelve per-thread partial dots v[token*3 + head] over the 16 lanes that
-// hold the same four tokens, so that each lane ends with the full dot product of
-// ONE (token, head).  With lane bits b3 b2 b1 b0:
-//   token = 2*b3 + b2,   head = b0 ? 2 : b1
+// Reduce twelve per-thread partial dots over the 16 lanes that hold the same four
+// tokens, so that each lane ends with the full dot product of ONE (token, head).
+// With lane bits b3 b2 b1 b0 the lane ends up owning
+//   token = 2*b3 + b2  (0: page A,row  1: A,row+8  2: B,row  3: B,row+8),  head = b0 ? 2 : b1.
+// The caller hands the dots in a LANE-DEPENDENT order, v[(2*P + R)*3 + head], where
+// P = 0 is the page this lane keeps (A if b3 = 0, else B) and R = 0 the row it keeps
+// (row if b2 = 0, else row+8): the exchange partner at distance 8 (4) keeps the other
+// page (row), so "keep the first half, send the second half" needs no selects.
 // (head 2 is held twice, by b1 = 0 and b1 = 1).  12 shuffles, 12 adds.
 __device__ __forceinline__ float reduce_scatter12(const float (&v)[12], int sub) {
   constexpr unsigned kFull = 0xffffffffu;
-  const bool b3 = sub & 8, b2 = sub & 4, b1 = sub & 2, b0 = sub & 1;
+  const bool b1 = sub & 2, b0 = sub & 1;
   float six[6];
 #pragma unroll
-  for (int i = 0; i < 6; ++i) {
-    const float keep = b3 ? v[6 + i] : v[i];
-    const float send = b3 ? v[i] : v[6 + i];
-    six[i] = keep + __shfl_xor_sync(kFull, send, 8);
-  }
+  for (int i = 0; i < 6; ++i) six[i] = v[i] + __shfl_xor_sync(kFull, v[6 + i], 8);
   float three[3];
 #pragma unroll
-  for (int h = 0; h < 3; ++h) {
-    const float keep = b2 ? six[3 + h] : six[h];
-    const float send = b2 ? six[h] : six[3 + h];
-    three[h] = keep + __shfl_xor_sync(kFull, send, 4);
-  }
+  for (int h = 0; h < 3; ++h) three[h] = six[h] + __shfl_xor_sync(kFull, six[3 + h], 4);
   float a = b1 ? three[1] : three[0];
   const float send_a = b1 ? three[0] : three[1];
   a += __shfl_xor_sync(kFull, send_a, 2);
@@ -200,8 +193,6 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   const int sub = lane & 15;                        // dim chunk, and lane in the 16-lane group
   const int head_group = warp >> 2;                 // heads 3*head_group .. +2 of the GQA group
   const int row = ((warp & 3) << 1) | (lane >> 4);  // token rows `row` and `row + 8` of a page
-  const int depth = p.depth;                        // page pairs in flight ahead of the math
-  const int slots = depth + 1;
 
   // blockIdx.x = (sequence * kv_heads + kv_head) * split_k + split
   const int split = blockIdx.x % p.split_k;
@@ -236,15 +227,20 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   const int chunk_offset = (((warp & 3) << 5) | lane) * Traits::kChunkBytes;
   constexpr int kRowPlus8 = 8 * 16 * Traits::kChunkBytes;
   const int fill_offset = head_group * 2 * Traits::kTileBytes + chunk_offset;  // K tiles first, then V tiles
-  const int64_t table_row = sequence * p.bt_sb;
-
-  // Page id of page `index` of this partition, or -1 when it does not exist or
-  // lies outside the pool (recorded in the status word, never dereferenced).
-  auto page_id_of = [&](int index) -> int {
-    if (index >= num_pages_here) return -1;
-    const int64_t raw = load_index(p.block_table, p.table_dtype,
-                                   table_row + static_cast<int64_t>(start_page + index) * p.bt_sp);
-    if (raw < 0 || raw >= pool_pages) {
+  // The partition's block-table entries: byte pointer to the next unread entry.
+  const int table_elem = p.table_dtype == QF_INDEX_I64 ? 8 : 4;
+  const int64_t table_step = p.bt_sp * table_elem;
+  const unsigned char* table_first =
+      static_cast<const unsigned char*>(p.block_table) +
+      (sequence * p.bt_sb + static_cast<int64_t>(start_page) * p.bt_sp) * table_elem;
+  const unsigned char* table_next = table_first;
+  // Page id stored at `at`, or -1 when the page does not exist or lies outside
+  // the pool (recorded in the status word, never dereferenced).
+  auto read_id = [&](const unsigned char* at, bool exists) -> int {
+    if (!exists) return -1;
+    const int64_t raw = table_elem == 8 ? *reinterpret_cast<const int64_t*>(at)
+                                        : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
+    if (static_cast<uint64_t>(raw) >= static_cast<uint64_t>(pool_pages)) {
       atomicExch(p.status, kStatusBadPageId);
       return -1;
     }
@@ -266,23 +262,31 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       }
     }
   };
-  // Page ids of the pair to be issued next; fetched one iteration early.
-  int next_id_a = page_id_of(0), next_id_b = page_id_of(1);
-  int next_pair = 0;  // pair whose copies are issued next
+  // Page ids of the pair to be issued next are fetched one iteration early.
+  int pages_left = num_pages_here;  // pages whose ids have not been fetched yet
+  int next_id_a = -1, next_id_b = -1;
+  auto fetch_ids = [&]() {
+    next_id_a = read_id(table_next, pages_left > 0);
+    next_id_b = read_id(table_next + table_step, pages_left > 1);
+    table_next += 2 * table_step;
+    pages_left -= 2;
+  };
+  fetch_ids();
+  int pairs_to_issue = num_pairs;
   int fill_slot = 0;
   auto issue_pair = [&]() {
-    if (next_pair < num_pairs) {
+    if (pairs_to_issue > 0) {
       unsigned char* dst = smem + fill_slot * Traits::kSlotBytes + fill_offset;
       copy_page(dst, next_id_a);
       copy_page(dst + Traits::kTileBytes, next_id_b);
-      ++next_pair;
-      next_id_a = page_id_of(2 * next_pair);
-      next_id_b = page_id_of(2 * next_pair + 1);
+      --pairs_to_issue;
+      fetch_ids();
     }
     commit_copies();  // always, so that group counting stays uniform
-    if (++fill_slot == slots) fill_slot = 0;
+    fill_slot = (fill_slot + 1) & (kSlots - 1);
   };
-  for (int i = 0; i < depth; ++i) issue_pair();
+#pragma unroll
+  for (int i = 0; i < kDepth; ++i) issue_pair();
 
   // ---- per-thread state: 3 heads x 8 dims of Q (pre-scaled) and of the output ----
   float2 q2[kHeadsPerThread][4];
@@ -312,6 +316,9 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   float my_offset = -INFINITY;  // exponent offset of my head, shared by the group (log2 units)
   float my_sum = 0.f;           // sum of p over my token stream
   float2* prob_slot = &prob_pairs[0][warp][lane >> 4][0];
+  // Offsets, inside a slot's K region, of the page / row this lane keeps and sends.
+  const int keep_page = (sub & 8) ? Traits::kTileBytes : 0, send_page = Traits::kTileBytes - keep_page;
+  const int keep_row = (sub & 4) ? kRowPlus8 : 0, send_row = kRowPlus8 - keep_row;
   constexpr int kProbParityStride = kConsumerWarps * 2 * 12;  // float2 elements
 
   // ------------------------------ main loop -------------------------------
@@ -327,9 +334,10 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     const int index = 2 * pair + (my_token >> 1);
     k_mul_next = v_mul_next = 1.f;
     if (index < num_pages_here) {
-      const int64_t raw = load_index(p.block_table, p.table_dtype,
-                                     table_row + static_cast<int64_t>(start_page + index) * p.bt_sp);
-      if (raw >= 0 && raw < pool_pages) {
+      const unsigned char* at = table_first + index * table_step;
+      const int64_t raw = table_elem == 8 ? *reinterpret_cast<const int64_t*>(at)
+                                          : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
+      if (static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages)) {
         k_mul_next = p.k_scale[raw * p.kv_heads + kv_head];
         v_mul_next = p.v_scale[raw * p.kv_heads + kv_head];
       }
@@ -337,9 +345,10 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   };
   if (FP8) fetch_scales(0);
   int read_slot = 0;
+  const int full_pairs = tokens_here >> 5;
   for (int pair = 0; pair < num_pairs; ++pair) {
     if (PROFILE) t_mark = clock64();
-    wait_copies(depth - 1);  // this thread's copies of `pair` have landed
+    wait_oldest_pair();      // this thread's copies of `pair` have landed
     twin_barrier(warp & 3);  // so have the twin's; and the twin is done with the previous slot
     if (PROFILE) t_wait += clock64() - t_mark;
     issue_pair();            // refill the slot both twins have just left
@@ -348,7 +357,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       fetch_scales(pair + 1);
     }
     const unsigned char* slot = smem + read_slot * Traits::kSlotBytes + chunk_offset;
-    if (++read_slot == slots) read_slot = 0;
+    read_slot = (read_slot + 1) & (kSlots - 1);
 
     // ---- scores: q . k for 3 heads x 4 tokens over this thread's 8 dims ----
     float dots[12];
@@ -363,15 +372,22 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
         dots[base + h] = d.x + d.y;
       }
     };
-    score_token(slot, 0);
-    score_token(slot + kRowPlus8, 3);
-    score_token(slot + Traits::kTileBytes, 6);
-    score_token(slot + Traits::kTileBytes + kRowPlus8, 9);
+    // lane-dependent order: kept page / kept row first (see reduce_scatter12)
+    score_token(slot + keep_page + keep_row, 0);
+    score_token(slot + keep_page + send_row, 3);
+    score_token(slot + send_page + keep_row, 6);
+    score_token(slot + send_page + send_row, 9);
     float score = reduce_scatter12(dots, sub);
+    // Pairs below `full_pairs` hold 32 existing tokens; only the partition's last
+    // pair can hold tokens past the sequence end or lack its second page.
+    const bool all_valid = pair < full_pairs;
     const int token_base = pair * 2 * QF_PAGE_SIZE + row;  // partition-relative index of token 0
-    const bool my_valid = token_base + (my_token >> 1) * QF_PAGE_SIZE + (my_token & 1) * 8 < tokens_here;
+    bool my_valid = true;
     if (FP8) score *= k_mul;
-    if (!my_valid) score = -INFINITY;
+    if (!all_valid) {
+      my_valid = token_base + (my_token >> 1) * QF_PAGE_SIZE + (my_token & 1) * 8 < tokens_here;
+      if (!my_valid) score = -INFINITY;
+    }
 
     // ---- online softmax; the offset of a head is shared by its four token lanes ----
     const bool grow = score > my_offset + kOffsetSlack;  // also the first valid token (offset -inf)
@@ -391,7 +407,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       }
     }
     float prob = fast_exp2(score - my_offset);
-    if (!my_valid) prob = 0.f;  // also covers offset == -inf (NaN from inf - inf)
+    if (!all_valid && !my_valid) prob = 0.f;  // also covers offset == -inf (NaN from inf - inf)
     my_sum += prob;
     if (FP8) prob *= v_mul;
 
@@ -399,9 +415,6 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     float2* probs = prob_slot + (pair & 1) * kProbParityStride;
     probs[my_token * 3 + my_head] = make_float2(prob, prob);  // head 2 is written twice, same value
     __syncwarp();
-    float4 pp[6];
-#pragma unroll
-    for (int i = 0; i < 6; ++i) pp[i] = reinterpret_cast<const float4*>(probs)[i];
 
     // ---- values: acc[h] += p[token][h] * v[token] ----
     auto add_token = [&](const unsigned char* at, int k) {
@@ -409,15 +422,13 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       to_pairs<T, FP8>(load_raw<FP8>(at), vreg);
 #pragma unroll
       for (int h = 0; h < kHeadsPerThread; ++h) {
-        const int i = k * 3 + h;  // compile-time after unrolling
-        const float2 p2 = (i & 1) ? make_float2(pp[i >> 1].z, pp[i >> 1].w)
-                                  : make_float2(pp[i >> 1].x, pp[i >> 1].y);
+        const float2 p2 = probs[k * 3 + h];
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[h][j] = __ffma2_rn(p2, vreg[j], acc[h][j]);
       }
     };
     const unsigned char* values = slot + 2 * Traits::kTileBytes;
-    if (token_base + 8 + QF_PAGE_SIZE < tokens_here) {
+    if (all_valid) {
       // all four tokens exist (the common case)
       add_token(values, 0);
       add_token(values + kRowPlus8, 1);
@@ -439,7 +450,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
 
   // ------------------------------ CTA merge -------------------------------
   // Barrier: every slot has been read, so the ring is free for the merge.
-  wait_copies(0);
+  wait_all_copies();
   __syncthreads();
   float* merge = reinterpret_cast<float*>(smem);  // [8 warps][3 heads][128]
   {
