@@ -196,6 +196,31 @@ int qf_splitk_reduce(const float* partial_out, const float* partial_max,
  * (custom_kernels/paged_decode_native_grouped.py:30-88).  `out` is required. */
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream);
 
+/* The same computation as qf_grouped_splitk_decode_attention, for callers that
+ * cannot provide (or allocate) the split-K partial buffers.  No counterpart in
+ * the reference: its wrappers always allocate partials with torch.  Meant for
+ * hosts without a caching allocator (a C++ serving loop bound straight to this
+ * ABI, where a cudaMalloc/cudaFree per decode step would synchronise the device)
+ * and for processes that gave all device memory to their own allocator at start,
+ * where a later cudaMalloc fails.
+ *   - args->partial_out / partial_max / partial_sum are IGNORED; the partials
+ *     live in a static device array of QF_STATIC_SCRATCH_BYTES that every GPU
+ *     loading this library holds until the process exits.  q, pools, tables and
+ *     `out` are still the caller's.
+ *   - Limit: batch * split_k * q_heads * (head_dim + 2) * 4 bytes must fit; a
+ *     larger request returns QF_EINVAL with the numbers in qf_last_error().
+ *   - The call allocates nothing (no cudaMalloc, cudaFree or allocating library
+ *     routine).  The FIRST call on each device looks up the array's device
+ *     address (cudaGetSymbolAddress, with that device current): make that first
+ *     call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps the previous
+ *     call's contents.  Nothing in it needs clearing (the partial pass rewrites
+ *     every row the combine reads), but two calls whose kernels overlap on the
+ *     GPU (different streams, or several host threads) race on it: keep them on
+ *     one stream or order them with events. */
+#define QF_STATIC_SCRATCH_BYTES (16u << 20)
+int qf_grouped_splitk_decode_attention_static(const qf_decode_attention_args* args, void* stream);
+
 /* Compiled resources and occupancy of the fast partial kernel for `dtype` /
  * `kv_fp8` on `device`.  Replaces grouped_gqa_splitk_diagnostics
  * (native_grouped_decode.cu:310-327).  Fills

@@ -36,6 +36,7 @@ _EXPORTS = {
     "packed_qkv_rope_cache": "packed_qkv_rope_cache",
     "grouped_splitk_decode_attention": "paged_decode_grouped_splitk",
     "splitk_reduce": "paged_decode_grouped_splitk",
+    "grouped_splitk_decode_attention_static": "paged_decode_grouped_splitk",
     "native_grouped_splitk_decode_attention": "paged_decode_native_grouped",
     "native_grouped_decode_diagnostics": "paged_decode_native_grouped",
     "native_grouped_stage_cycles": "paged_decode_native_grouped",

@@ -31,7 +31,9 @@ EXPORTED_SYMBOLS = (
     "qf_quantize_kv_pages_e4m3", "qf_grouped_gqa_splitk_partial_out", "qf_splitk_reduce",
     "qf_grouped_splitk_decode_attention", "qf_grouped_gqa_splitk_diagnostics",
     "qf_grouped_gqa_splitk_profile_out", "qf_device_status", "qf_set_tuning",
+    "qf_grouped_splitk_decode_attention_static",
 )
+STATIC_SCRATCH_BYTES = 16 << 20
 
 
 class RopeKvWriteArgs(Structure):
@@ -113,6 +115,7 @@ def library():
     lib.qf_grouped_gqa_splitk_partial_out.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
     lib.qf_grouped_gqa_splitk_profile_out.argtypes = [POINTER(DecodeAttentionArgs), c_void_p, c_void_p]
     lib.qf_grouped_splitk_decode_attention.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
+    lib.qf_grouped_splitk_decode_attention_static.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
     lib.qf_splitk_reduce.argtypes = (
         [c_void_p] * 3 + [c_int64] * 7 + [c_void_p] + [c_int64] * 3 + [c_int32] * 5 + [c_void_p])
     lib.qf_grouped_gqa_splitk_diagnostics.argtypes = [c_int32, c_int32, c_int32, POINTER(c_int64)]

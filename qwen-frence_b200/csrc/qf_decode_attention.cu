@@ -486,3 +486,68 @@ int qf_set_tuning(int32_t stages, int32_t force_generic) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Split-K attention whose partial buffers live in a static device array.
+//
+// Some hosts of this library cannot hand it scratch memory: a C++ serving loop
+// that binds the C ABI directly has no caching allocator to draw the partial
+// buffers from, and a raw cudaMalloc / cudaFree per decode step synchronises
+// the device and stalls the step; other processes give all device memory to
+// their own allocator up front, so a later cudaMalloc simply fails.  For them
+// the partials of this one entry point come from the array below, which every
+// GPU that loads the library holds (kStaticScratchBytes) until the process ends.
+// ---------------------------------------------------------------------------
+namespace qf {
+namespace {
+
+constexpr size_t kStaticScratchBytes = QF_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device
+// address: the address is looked up once per device, with that device current.
+int static_scratch_on_current_device(float** out) {
+  static std::mutex mutex;
+  static void* resolved[64] = {};
+  int device = 0;
+  QF_CUDA(cudaGetDevice(&device));
+  QF_REQUIRE(device >= 0 && device < 64, "device ordinal %d is out of range", device);
+  std::lock_guard<std::mutex> lock(mutex);
+  if (resolved[device] == nullptr) {
+    void* address = nullptr;
+    QF_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
+    QF_REQUIRE(address != nullptr, "the static scratch array has no device address");
+    resolved[device] = address;
+  }
+  *out = static_cast<float*>(resolved[device]);
+  return QF_OK;
+}
+
+}  // namespace
+}  // namespace qf
+
+extern "C" int qf_grouped_splitk_decode_attention_static(const qf_decode_attention_args* args,
+                                                         void* stream) {
+  QF_REQUIRE(args != nullptr, "args must not be null");
+  QF_REQUIRE(args->batch >= 0 && args->split_k >= 1 && args->q_heads >= 1 && args->head_dim >= 1,
+             "invalid batch, split or head counts");
+  const unsigned long long rows = static_cast<unsigned long long>(args->batch) *
+                                  static_cast<unsigned long long>(args->split_k) *
+                                  static_cast<unsigned long long>(args->q_heads);
+  const unsigned long long needed = rows * (static_cast<unsigned long long>(args->head_dim) + 2ull) * sizeof(float);
+  QF_REQUIRE(needed <= qf::kStaticScratchBytes,
+             "batch * split_k * q_heads * (head_dim + 2) fp32 partials need %llu bytes; the static scratch "
+             "holds %llu (QF_STATIC_SCRATCH_BYTES): lower split_k or pass your own buffers to "
+             "qf_grouped_splitk_decode_attention",
+             needed, static_cast<unsigned long long>(qf::kStaticScratchBytes));
+  float* scratch = nullptr;
+  const int rc = qf::static_scratch_on_current_device(&scratch);
+  if (rc != QF_OK) return rc;
+  // Every (sequence, split, head) row of the three partial tensors is written by the
+  // partial pass before the combine reads it, so nothing has to start at zero.
+  qf_decode_attention_args local = *args;
+  local.partial_out = scratch;
+  local.partial_max = scratch + rows * static_cast<unsigned long long>(args->head_dim);
+  local.partial_sum = local.partial_max + rows;
+  return qf_grouped_splitk_decode_attention(&local, stream);
+}

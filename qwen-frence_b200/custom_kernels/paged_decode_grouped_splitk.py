@@ -206,3 +206,47 @@ def grouped_splitk_decode_attention(
                                    partials=(partial_out, partial_max, partial_sum), out=out)
         cabi.check(lib.qf_grouped_splitk_decode_attention(ctypes.byref(args), stream))
     return out
+
+
+def grouped_splitk_decode_attention_static(q, k_pool, v_pool, block_table, seq_lens, out, *,
+                                           split_k, scale=None):
+    """Split-K decode attention whose partial buffers come from the library's static
+    device array instead of an allocation.
+
+    For hosts that cannot allocate per call: a serving loop without a caching
+    allocator (a raw cudaMalloc per decode step synchronises the device), or a
+    process whose device memory was all handed to another allocator at start.  The
+    caller passes the inputs and `out` (B, heads, D, q's dtype); this wrapper and
+    the C entry point allocate nothing.  Limit: batch * split_k * heads * (D + 2)
+    fp32 values must fit in 16 MiB, else RuntimeError.  The first call on a device
+    resolves the array's address and should be made before any stream capture;
+    calls that overlap on the GPU share the array and race.  No counterpart in the
+    reference.
+    """
+    import ctypes
+
+    import torch
+
+    _require(q.ndim == 3 and k_pool.ndim == 4 and k_pool.shape == v_pool.shape,
+             "expected Q rank three and matching rank-four K/V pools")
+    _require(out.shape == q.shape and out.dtype == q.dtype and out.device == q.device,
+             "out must match q in shape, dtype and device")
+    _require(q.dtype in (torch.float16, torch.bfloat16) and k_pool.dtype == q.dtype
+             and v_pool.dtype == q.dtype, "Q/K/V must share float16 or bfloat16")
+    _require(block_table.ndim == 2 and seq_lens.ndim == 1 and block_table.shape[0] == q.shape[0]
+             and seq_lens.numel() == q.shape[0], "batch dimensions must match")
+    _require(all(t.dtype in (torch.int32, torch.int64) for t in (block_table, seq_lens)),
+             "page table and lengths must use integer tensors")
+    _require(isinstance(split_k, int) and not isinstance(split_k, bool) and split_k >= 1,
+             "split_k must be a positive integer")
+    _require(all(t.is_cuda and t.device == q.device for t in (k_pool, v_pool, block_table, seq_lens)),
+             "all inputs must share one CUDA device")
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    cabi = _cabi()
+    args = fill_attention_args(cabi, q, k_pool, v_pool, block_table, seq_lens, split_k=split_k,
+                               scale=scale, partials=None, out=out)
+    with cabi.device_of(q):
+        cabi.check(cabi.library().qf_grouped_splitk_decode_attention_static(
+            ctypes.byref(args), cabi.stream_pointer(q.device)))
+    return out
