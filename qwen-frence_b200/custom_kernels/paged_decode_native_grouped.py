@@ -166,7 +166,7 @@ def native_grouped_stage_cycles(
     """Run the instrumented partial once and return per-CTA stage cycles.
 
     Returns int64 [B, Hkv, split_k, 4]: clock64() cycles one warp of each CTA
-    spent {waiting for pages, in QK + softmax + PV, 0, 0} (this kernel
+    spent {waiting for pages, in the whole page loop, 0, 0} (this kernel
     overlaps loading with math, so there is no separate load or PV stage).
     Mirrors custom_kernels/paged_decode_native_grouped.py:96-119.
     """
