@@ -181,34 +181,69 @@ struct ReduceParams {
   int q_heads, head_dim, split_k;
 };
 
+constexpr int kReduceChunk = 256;  // partitions whose weights are staged at a time
+
 template <typename T>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
+  __shared__ float s_weight[kReduceChunk];   // exp(offset_k - top), 0 for an empty partition
+  __shared__ float s_red[8];
+  __shared__ float s_top;
   const int sequence = blockIdx.x / p.q_heads;
   const int head = blockIdx.x - sequence * p.q_heads;
-  const int d = threadIdx.x;
-  if (d >= p.head_dim) return;
+  const int tid = threadIdx.x;
   const float* pm = p.pm + sequence * p.pm_sb + head * p.pm_sh;
   const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
-  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + d * p.po_sd;
+  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + tid * p.po_sd;
 
-  // Pass 1: the largest offset among non-empty partitions (broadcast loads).
+  // Pass 1: the largest offset among non-empty partitions; every thread takes a
+  // strided share of the partitions, so the loads are issued together.
   float top = -INFINITY;
-  for (int k = 0; k < p.split_k; ++k) {
+  for (int k = tid; k < p.split_k; k += blockDim.x) {
     if (ps[k * p.pm_sk] > 0.f) top = fmaxf(top, pm[k * p.pm_sk]);
   }
-  // Pass 2: independent loads, one exp per partition.
-  float acc = 0.f, total = 0.f;
-#pragma unroll 4
-  for (int k = 0; k < p.split_k; ++k) {
-    const float sum = ps[k * p.pm_sk];
-    if (sum > 0.f) {
-      const float w = expf(pm[k * p.pm_sk] - top);
-      acc += po[k * p.po_sk] * w;
-      total += sum * w;
-    }
+  for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+  if ((tid & 31) == 0) s_red[tid >> 5] = top;
+  __syncthreads();
+  if (tid == 0) {
+    float m = -INFINITY;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, s_red[w]);
+    s_top = m;
   }
-  const float result = acc / (total > 0.f ? total : 1.f);
-  static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + d * p.o_sd] = from_float<T>(result);
+  __syncthreads();
+  top = s_top;
+
+  // Pass 2: weights of a chunk of partitions go to shared memory (one exp per
+  // partition, computed in parallel), then every thread accumulates its head
+  // dimension over the chunk with independent loads.
+  float acc = 0.f, total = 0.f;
+  for (int first = 0; first < p.split_k; first += kReduceChunk) {
+    const int count = min(kReduceChunk, p.split_k - first);
+    for (int k = tid; k < count; k += blockDim.x) {
+      const float sum = ps[(first + k) * p.pm_sk];
+      s_weight[k] = sum > 0.f ? expf(pm[(first + k) * p.pm_sk] - top) : 0.f;
+    }
+    __syncthreads();
+    if (tid < p.head_dim) {
+#pragma unroll 4
+      for (int k = 0; k < count; ++k) {
+        const float w = s_weight[k];
+        if (w != 0.f) acc += po[(first + k) * p.po_sk] * w;
+      }
+    }
+    if (tid == 0) {
+      for (int k = 0; k < count; ++k) {
+        const float w = s_weight[k];
+        if (w != 0.f) total += ps[(first + k) * p.pm_sk] * w;
+      }
+      s_red[0] = total;
+    }
+    __syncthreads();
+  }
+  total = s_red[0];
+  if (tid < p.head_dim) {
+    const float result = acc / (total > 0.f ? total : 1.f);
+    static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + tid * p.o_sd] = from_float<T>(result);
+  }
 }
 
 // ---------------------------------------------------------------------------

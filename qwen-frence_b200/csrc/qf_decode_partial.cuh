@@ -187,6 +187,8 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   __shared__ float cta_sum[QF_GQA_GROUP];
 
   constexpr unsigned kFull = 0xffffffffu;
+  long long t_entry = 0;
+  if (PROFILE) t_entry = clock64();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -271,7 +273,6 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     table_next += 2 * table_step;
     pages_left -= 2;
   };
-  fetch_ids();
   int pairs_to_issue = num_pairs;
   int fill_slot = 0;
   auto issue_pair = [&]() {
@@ -285,8 +286,28 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     commit_copies();  // always, so that group counting stays uniform
     fill_slot = (fill_slot + 1) & (kSlots - 1);
   };
+  {
+    // Prologue: the ids of the first kDepth + 1 pairs are read in ONE round trip
+    // (independent loads), then the first kDepth pairs are put in flight.
+    int first_ids[2 * kDepth + 2];
 #pragma unroll
-  for (int i = 0; i < kDepth; ++i) issue_pair();
+    for (int i = 0; i < 2 * kDepth + 2; ++i) first_ids[i] = read_id(table_first + i * table_step, i < num_pages_here);
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i) {
+      if (i < num_pairs) {
+        unsigned char* dst = smem + i * Traits::kSlotBytes + fill_offset;
+        copy_page(dst, first_ids[2 * i]);
+        copy_page(dst + Traits::kTileBytes, first_ids[2 * i + 1]);
+      }
+      commit_copies();
+    }
+    fill_slot = kDepth & (kSlots - 1);
+    pairs_to_issue = max(num_pairs - kDepth, 0);
+    next_id_a = first_ids[2 * kDepth];
+    next_id_b = first_ids[2 * kDepth + 1];
+    table_next = table_first + (2 * kDepth + 2) * table_step;
+    pages_left = num_pages_here - (2 * kDepth + 2);
+  }
 
   // ---- per-thread state: 3 heads x 8 dims of Q (pre-scaled) and of the output ----
   float2 q2[kHeadsPerThread][4];
@@ -442,11 +463,8 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       if (token_base + QF_PAGE_SIZE + 8 < tokens_here) add_token(values + Traits::kTileBytes + kRowPlus8, 3);
     }
   }
-  if (PROFILE && p.cycles != nullptr && tid == 32) {
-    // One warp per CTA reports {waiting for pages, whole loop, 0, 0}.
-    long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;
-    dst[0] = t_wait, dst[1] = clock64() - t_total, dst[2] = 0, dst[3] = 0;
-  }
+  long long t_loop_end = 0;
+  if (PROFILE) t_loop_end = clock64();
 
   // ------------------------------ CTA merge -------------------------------
   // Barrier: every slot has been read, so the ring is free for the merge.
@@ -519,6 +537,11 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     // natural-log units, as the combine and the reference's reduce expect
     p.partial_max[partial_row + tid] = cta_offset[tid] * kLn2;
     p.partial_sum[partial_row + tid] = cta_sum[tid];
+  }
+  if (PROFILE && p.cycles != nullptr && tid == 32) {
+    // One warp per CTA reports {waiting for pages, page loop, set-up before it, merge after it}.
+    long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;
+    dst[0] = t_wait, dst[1] = t_loop_end - t_total, dst[2] = t_total - t_entry, dst[3] = clock64() - t_loop_end;
   }
 }
 
