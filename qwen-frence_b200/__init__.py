@@ -13,6 +13,7 @@ current torch stream; none has a CPU fallback):
     packed_qkv_rope_cache                                  custom_kernels/packed_qkv_rope_cache.py
     grouped_splitk_decode_attention, splitk_reduce         custom_kernels/paged_decode_grouped_splitk.py
     native_grouped_splitk_decode_attention,
+    grouped_gqa_splitk_partial_out,
     native_grouped_decode_diagnostics,
     native_grouped_stage_cycles                            custom_kernels/paged_decode_native_grouped.py
     quantize_kv_pool_e4m3, dequantize_kv_pool_e4m3,
@@ -38,6 +39,7 @@ _EXPORTS = {
     "splitk_reduce": "paged_decode_grouped_splitk",
     "grouped_splitk_decode_attention_static": "paged_decode_grouped_splitk",
     "native_grouped_splitk_decode_attention": "paged_decode_native_grouped",
+    "grouped_gqa_splitk_partial_out": "paged_decode_native_grouped",
     "native_grouped_decode_diagnostics": "paged_decode_native_grouped",
     "native_grouped_stage_cycles": "paged_decode_native_grouped",
     "quantize_kv_pool_e4m3": "fp8_paged_kv",

@@ -199,4 +199,8 @@ def device_status(reset=True):
 
 
 def set_tuning(stages=0, force_generic=False):
-    check(library().qf_set_tuning(int(stages), 1 if force_generic else 0))
+    """Kernel selection for tests: force_generic 1 (or True) sends every launch to the
+    stride-generic kernel, 2 keeps the fast per-partition kernel but turns the
+    persistent one off, 3 uses the persistent one whenever the layout allows (also
+    for batches with few split slots); 0 restores the defaults."""
+    check(library().qf_set_tuning(int(stages), int(force_generic)))

@@ -1,8 +1,10 @@
 // GQA paged decode attention over block tables: split-K partial pass, combine,
 // and the host entry points.
 //
-// The fast partial kernel (sm_100a, cp.async ring, Qwen geometry) lives in
-// qf_decode_partial.cuh.
+// The fast partial kernels (sm_100a, cp.async ring, Qwen geometry) live in
+// qf_decode_partial.cuh (one CTA per partition, the reference's balanced
+// partitions) and qf_decode_stream.cuh (persistent CTAs that share the batch's
+// pages equally; what the fused attention entry point runs).
 //
 // A stride-generic kernel covers every other layout and geometry the
 // reference accepts (custom_kernels/paged_decode_grouped_splitk.py:228-334):
@@ -12,6 +14,7 @@
 
 #include "qf_common.cuh"
 #include "qf_decode_partial.cuh"
+#include "qf_decode_stream.cuh"
 
 namespace qf {
 namespace {
@@ -179,14 +182,22 @@ struct ReduceParams {
   void* out;
   int64_t o_sb, o_sh, o_sd;
   int q_heads, head_dim, split_k;
+  // Only for partials written by the streamed kernel:
+  const void* seq_lens;
+  int64_t lens_stride;
+  int lens_dtype;
 };
 
 constexpr int kReduceChunk = 256;  // partitions whose weights are staged at a time
 
-template <typename T>
+// STREAMED: the partials come from decode_stream_kernel.  A sequence then fills
+// only its first few split slots, the slot after the last one holds sum = -1
+// (unless all slots are used), and a sequence without tokens has no slot at all.
+template <typename T, bool STREAMED>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
   __shared__ float s_weight[kReduceChunk];   // exp(offset_k - top), 0 for an empty partition
   __shared__ float s_red[8];
+  __shared__ int s_first[8];
   __shared__ float s_top;
   const int sequence = blockIdx.x / p.q_heads;
   const int head = blockIdx.x - sequence * p.q_heads;
@@ -195,10 +206,28 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
   const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
   const float* po = p.po + sequence * p.po_sb + head * p.po_sh + tid * p.po_sd;
 
+  int split_k = p.split_k;
+  if (STREAMED) {
+    if (load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) <= 0) {
+      if (tid < p.head_dim) {
+        static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + tid * p.o_sd] = from_float<T>(0.f);
+      }
+      return;
+    }
+    int first = p.split_k;  // the first slot marked "no further pieces"
+    for (int k = tid; k < p.split_k; k += blockDim.x) {
+      if (ps[k * p.pm_sk] < 0.f) first = min(first, k);
+    }
+    for (int off = 16; off > 0; off >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, off));
+    if ((tid & 31) == 0) s_first[tid >> 5] = first;
+    __syncthreads();
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) split_k = min(split_k, s_first[w]);
+  }
+
   // Pass 1: the largest offset among non-empty partitions; every thread takes a
   // strided share of the partitions, so the loads are issued together.
   float top = -INFINITY;
-  for (int k = tid; k < p.split_k; k += blockDim.x) {
+  for (int k = tid; k < split_k; k += blockDim.x) {
     if (ps[k * p.pm_sk] > 0.f) top = fmaxf(top, pm[k * p.pm_sk]);
   }
   for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
@@ -216,8 +245,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
   // partition, computed in parallel), then every thread accumulates its head
   // dimension over the chunk with independent loads.
   float acc = 0.f, total = 0.f;
-  for (int first = 0; first < p.split_k; first += kReduceChunk) {
-    const int count = min(kReduceChunk, p.split_k - first);
+  for (int first = 0; first < split_k; first += kReduceChunk) {
+    const int count = min(kReduceChunk, split_k - first);
     for (int k = tid; k < count; k += blockDim.x) {
       const float sum = ps[(first + k) * p.pm_sk];
       s_weight[k] = sum > 0.f ? expf(pm[(first + k) * p.pm_sk] - top) : 0.f;
@@ -277,6 +306,39 @@ int launch_fast(const FastParams& p, cudaStream_t stream) {
   return QF_OK;
 }
 
+// Resident CTAs of the streamed kernel on the current device: two per SM.
+int stream_ctas_on_current_device() {
+  static std::mutex mutex;
+  static int cache[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cache[device] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    cache[device] = sms * QF_MIN_CTAS;
+  }
+  return cache[device];
+}
+
+size_t stream_smem_bytes(bool fp8) {
+  return static_cast<size_t>(kSlots) * (fp8 ? 8192 : 16384) + kMergeFloats * sizeof(float);
+}
+
+template <typename T, bool FP8>
+int launch_stream(const FastParams& p, cudaStream_t stream) {
+  auto kernel = decode_stream_kernel<T, FP8>;
+  const size_t smem = stream_smem_bytes(FP8);
+  QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  const int resident = stream_ctas_on_current_device();
+  QF_REQUIRE(resident >= p.kv_heads, "could not size the streamed kernel for this device");
+  StreamParams sp{p, resident / p.kv_heads};
+  kernel<<<static_cast<unsigned>(sp.ctas_per_head * p.kv_heads), kFastThreads, smem, stream>>>(sp);
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
 int validate(const qf_decode_attention_args* a, bool need_out) {
@@ -310,7 +372,7 @@ int validate(const qf_decode_attention_args* a, bool need_out) {
 }
 
 bool fast_path_ok(const qf_decode_attention_args* a) {
-  if (g_force_generic) return false;
+  if (g_force_generic == 1) return false;
   if (a->head_dim != QF_HEAD_DIM || a->page_size != QF_PAGE_SIZE) return false;
   if (a->q_heads != a->kv_heads * QF_GQA_GROUP) return false;
   if (a->num_pages < 1 || a->kv_heads > 65535) return false;
@@ -326,6 +388,59 @@ bool fast_path_ok(const qf_decode_attention_args* a) {
   return true;
 }
 
+FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* cycles, int* status) {
+  FastParams p{};
+  p.q = a->q, p.q_sb = a->q_stride_b, p.q_sh = a->q_stride_h;
+  const int64_t elem = a->kv_fp8 ? 1 : 2;
+  p.k_pool = static_cast<const unsigned char*>(a->k_pool);
+  p.v_pool = static_cast<const unsigned char*>(a->v_pool);
+  p.k_page_bytes = a->k_stride_page * elem, p.k_tok_bytes = a->k_stride_tok * elem;
+  p.k_head_bytes = a->k_stride_head * elem;
+  p.v_page_bytes = a->v_stride_page * elem, p.v_tok_bytes = a->v_stride_tok * elem;
+  p.v_head_bytes = a->v_stride_head * elem;
+  p.block_table = a->block_table, p.bt_sb = a->table_stride_b, p.bt_sp = a->table_stride_p;
+  p.seq_lens = a->seq_lens, p.lens_stride = a->lens_stride;
+  p.k_scale = a->k_scale, p.v_scale = a->v_scale;
+  p.partial_out = a->partial_out, p.partial_max = a->partial_max, p.partial_sum = a->partial_sum;
+  p.out = out, p.o_sb = a->o_stride_b, p.o_sh = a->o_stride_h, p.o_sd = a->o_stride_d;
+  p.num_pages = a->num_pages;
+  p.cycles = cycles;
+  p.status = status;
+  p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
+  p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
+  p.scale_log2 = a->scale * kLog2e;
+  return p;
+}
+
+// The streamed kernel serves the fused attention entry point when the layout is
+// the fast one, the batch's prefix fits in its shared memory, and the split slots
+// cannot become the limit: a sequence may be cut into at most split_k pieces, so
+// a CTA's share is at least longest / (split_k - 1) pairs, and with few sequences
+// and few slots that would leave most resident CTAs without work.  The lengths
+// live on the device, so the test uses what the host knows: batch * (split_k - 1)
+// slots per KV head against twice the resident CTAs per KV head.
+bool stream_path_ok(const qf_decode_attention_args* a) {
+  if ((g_force_generic != 0 && g_force_generic != 3) || !fast_path_ok(a) || a->split_k < 2) return false;
+  if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return false;
+  const int resident = stream_ctas_on_current_device();
+  if (resident < a->kv_heads) return false;
+  if (g_force_generic == 3) return true;  // tests: the streamed kernel whatever the slot count
+  const int64_t per_head = resident / a->kv_heads;
+  return static_cast<int64_t>(a->batch) * (a->split_k - 1) >= 2 * per_head;
+}
+
+int launch_streamed_partial(const qf_decode_attention_args* a, cudaStream_t stream) {
+  int* status = status_word_for_current_device();
+  QF_REQUIRE(status != nullptr, "could not resolve the device status word");
+  const FastParams p = fast_params(a, nullptr, nullptr, status);
+  if (a->kv_fp8) {
+    return a->dtype == QF_DTYPE_F16 ? launch_stream<__half, true>(p, stream)
+                                    : launch_stream<__nv_bfloat16, true>(p, stream);
+  }
+  return a->dtype == QF_DTYPE_F16 ? launch_stream<__half, false>(p, stream)
+                                  : launch_stream<__nv_bfloat16, false>(p, stream);
+}
+
 template <bool PROFILE>
 int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long* cycles,
                    cudaStream_t stream) {
@@ -335,26 +450,7 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
   void* out = direct_out ? a->out : nullptr;
 
   if (fast_path_ok(a)) {
-    FastParams p{};
-    p.q = a->q, p.q_sb = a->q_stride_b, p.q_sh = a->q_stride_h;
-    const int64_t elem = a->kv_fp8 ? 1 : 2;
-    p.k_pool = static_cast<const unsigned char*>(a->k_pool);
-    p.v_pool = static_cast<const unsigned char*>(a->v_pool);
-    p.k_page_bytes = a->k_stride_page * elem, p.k_tok_bytes = a->k_stride_tok * elem;
-    p.k_head_bytes = a->k_stride_head * elem;
-    p.v_page_bytes = a->v_stride_page * elem, p.v_tok_bytes = a->v_stride_tok * elem;
-    p.v_head_bytes = a->v_stride_head * elem;
-    p.block_table = a->block_table, p.bt_sb = a->table_stride_b, p.bt_sp = a->table_stride_p;
-    p.seq_lens = a->seq_lens, p.lens_stride = a->lens_stride;
-    p.k_scale = a->k_scale, p.v_scale = a->v_scale;
-    p.partial_out = a->partial_out, p.partial_max = a->partial_max, p.partial_sum = a->partial_sum;
-    p.out = out, p.o_sb = a->o_stride_b, p.o_sh = a->o_stride_h, p.o_sd = a->o_stride_d;
-    p.num_pages = a->num_pages;
-    p.cycles = cycles;
-    p.status = status;
-    p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
-    p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
-    p.scale_log2 = a->scale * kLog2e;
+    const FastParams p = fast_params(a, out, cycles, status);
     if (a->kv_fp8) {
       return a->dtype == QF_DTYPE_F16
                  ? launch_fast<__half, true, PROFILE>(p, stream)
@@ -398,14 +494,20 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
   return QF_OK;
 }
 
-int launch_reduce(const ReduceParams& r, int batch, int dtype, cudaStream_t stream) {
+int launch_reduce(const ReduceParams& r, int batch, int dtype, bool streamed, cudaStream_t stream) {
   if (batch == 0) return QF_OK;
   const unsigned blocks = static_cast<unsigned>(static_cast<int64_t>(batch) * r.q_heads);
   const int threads = ((r.head_dim + 31) / 32) * 32;
-  if (dtype == QF_DTYPE_F16)
-    splitk_reduce_kernel<__half><<<blocks, threads, 0, stream>>>(r);
-  else
-    splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(r);
+  if (streamed) {
+    if (dtype == QF_DTYPE_F16)
+      splitk_reduce_kernel<__half, true><<<blocks, threads, 0, stream>>>(r);
+    else
+      splitk_reduce_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(r);
+  } else if (dtype == QF_DTYPE_F16) {
+    splitk_reduce_kernel<__half, false><<<blocks, threads, 0, stream>>>(r);
+  } else {
+    splitk_reduce_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(r);
+  }
   QF_CUDA(cudaGetLastError());
   return QF_OK;
 }
@@ -449,7 +551,7 @@ int qf_splitk_reduce(const float* partial_out, const float* partial_max, const f
   r.pm_sb = pm_stride_b, r.pm_sk = pm_stride_k, r.pm_sh = pm_stride_h;
   r.out = out, r.o_sb = o_stride_b, r.o_sh = o_stride_h, r.o_sd = o_stride_d;
   r.q_heads = q_heads, r.head_dim = head_dim, r.split_k = split_k;
-  return qf::launch_reduce(r, batch, dtype, static_cast<cudaStream_t>(stream));
+  return qf::launch_reduce(r, batch, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {
@@ -457,7 +559,9 @@ int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, voi
   if (rc != QF_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (args->split_k == 1) return qf::launch_partial<false>(args, true, nullptr, s);
-  rc = qf::launch_partial<false>(args, false, nullptr, s);
+  if (args->batch == 0) return QF_OK;
+  const bool streamed = qf::stream_path_ok(args);
+  rc = streamed ? qf::launch_streamed_partial(args, s) : qf::launch_partial<false>(args, false, nullptr, s);
   if (rc != QF_OK) return rc;
   qf::ReduceParams r{};
   r.po = args->partial_out, r.pm = args->partial_max, r.ps = args->partial_sum;
@@ -466,7 +570,8 @@ int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, voi
   r.pm_sb = k * hq, r.pm_sk = hq, r.pm_sh = 1;
   r.out = args->out, r.o_sb = args->o_stride_b, r.o_sh = args->o_stride_h, r.o_sd = args->o_stride_d;
   r.q_heads = args->q_heads, r.head_dim = args->head_dim, r.split_k = args->split_k;
-  return qf::launch_reduce(r, args->batch, args->dtype, s);
+  r.seq_lens = args->seq_lens, r.lens_stride = args->lens_stride, r.lens_dtype = args->lens_dtype;
+  return qf::launch_reduce(r, args->batch, args->dtype, streamed, s);
 }
 
 int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_fp8, int64_t* info) {
@@ -515,8 +620,9 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 
 int qf_set_tuning(int32_t stages, int32_t force_generic) {
   QF_REQUIRE(stages >= 0 && stages <= 64, "stages must be in [0, 64]");
+  QF_REQUIRE(force_generic >= 0 && force_generic <= 3, "force_generic must be in [0, 3]");
   qf::g_tuned_stages = stages;
-  qf::g_force_generic = force_generic ? 1 : 0;
+  qf::g_force_generic = force_generic;
   return QF_OK;
 }
 

@@ -171,6 +171,209 @@ __device__ __forceinline__ float reduce_scatter12(const float (&v)[12], int sub)
 __device__ __forceinline__ constexpr int head_lane(int h) { return h == 0 ? 0 : h == 1 ? 2 : 1; }
 
 
+// What a lane does inside its 16-lane group, fixed for the kernel's lifetime.
+template <typename T, bool FP8>
+struct LaneRole {
+  int sub;        // dim chunk, and lane within the 16-lane group
+  int row;        // token rows `row` and `row + 8` of a page
+  int my_token;   // after the reduce-scatter this lane owns one (token, head):
+  int my_head;    //   token 0: (page A, row)  1: (A, row+8)  2: (B, row)  3: (B, row+8)
+  int keep_page, send_page;  // byte offsets, inside a slot's K region, of the page / row
+  int keep_row, send_row;    //   this lane keeps and sends in the reduce-scatter
+  __device__ __forceinline__ LaneRole(int sub_, int row_) : sub(sub_), row(row_) {
+    using Traits = TileTraits<T, FP8>;
+    constexpr int kRowPlus8 = 8 * 16 * Traits::kChunkBytes;
+    my_token = ((sub >> 3) & 1) * 2 + ((sub >> 2) & 1);
+    my_head = (sub & 1) ? 2 : ((sub >> 1) & 1);
+    keep_page = (sub & 8) ? Traits::kTileBytes : 0, send_page = Traits::kTileBytes - keep_page;
+    keep_row = (sub & 4) ? kRowPlus8 : 0, send_row = kRowPlus8 - keep_row;
+  }
+};
+
+// One page pair (A, B) = four tokens per thread: scores of 3 heads x 4 tokens,
+// online softmax with the lazily moving offset, probabilities through shared
+// memory, accumulate p * V.  `slot` points at this thread's chunk of token row
+// `row` in the pair's K(A) tile; `token_base` is the index, counted from the first
+// token of the range `tokens_here` is measured in, of token 0; a token exists iff
+// its index is below `tokens_here`, and `all_valid` promises that all 32 do.
+template <typename T, bool FP8>
+__device__ __forceinline__ void attend_pair(const unsigned char* slot, float2* probs,
+                                            const LaneRole<T, FP8>& role,
+                                            const float2 (&q2)[kHeadsPerThread][4],
+                                            float2 (&acc)[kHeadsPerThread][4], float& my_offset,
+                                            float& my_sum, bool all_valid, int token_base,
+                                            int tokens_here, float k_mul, float v_mul) {
+  using Traits = TileTraits<T, FP8>;
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kRowPlus8 = 8 * 16 * Traits::kChunkBytes;
+  // ---- scores: q . k for 3 heads x 4 tokens over this thread's 8 dims ----
+  float dots[12];
+  auto score_token = [&](const unsigned char* at, int base) {
+    float2 kreg[4];
+    to_pairs<T, FP8>(load_raw<FP8>(at), kreg);
+#pragma unroll
+    for (int h = 0; h < kHeadsPerThread; ++h) {
+      float2 d = __fmul2_rn(q2[h][0], kreg[0]);
+#pragma unroll
+      for (int j = 1; j < 4; ++j) d = __ffma2_rn(q2[h][j], kreg[j], d);
+      dots[base + h] = d.x + d.y;
+    }
+  };
+  // lane-dependent order: kept page / kept row first (see reduce_scatter12)
+  score_token(slot + role.keep_page + role.keep_row, 0);
+  score_token(slot + role.keep_page + role.send_row, 3);
+  score_token(slot + role.send_page + role.keep_row, 6);
+  score_token(slot + role.send_page + role.send_row, 9);
+  float score = reduce_scatter12(dots, role.sub);
+  bool my_valid = true;
+  if (FP8) score *= k_mul;
+  if (!all_valid) {
+    my_valid = token_base + (role.my_token >> 1) * QF_PAGE_SIZE + (role.my_token & 1) * 8 < tokens_here;
+    if (!my_valid) score = -INFINITY;
+  }
+
+  // ---- online softmax; the offset of a head is shared by its four token lanes ----
+  const bool grow = score > my_offset + kOffsetSlack;  // also the first valid token (offset -inf)
+  if (__any_sync(kFull, grow)) {
+    float target = fmaxf(my_offset, score);
+    target = fmaxf(target, __shfl_xor_sync(kFull, target, 8));
+    target = fmaxf(target, __shfl_xor_sync(kFull, target, 4));
+    const float corr = my_offset == -INFINITY ? 0.f : fast_exp2(my_offset - target);
+    my_sum *= corr;
+    my_offset = target;
+#pragma unroll
+    for (int h = 0; h < kHeadsPerThread; ++h) {
+      const float ch = __shfl_sync(kFull, corr, head_lane(h), 16);
+      const float2 c2 = make_float2(ch, ch);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[h][j] = __fmul2_rn(acc[h][j], c2);
+    }
+  }
+  float prob = fast_exp2(score - my_offset);
+  if (!all_valid && !my_valid) prob = 0.f;  // also covers offset == -inf (NaN from inf - inf)
+  my_sum += prob;
+  if (FP8) prob *= v_mul;
+
+  // ---- publish the twelve probabilities of this group as (p, p) pairs ----
+  probs[role.my_token * 3 + role.my_head] = make_float2(prob, prob);  // head 2 is written twice, same value
+  __syncwarp();
+
+  // ---- values: acc[h] += p[token][h] * v[token] ----
+  auto add_token = [&](const unsigned char* at, int k) {
+    float2 vreg[4];
+    to_pairs<T, FP8>(load_raw<FP8>(at), vreg);
+#pragma unroll
+    for (int h = 0; h < kHeadsPerThread; ++h) {
+      const float2 p2 = probs[k * 3 + h];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[h][j] = __ffma2_rn(p2, vreg[j], acc[h][j]);
+    }
+  };
+  const unsigned char* values = slot + 2 * Traits::kTileBytes;
+  if (all_valid) {
+    // all four tokens exist (the common case)
+    add_token(values, 0);
+    add_token(values + kRowPlus8, 1);
+    add_token(values + Traits::kTileBytes, 2);
+    add_token(values + Traits::kTileBytes + kRowPlus8, 3);
+  } else {
+    // a token that does not exist may hold anything (NaN included): skip it
+    if (token_base < tokens_here) add_token(values, 0);
+    if (token_base + 8 < tokens_here) add_token(values + kRowPlus8, 1);
+    if (token_base + QF_PAGE_SIZE < tokens_here) add_token(values + Traits::kTileBytes, 2);
+    if (token_base + QF_PAGE_SIZE + 8 < tokens_here) add_token(values + Traits::kTileBytes + kRowPlus8, 3);
+  }
+}
+
+// Shared-memory state of the once-per-partition merge of the sixteen 16-lane groups.
+struct MergeShared {
+  float group_offset[2][kGroupRows][kHeadsPerThread];  // [head group][row][head]
+  float group_sum[2][kGroupRows][kHeadsPerThread];
+  float cta_offset[QF_GQA_GROUP];
+  float cta_sum[QF_GQA_GROUP];
+};
+
+// Merge the per-group (accumulator, offset, sum) states of a CTA and store the
+// result: the unnormalised fp32 partial of the six heads (`partial_out_row`,
+// [6][128]) with its offset in natural-log units and its sum, and / or the
+// normalised output (`out_row`, head stride o_sh, dim stride o_sd).  `merge` is
+// kMergeFloats of shared memory nobody else touches until the call returns.  Every
+// thread of the CTA calls this; it contains three CTA-wide barriers.
+template <typename T>
+__device__ __forceinline__ void merge_and_store(MergeShared& ms, float* merge,
+                                                float2 (&acc)[kHeadsPerThread][4], float my_offset,
+                                                float my_sum, int my_token, int my_head,
+                                                float* partial_out_row, float* partial_max_row,
+                                                float* partial_sum_row, T* out_row, int64_t o_sh,
+                                                int64_t o_sd) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane & 15;
+  const int head_group = warp >> 2;
+  const int row = ((warp & 3) << 1) | (lane >> 4);
+  {
+    // sum of a head over the group's four token streams (lanes differing in bits 3, 2)
+    float total = my_sum + __shfl_xor_sync(kFull, my_sum, 8);
+    total += __shfl_xor_sync(kFull, total, 4);
+    if (my_token == 0 && sub == head_lane(my_head)) {
+      ms.group_offset[head_group][row][my_head] = my_offset;
+      ms.group_sum[head_group][row][my_head] = total;
+    }
+  }
+  __syncthreads();
+  if (tid < QF_GQA_GROUP) {
+    const int g = tid / kHeadsPerThread, h = tid - g * kHeadsPerThread;
+    float m = -INFINITY;
+    for (int r = 0; r < kGroupRows; ++r) m = fmaxf(m, ms.group_offset[g][r][h]);
+    float total = 0.f;
+    for (int r = 0; r < kGroupRows; ++r) {
+      const float mg = ms.group_offset[g][r][h];
+      if (mg != -INFINITY) total += ms.group_sum[g][r][h] * fast_exp2(mg - m);
+    }
+    ms.cta_offset[tid] = m;
+    ms.cta_sum[tid] = total;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < kHeadsPerThread; ++h) {
+    const float mg = ms.group_offset[head_group][row][h];
+    const float f = mg == -INFINITY ? 0.f : fast_exp2(mg - ms.cta_offset[head_group * kHeadsPerThread + h]);
+    const float2 f2 = make_float2(f, f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = __fmul2_rn(acc[h][j], f2);
+      a.x += __shfl_xor_sync(kFull, a.x, 16);
+      a.y += __shfl_xor_sync(kFull, a.y, 16);
+      acc[h][j] = a;
+    }
+    if (lane < 16) {
+      float4* dst =
+          reinterpret_cast<float4*>(merge + (warp * kHeadsPerThread + h) * QF_HEAD_DIM + sub * 8);
+      dst[0] = make_float4(acc[h][0].x, acc[h][0].y, acc[h][1].x, acc[h][1].y);
+      dst[1] = make_float4(acc[h][2].x, acc[h][2].y, acc[h][3].x, acc[h][3].y);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < (QF_GQA_GROUP * QF_HEAD_DIM) / kFastThreads; ++i) {
+    const int e = tid + i * kFastThreads;  // (head, dim) flattened
+    const int head = e >> 7, d = e & 127;
+    const int g = head / kHeadsPerThread, h = head - g * kHeadsPerThread;
+    float value = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) value += merge[((g * 4 + w) * kHeadsPerThread + h) * QF_HEAD_DIM + d];
+    if (partial_out_row != nullptr) partial_out_row[e] = value;
+    if (out_row != nullptr) {
+      const float total = ms.cta_sum[head];
+      out_row[head * o_sh + d * o_sd] = from_float<T>(value / (total > 0.f ? total : 1.f));
+    }
+  }
+  if (tid < QF_GQA_GROUP && partial_max_row != nullptr) {
+    // natural-log units, as the combine and the reference's reduce expect
+    partial_max_row[tid] = ms.cta_offset[tid] * kLn2;
+    partial_sum_row[tid] = ms.cta_sum[tid];
+  }
+}
+
 #ifndef QF_MIN_CTAS
 #define QF_MIN_CTAS 2
 #endif
@@ -181,12 +384,8 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   extern __shared__ __align__(1024) unsigned char smem[];  // ring of page-pair slots; merge scratch later
   // Probabilities of one iteration as (p, p) operands: [parity][warp][half-warp][token*3 + head]
   __shared__ __align__(16) float2 prob_pairs[2][kConsumerWarps][2][12];
-  __shared__ float group_offset[2][kGroupRows][kHeadsPerThread];  // [head group][row][head]
-  __shared__ float group_sum[2][kGroupRows][kHeadsPerThread];
-  __shared__ float cta_offset[QF_GQA_GROUP];
-  __shared__ float cta_sum[QF_GQA_GROUP];
+  __shared__ MergeShared merge_state;
 
-  constexpr unsigned kFull = 0xffffffffu;
   long long t_entry = 0;
   if (PROFILE) t_entry = clock64();
   const int tid = threadIdx.x;
@@ -330,16 +529,11 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       q2[h][3] = __fmul2_rn(unpack2<T>(raw.w), s2);
     }
   }
-  // After the reduce-scatter this lane owns one (token, head) of its group:
-  // token 0: (page A, row)  1: (A, row+8)  2: (B, row)  3: (B, row+8)
-  const int my_token = ((sub >> 3) & 1) * 2 + ((sub >> 2) & 1);
-  const int my_head = (sub & 1) ? 2 : ((sub >> 1) & 1);
+  const LaneRole<T, FP8> role(sub, row);
+  const int my_token = role.my_token, my_head = role.my_head;
   float my_offset = -INFINITY;  // exponent offset of my head, shared by the group (log2 units)
   float my_sum = 0.f;           // sum of p over my token stream
   float2* prob_slot = &prob_pairs[0][warp][lane >> 4][0];
-  // Offsets, inside a slot's K region, of the page / row this lane keeps and sends.
-  const int keep_page = (sub & 8) ? Traits::kTileBytes : 0, send_page = Traits::kTileBytes - keep_page;
-  const int keep_row = (sub & 4) ? kRowPlus8 : 0, send_row = kRowPlus8 - keep_row;
   constexpr int kProbParityStride = kConsumerWarps * 2 * 12;  // float2 elements
 
   // ------------------------------ main loop -------------------------------
@@ -380,88 +574,11 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     const unsigned char* slot = smem + read_slot * Traits::kSlotBytes + chunk_offset;
     read_slot = (read_slot + 1) & (kSlots - 1);
 
-    // ---- scores: q . k for 3 heads x 4 tokens over this thread's 8 dims ----
-    float dots[12];
-    auto score_token = [&](const unsigned char* at, int base) {
-      float2 kreg[4];
-      to_pairs<T, FP8>(load_raw<FP8>(at), kreg);
-#pragma unroll
-      for (int h = 0; h < kHeadsPerThread; ++h) {
-        float2 d = __fmul2_rn(q2[h][0], kreg[0]);
-#pragma unroll
-        for (int j = 1; j < 4; ++j) d = __ffma2_rn(q2[h][j], kreg[j], d);
-        dots[base + h] = d.x + d.y;
-      }
-    };
-    // lane-dependent order: kept page / kept row first (see reduce_scatter12)
-    score_token(slot + keep_page + keep_row, 0);
-    score_token(slot + keep_page + send_row, 3);
-    score_token(slot + send_page + keep_row, 6);
-    score_token(slot + send_page + send_row, 9);
-    float score = reduce_scatter12(dots, sub);
     // Pairs below `full_pairs` hold 32 existing tokens; only the partition's last
     // pair can hold tokens past the sequence end or lack its second page.
-    const bool all_valid = pair < full_pairs;
-    const int token_base = pair * 2 * QF_PAGE_SIZE + row;  // partition-relative index of token 0
-    bool my_valid = true;
-    if (FP8) score *= k_mul;
-    if (!all_valid) {
-      my_valid = token_base + (my_token >> 1) * QF_PAGE_SIZE + (my_token & 1) * 8 < tokens_here;
-      if (!my_valid) score = -INFINITY;
-    }
-
-    // ---- online softmax; the offset of a head is shared by its four token lanes ----
-    const bool grow = score > my_offset + kOffsetSlack;  // also the first valid token (offset -inf)
-    if (__any_sync(kFull, grow)) {
-      float target = fmaxf(my_offset, score);
-      target = fmaxf(target, __shfl_xor_sync(kFull, target, 8));
-      target = fmaxf(target, __shfl_xor_sync(kFull, target, 4));
-      const float corr = my_offset == -INFINITY ? 0.f : fast_exp2(my_offset - target);
-      my_sum *= corr;
-      my_offset = target;
-#pragma unroll
-      for (int h = 0; h < kHeadsPerThread; ++h) {
-        const float ch = __shfl_sync(kFull, corr, head_lane(h), 16);
-        const float2 c2 = make_float2(ch, ch);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[h][j] = __fmul2_rn(acc[h][j], c2);
-      }
-    }
-    float prob = fast_exp2(score - my_offset);
-    if (!all_valid && !my_valid) prob = 0.f;  // also covers offset == -inf (NaN from inf - inf)
-    my_sum += prob;
-    if (FP8) prob *= v_mul;
-
-    // ---- publish the twelve probabilities of this group as (p, p) pairs ----
-    float2* probs = prob_slot + (pair & 1) * kProbParityStride;
-    probs[my_token * 3 + my_head] = make_float2(prob, prob);  // head 2 is written twice, same value
-    __syncwarp();
-
-    // ---- values: acc[h] += p[token][h] * v[token] ----
-    auto add_token = [&](const unsigned char* at, int k) {
-      float2 vreg[4];
-      to_pairs<T, FP8>(load_raw<FP8>(at), vreg);
-#pragma unroll
-      for (int h = 0; h < kHeadsPerThread; ++h) {
-        const float2 p2 = probs[k * 3 + h];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[h][j] = __ffma2_rn(p2, vreg[j], acc[h][j]);
-      }
-    };
-    const unsigned char* values = slot + 2 * Traits::kTileBytes;
-    if (all_valid) {
-      // all four tokens exist (the common case)
-      add_token(values, 0);
-      add_token(values + kRowPlus8, 1);
-      add_token(values + Traits::kTileBytes, 2);
-      add_token(values + Traits::kTileBytes + kRowPlus8, 3);
-    } else {
-      // a token that does not exist may hold anything (NaN included): skip it
-      if (token_base < tokens_here) add_token(values, 0);
-      if (token_base + 8 < tokens_here) add_token(values + kRowPlus8, 1);
-      if (token_base + QF_PAGE_SIZE < tokens_here) add_token(values + Traits::kTileBytes, 2);
-      if (token_base + QF_PAGE_SIZE + 8 < tokens_here) add_token(values + Traits::kTileBytes + kRowPlus8, 3);
-    }
+    attend_pair<T, FP8>(slot, prob_slot + (pair & 1) * kProbParityStride, role, q2, acc, my_offset,
+                        my_sum, pair < full_pairs, pair * 2 * QF_PAGE_SIZE + row, tokens_here, k_mul,
+                        v_mul);
   }
   long long t_loop_end = 0;
   if (PROFILE) t_loop_end = clock64();
@@ -470,74 +587,16 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   // Barrier: every slot has been read, so the ring is free for the merge.
   wait_all_copies();
   __syncthreads();
-  float* merge = reinterpret_cast<float*>(smem);  // [8 warps][3 heads][128]
-  {
-    // sum of a head over the group's four token streams (lanes differing in bits 3, 2)
-    float total = my_sum + __shfl_xor_sync(kFull, my_sum, 8);
-    total += __shfl_xor_sync(kFull, total, 4);
-    if (my_token == 0 && sub == head_lane(my_head)) {
-      group_offset[head_group][row][my_head] = my_offset;
-      group_sum[head_group][row][my_head] = total;
-    }
-  }
-  __syncthreads();
-  if (tid < QF_GQA_GROUP) {
-    const int g = tid / kHeadsPerThread, h = tid - g * kHeadsPerThread;
-    float m = -INFINITY;
-    for (int r = 0; r < kGroupRows; ++r) m = fmaxf(m, group_offset[g][r][h]);
-    float total = 0.f;
-    for (int r = 0; r < kGroupRows; ++r) {
-      const float mg = group_offset[g][r][h];
-      if (mg != -INFINITY) total += group_sum[g][r][h] * fast_exp2(mg - m);
-    }
-    cta_offset[tid] = m;
-    cta_sum[tid] = total;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < kHeadsPerThread; ++h) {
-    const float mg = group_offset[head_group][row][h];
-    const float f = mg == -INFINITY ? 0.f : fast_exp2(mg - cta_offset[head_group * kHeadsPerThread + h]);
-    const float2 f2 = make_float2(f, f);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 a = __fmul2_rn(acc[h][j], f2);
-      a.x += __shfl_xor_sync(kFull, a.x, 16);
-      a.y += __shfl_xor_sync(kFull, a.y, 16);
-      acc[h][j] = a;
-    }
-    if (lane < 16) {
-      float4* dst =
-          reinterpret_cast<float4*>(merge + (warp * kHeadsPerThread + h) * QF_HEAD_DIM + sub * 8);
-      dst[0] = make_float4(acc[h][0].x, acc[h][0].y, acc[h][1].x, acc[h][1].y);
-      dst[1] = make_float4(acc[h][2].x, acc[h][2].y, acc[h][3].x, acc[h][3].y);
-    }
-  }
-  __syncthreads();
   const int64_t head0 = static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
   const int64_t partial_row =
       (static_cast<int64_t>(sequence) * p.split_k + split) * p.q_heads + head0;
-#pragma unroll
-  for (int i = 0; i < (QF_GQA_GROUP * QF_HEAD_DIM) / kFastThreads; ++i) {
-    const int e = tid + i * kFastThreads;  // (head, dim) flattened
-    const int head = e >> 7, d = e & 127;
-    const int g = head / kHeadsPerThread, h = head - g * kHeadsPerThread;
-    float value = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) value += merge[((g * 4 + w) * kHeadsPerThread + h) * QF_HEAD_DIM + d];
-    if (p.partial_out != nullptr) p.partial_out[partial_row * QF_HEAD_DIM + e] = value;
-    if (p.out != nullptr) {
-      const float total = cta_sum[head];
-      const float norm = value / (total > 0.f ? total : 1.f);
-      static_cast<T*>(p.out)[sequence * p.o_sb + (head0 + head) * p.o_sh + d * p.o_sd] =
-          from_float<T>(norm);
-    }
-  }
-  if (tid < QF_GQA_GROUP && p.partial_max != nullptr) {
-    // natural-log units, as the combine and the reference's reduce expect
-    p.partial_max[partial_row + tid] = cta_offset[tid] * kLn2;
-    p.partial_sum[partial_row + tid] = cta_sum[tid];
-  }
+  merge_and_store<T>(
+      merge_state, reinterpret_cast<float*>(smem), acc, my_offset, my_sum, my_token, my_head,
+      p.partial_out != nullptr ? p.partial_out + partial_row * QF_HEAD_DIM : nullptr,
+      p.partial_max != nullptr ? p.partial_max + partial_row : nullptr,
+      p.partial_max != nullptr ? p.partial_sum + partial_row : nullptr,
+      p.out != nullptr ? static_cast<T*>(p.out) + sequence * p.o_sb + head0 * p.o_sh : nullptr, p.o_sh,
+      p.o_sd);
   if (PROFILE && p.cycles != nullptr && tid == 32) {
     // One warp per CTA reports {waiting for pages, page loop, set-up before it, merge after it}.
     long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * 4;

@@ -12,9 +12,9 @@ call can be recorded into a CUDA graph exactly like the reference's
 (custom_kernels/paged_decode_grouped_splitk.py:247-252).
 
 The work is done by libqf_hotpath.so: `qf_grouped_splitk_decode_attention`
-runs the partial pass (one CTA per sequence, KV head and split; all query heads
-of a GQA group share each page load) and, for split_k > 1, the combine.  The
-Triton knobs `num_stages`, `heads_per_program` and `num_warps` are validated as
+runs the partial pass (all query heads of a GQA group share each page load; for
+split_k > 1 persistent CTAs share the batch's pages equally, and the partial
+buffers are their private scratch) and the combine.  The Triton knobs `num_stages`, `heads_per_program` and `num_warps` are validated as
 the reference validates them and otherwise ignored.
 """
 

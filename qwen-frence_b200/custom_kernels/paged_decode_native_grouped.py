@@ -4,11 +4,14 @@ Drop-in for custom_kernels/paged_decode_native_grouped.py: same three entry
 points and signatures, so baseline/kernel_dispatch.py:84-88 and
 engine/kvcache/paged_decode_attention.py:228-234 call it unchanged.
 
-The partial kernel assigns one CTA to a (request, KV head, split); the six
-query heads of the group share every K/V page, which is copied once into a
-shared-memory ring; the combine merges the numerically stable fp32 partials.
-Both run inside libqf_hotpath.so (sm_100a); nothing here depends on Triton, on
-a torch C++ extension or on a CPU fallback.
+The six query heads of a GQA group share every K/V page, which is copied once
+into a shared-memory ring; the combine merges the numerically stable fp32
+partials.  `native_grouped_splitk_decode_attention` runs the persistent kernel
+(resident CTAs that share the batch's pages equally, then the combine);
+`grouped_gqa_splitk_partial_out` runs one CTA per (request, KV head, split) and
+returns the reference's balanced partitions.  Everything runs inside
+libqf_hotpath.so (sm_100a); nothing here depends on Triton, on a torch C++
+extension or on a CPU fallback.
 """
 
 from __future__ import annotations
@@ -133,6 +136,42 @@ def native_grouped_splitk_decode_attention(
     return out
 
 
+def grouped_gqa_splitk_partial_out(q, k_pool, v_pool, block_table, seq_lens,
+                                   partial_out, partial_max, partial_sum, scale):
+    """The partial pass alone, into caller buffers, one partition per split slot.
+
+    Same arguments as the extension op the reference binds
+    (custom_kernels/native_grouped_decode.cu:329-403): partition s of a sequence
+    covers pages [s*P/K, (s+1)*P/K); partial_out (B, K, H, 128) is unnormalised,
+    partial_max an exponent offset in natural-log units, partial_sum the matching
+    sum; an empty partition is (0, -inf, 0).  Returns None.
+    """
+    import ctypes
+
+    import torch
+
+    batch, query_heads, head_dim = _check_layout(q, k_pool, v_pool)
+    cabi = _extension()
+    _check_metadata(torch, q, k_pool, v_pool, block_table, seq_lens)
+    _require(partial_out.ndim == 4 and partial_out.shape[0] == batch
+             and tuple(partial_out.shape[2:]) == (query_heads, head_dim),
+             "preallocated partial output has the wrong shape")
+    split_k = partial_out.shape[1]
+    _require(tuple(partial_max.shape) == (batch, split_k, query_heads)
+             and partial_sum.shape == partial_max.shape,
+             "preallocated partial statistics have the wrong shape")
+    _require(all(t.dtype == torch.float32 and t.is_contiguous() and t.device == q.device
+                 for t in (partial_out, partial_max, partial_sum)),
+             "partial outputs must be contiguous float32")
+    splitk = _sibling("paged_decode_grouped_splitk")
+    args = splitk.fill_attention_args(
+        cabi, q, k_pool, v_pool, block_table, seq_lens, split_k=split_k, scale=scale,
+        partials=(partial_out, partial_max, partial_sum), out=None)
+    with cabi.device_of(q):
+        cabi.check(cabi.library().qf_grouped_gqa_splitk_partial_out(
+            ctypes.byref(args), cabi.stream_pointer(q.device)))
+
+
 def native_grouped_decode_diagnostics(q, block_table):
     """Compiled resources and occupancy of the partial kernel, without counters.
 
@@ -165,9 +204,10 @@ def native_grouped_stage_cycles(
 ):
     """Run the instrumented partial once and return per-CTA stage cycles.
 
-    Returns int64 [B, Hkv, split_k, 4]: clock64() cycles one warp of each CTA
-    spent {waiting for pages, in the whole page loop, 0, 0} (this kernel
-    overlaps loading with math, so there is no separate load or PV stage).
+    Returns int64 [B, Hkv, split_k, 4]: clock64() cycles one warp of each CTA of
+    the per-partition kernel spent {waiting for pages, in the whole page loop, in
+    the set-up before it, in the merge after it} (loading overlaps the math, so
+    there is no separate load or PV stage).
     Mirrors custom_kernels/paged_decode_native_grouped.py:96-119.
     """
     import ctypes

@@ -97,7 +97,8 @@ def test_partials_match_oracle_partition_by_partition(package, oracle, cuda_devi
     partials = (torch.full((batch, split_k, 12, 128), float("nan"), device=cuda_device),
                 torch.full((batch, split_k, 12), float("nan"), device=cuda_device),
                 torch.full((batch, split_k, 12), float("nan"), device=cuda_device))
-    out = package.native_grouped_splitk_decode_attention(*dev, split_k=split_k, partials=partials)
+    package.grouped_gqa_splitk_partial_out(*dev, *partials, 128 ** -0.5)
+    out = package.splitk_reduce(*partials, torch.empty_like(dev[0]))
     po, pm, ps = (t.cpu() for t in partials)
     ro, rm, rs = oracle.splitk_partial(*host, split_k=split_k)
     empty = rs == 0
@@ -109,9 +110,9 @@ def test_partials_match_oracle_partition_by_partition(package, oracle, cuda_devi
     torch.testing.assert_close(ps * factor, rs, atol=1e-4, rtol=1e-4)
     torch.testing.assert_close(po * factor[..., None], ro, atol=2e-3, rtol=2e-3)
     assert_attention_close(out, oracle.splitk_reduce(ro, rm, rs))
-    # the standalone combine entry point on the kernel's own partials
-    again = package.splitk_reduce(*partials, torch.empty_like(out))
-    assert torch.equal(again, out)
+    # the fused entry point (persistent kernel, pieces instead of partitions)
+    fused = package.native_grouped_splitk_decode_attention(*dev, split_k=split_k)
+    assert_attention_close(fused, out)
 
 
 def test_known_answers(package, cuda_device):
@@ -251,6 +252,110 @@ def test_bad_page_id_is_reported_not_dereferenced(package, cuda_device):
     table = table.clone()
     table[0, 1] = 10_000
     out = package.grouped_splitk_decode_attention(q, k, v, table, lens, split_k=1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert package.cabi.device_status() == 2
+    assert package.cabi.device_status() == 0
+
+
+# ---------------------------------------------------------------------------
+# The persistent kernel behind the fused entry point (split_k >= 2): CTAs share
+# the batch's page pairs equally, so a CTA's share crosses sequence boundaries.
+# ---------------------------------------------------------------------------
+def _streamed(package, dev, split_k, **kwargs):
+    package.cabi.set_tuning(force_generic=3)  # persistent kernel whatever the batch size
+    try:
+        return package.grouped_splitk_decode_attention(*dev, split_k=split_k, **kwargs)
+    finally:
+        package.cabi.set_tuning()
+
+
+def _streamed_and_partitioned(package, dev, split_k):
+    streamed = _streamed(package, dev, split_k)
+    package.cabi.set_tuning(force_generic=2)
+    try:
+        partitioned = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+    finally:
+        package.cabi.set_tuning()
+    return streamed, partitioned
+
+
+@pytest.mark.parametrize("split_k", [2, 3, 10, 64])
+def test_streamed_kernel_mixed_lengths(package, oracle, cuda_device, split_k):
+    """Empty, one-token, page-straddling and long sequences in one batch; the table is
+    padded with -1 and the tail of every last page is NaN."""
+    generator = torch.Generator().manual_seed(split_k)
+    lengths = [0, 1, 31, 32, 33, 0, 64, 65, 4000, 16, 17, 0] + \
+        torch.randint(1, 1500, (40,), generator=generator).tolist()
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=21, poison=True)
+    expected = oracle.paged_attention(*host)
+    streamed, partitioned = _streamed_and_partitioned(package, dev, split_k)
+    assert_attention_close(streamed, expected)
+    assert_attention_close(partitioned, expected)
+    assert torch.isfinite(streamed.float()).all()
+    assert (streamed[[0, 5, 11]] == 0).all()
+
+
+def test_streamed_kernel_many_short_sequences(package, oracle, cuda_device):
+    """Hundreds of sequences of one or two page pairs: every CTA's share holds many
+    pieces, and most sequences fit in one."""
+    generator = torch.Generator().manual_seed(5)
+    lengths = torch.randint(0, 50, (700,), generator=generator).tolist()
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=22)
+    expected = oracle.paged_attention(*host)
+    streamed, _ = _streamed_and_partitioned(package, dev, 2)
+    assert_attention_close(streamed, expected)
+
+
+def test_streamed_kernel_one_long_sequence_few_slots(package, oracle, cuda_device):
+    """split_k = 2 with one long sequence: the share is set by the slot limit (no
+    sequence may be cut into more than split_k pieces), not by the CTA count."""
+    host, dev = _fast_path_inputs(cuda_device, [9000, 40, 3], seed=23)
+    expected = oracle.paged_attention(*host)
+    for split_k in (2, 3):
+        streamed, _ = _streamed_and_partitioned(package, dev, split_k)
+        assert_attention_close(streamed, expected)
+
+
+def test_streamed_kernel_reuses_partial_buffers(package, oracle, cuda_device):
+    """End-of-sequence marks left in the partial buffers by one call must not leak
+    into the next call with other lengths (and NaN-filled buffers are harmless)."""
+    split_k = 6
+    first, dev_first = _fast_path_inputs(cuda_device, [3000, 10, 500, 0], seed=24)
+    second, dev_second = _fast_path_inputs(cuda_device, [20, 2500, 0, 700], seed=25)
+    partials = (torch.full((4, split_k, 12, 128), float("nan"), device=cuda_device),
+                torch.full((4, split_k, 12), float("nan"), device=cuda_device),
+                torch.full((4, split_k, 12), float("nan"), device=cuda_device))
+    for host, dev in ((first, dev_first), (second, dev_second), (first, dev_first)):
+        out = _streamed(package, dev, split_k, partials=partials)
+        assert_attention_close(out, oracle.paged_attention(*host))
+
+
+@pytest.mark.parametrize("dtype,index_dtype", [(torch.bfloat16, torch.int64), (torch.float16, torch.int64)])
+def test_streamed_kernel_dtypes(package, oracle, cuda_device, dtype, index_dtype):
+    lengths = [700, 0, 33, 1200, 95]
+    host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=26)
+    dq, dk, dv, dtable, dlens = dev
+    out = _streamed(package, (dq, dk, dv, dtable.to(index_dtype), dlens.to(index_dtype)), 4)
+    assert_attention_close(out, oracle.paged_attention(*host))
+
+
+def test_streamed_kernel_batch_above_prefix_capacity(package, oracle, cuda_device):
+    """More than 1024 sequences do not fit the persistent kernel's shared-memory
+    prefix; the per-partition kernel takes over."""
+    generator = torch.Generator().manual_seed(9)
+    lengths = torch.randint(0, 40, (1100,), generator=generator).tolist()
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=27)
+    out = package.grouped_splitk_decode_attention(*dev, split_k=2)
+    assert_attention_close(out, oracle.paged_attention(*host))
+
+
+def test_streamed_kernel_bad_page_id(package, cuda_device):
+    (_, dev) = _fast_path_inputs(cuda_device, [200, 40])
+    q, k, v, table, lens = dev
+    table = table.clone()
+    table[0, 3] = 10_000
+    out = _streamed(package, (q, k, v, table, lens), 2)
     torch.cuda.synchronize()
     assert torch.isfinite(out.float()).all()
     assert package.cabi.device_status() == 2
