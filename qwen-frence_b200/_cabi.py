@@ -201,6 +201,7 @@ def device_status(reset=True):
 def set_tuning(stages=0, force_generic=False):
     """Kernel selection for tests: force_generic 1 (or True) sends every launch to the
     stride-generic kernel, 2 keeps the fast per-partition kernel but turns the
-    persistent one off, 3 uses the persistent one whenever the layout allows (also
-    for batches with few split slots); 0 restores the defaults."""
+    persistent ones off, 3 / 4 use the persistent CUDA-core / tensor-core kernel
+    whenever the layout allows (also for batches with few split slots); 0 restores
+    the defaults."""
     check(library().qf_set_tuning(int(stages), int(force_generic)))

@@ -3,8 +3,10 @@
 //
 // The fast partial kernels (sm_100a, cp.async ring, Qwen geometry) live in
 // qf_decode_partial.cuh (one CTA per partition, the reference's balanced
-// partitions) and qf_decode_stream.cuh (persistent CTAs that share the batch's
-// pages equally; what the fused attention entry point runs).
+// partitions), qf_decode_stream.cuh (persistent CTAs that share the batch's
+// pages equally, CUDA-core math; the fused entry point's kernel for FP8 pools)
+// and qf_decode_mma.cuh (the same scheduling with tensor-core math; the fused
+// entry point's kernel for fp16 / bf16 pools).
 //
 // A stride-generic kernel covers every other layout and geometry the
 // reference accepts (custom_kernels/paged_decode_grouped_splitk.py:228-334):
@@ -15,6 +17,7 @@
 #include "qf_common.cuh"
 #include "qf_decode_partial.cuh"
 #include "qf_decode_stream.cuh"
+#include "qf_decode_mma.cuh"
 
 namespace qf {
 namespace {
@@ -339,6 +342,25 @@ int launch_stream(const FastParams& p, cudaStream_t stream) {
   return QF_OK;
 }
 
+size_t mma_smem_bytes() {
+  return static_cast<size_t>(kMmaWarps) * kRingTiles * kTileBytes16 + kMmaMergeFloats * sizeof(float);
+}
+
+// One CTA per SM (its rings take most of the shared memory).
+template <typename T>
+int launch_mma(const FastParams& p, cudaStream_t stream) {
+  auto kernel = decode_mma_kernel<T>;
+  const size_t smem = mma_smem_bytes();
+  QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  const int resident = stream_ctas_on_current_device() / QF_MIN_CTAS;
+  QF_REQUIRE(resident >= p.kv_heads, "could not size the tensor-core kernel for this device");
+  StreamParams sp{p, resident / p.kv_heads};
+  kernel<<<static_cast<unsigned>(sp.ctas_per_head * p.kv_heads), kFastThreads, smem, stream>>>(sp);
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
 int validate(const qf_decode_attention_args* a, bool need_out) {
@@ -412,27 +434,40 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
   return p;
 }
 
-// The streamed kernel serves the fused attention entry point when the layout is
-// the fast one, the batch's prefix fits in its shared memory, and the split slots
+// A persistent kernel serves the fused attention entry point when the layout is
+// the fast one, the batch's prefix fits in shared memory, and the split slots
 // cannot become the limit: a sequence may be cut into at most split_k pieces, so
-// a CTA's share is at least longest / (split_k - 1) pairs, and with few sequences
+// a CTA's share is at least longest / (split_k - 1) units, and with few sequences
 // and few slots that would leave most resident CTAs without work.  The lengths
 // live on the device, so the test uses what the host knows: batch * (split_k - 1)
-// slots per KV head against twice the resident CTAs per KV head.
-bool stream_path_ok(const qf_decode_attention_args* a) {
-  if ((g_force_generic != 0 && g_force_generic != 3) || !fast_path_ok(a) || a->split_k < 2) return false;
-  if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return false;
-  const int resident = stream_ctas_on_current_device();
-  if (resident < a->kv_heads) return false;
-  if (g_force_generic == 3) return true;  // tests: the streamed kernel whatever the slot count
-  const int64_t per_head = resident / a->kv_heads;
-  return static_cast<int64_t>(a->batch) * (a->split_k - 1) >= 2 * per_head;
+// slots per KV head against twice the resident CTAs per KV head.  fp16 / bf16
+// pools take the tensor-core kernel, FP8 pools the CUDA-core one.
+enum class FusedKernel { kPartitioned, kStreamed, kTensorCore };
+
+FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
+  const int mode = g_force_generic;  // 0 automatic, 3 / 4 force a persistent kernel (tests)
+  if ((mode != 0 && mode != 3 && mode != 4) || !fast_path_ok(a) || a->split_k < 2) {
+    return FusedKernel::kPartitioned;
+  }
+  if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return FusedKernel::kPartitioned;
+  const int resident = stream_ctas_on_current_device();  // two per SM
+  if (resident / QF_MIN_CTAS < a->kv_heads) return FusedKernel::kPartitioned;
+  const bool tensor_core = !a->kv_fp8 && mode != 3;
+  if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
+  const int64_t per_head = (tensor_core ? resident / QF_MIN_CTAS : resident) / a->kv_heads;
+  if (mode == 0 && static_cast<int64_t>(a->batch) * (a->split_k - 1) < 2 * per_head) {
+    return FusedKernel::kPartitioned;
+  }
+  return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 
-int launch_streamed_partial(const qf_decode_attention_args* a, cudaStream_t stream) {
+int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kind, cudaStream_t stream) {
   int* status = status_word_for_current_device();
   QF_REQUIRE(status != nullptr, "could not resolve the device status word");
   const FastParams p = fast_params(a, nullptr, nullptr, status);
+  if (kind == FusedKernel::kTensorCore) {
+    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half>(p, stream) : launch_mma<__nv_bfloat16>(p, stream);
+  }
   if (a->kv_fp8) {
     return a->dtype == QF_DTYPE_F16 ? launch_stream<__half, true>(p, stream)
                                     : launch_stream<__nv_bfloat16, true>(p, stream);
@@ -560,8 +595,10 @@ int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, voi
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (args->split_k == 1) return qf::launch_partial<false>(args, true, nullptr, s);
   if (args->batch == 0) return QF_OK;
-  const bool streamed = qf::stream_path_ok(args);
-  rc = streamed ? qf::launch_streamed_partial(args, s) : qf::launch_partial<false>(args, false, nullptr, s);
+  const qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  const bool streamed = kind != qf::FusedKernel::kPartitioned;
+  rc = streamed ? qf::launch_persistent_partial(args, kind, s)
+                : qf::launch_partial<false>(args, false, nullptr, s);
   if (rc != QF_OK) return rc;
   qf::ReduceParams r{};
   r.po = args->partial_out, r.pm = args->partial_max, r.ps = args->partial_sum;
@@ -620,7 +657,7 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 
 int qf_set_tuning(int32_t stages, int32_t force_generic) {
   QF_REQUIRE(stages >= 0 && stages <= 64, "stages must be in [0, 64]");
-  QF_REQUIRE(force_generic >= 0 && force_generic <= 3, "force_generic must be in [0, 3]");
+  QF_REQUIRE(force_generic >= 0 && force_generic <= 4, "force_generic must be in [0, 4]");
   qf::g_tuned_stages = stages;
   qf::g_force_generic = force_generic;
   return QF_OK;

@@ -47,6 +47,72 @@ struct StreamParams {
   int ctas_per_head;  // resident CTAs that share one KV head's pair list
 };
 
+// The launch-wide work list in shared memory: sequences in units of
+// `kUnitTokens` tokens (a page pair here, a page in the tensor-core kernel).
+struct WorkList {
+  int first_unit[kMaxStreamBatch + 1];  // exclusive prefix of units over sequences; [kMaxStreamBatch] = total
+  int length[kMaxStreamBatch];          // clamped sequence lengths
+  int warp_total[kFastThreads / 32];
+  int warp_longest[kFastThreads / 32];
+};
+
+// Every thread of a kFastThreads-wide CTA calls this once (it has two CTA-wide
+// barriers); returns the longest sequence in units.  The total is
+// list.first_unit[kMaxStreamBatch].
+template <int kUnitTokens>
+__device__ __forceinline__ int build_work_list(WorkList& list, const void* seq_lens, int lens_dtype,
+                                               int64_t lens_stride, int batch) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int running = 0, longest = 0;
+  int before[kScanPerThread];
+#pragma unroll
+  for (int i = 0; i < kScanPerThread; ++i) {
+    const int b = tid * kScanPerThread + i;
+    int len = 0;
+    if (b < batch) {
+      int64_t raw = load_index(seq_lens, lens_dtype, b * lens_stride);
+      raw = raw < 0 ? 0 : raw;
+      len = static_cast<int>(raw > kMaxStreamLen ? kMaxStreamLen : raw);
+    }
+    list.length[b] = len;
+    const int units = (len + kUnitTokens - 1) / kUnitTokens;
+    before[i] = running;
+    running += units;
+    longest = max(longest, units);
+  }
+  int inclusive = running;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int up = __shfl_up_sync(kFull, inclusive, off);
+    if (lane >= off) inclusive += up;
+    longest = max(longest, __shfl_xor_sync(kFull, longest, off));
+  }
+  if (lane == 31) list.warp_total[warp] = inclusive, list.warp_longest[warp] = longest;
+  __syncthreads();
+  int base = inclusive - running;  // units of earlier threads of this warp
+  for (int w = 0; w < warp; ++w) base += list.warp_total[w];
+#pragma unroll
+  for (int i = 0; i < kScanPerThread; ++i) list.first_unit[tid * kScanPerThread + i] = base + before[i];
+  if (tid == kFastThreads - 1) list.first_unit[kMaxStreamBatch] = base + running;
+  __syncthreads();
+  longest = 0;
+#pragma unroll
+  for (int w = 0; w < kFastThreads / 32; ++w) longest = max(longest, list.warp_longest[w]);
+  return longest;
+}
+
+// The last sequence whose first unit is <= `unit` (it is not empty when `unit` is
+// below the total, because the next prefix is larger).
+__device__ __forceinline__ int sequence_of_unit(const WorkList& list, int batch, int unit) {
+  int lo = 0, hi = batch - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (list.first_unit[mid] <= unit) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
 template <typename T, bool FP8>
 __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     decode_stream_kernel(const StreamParams sp) {
@@ -56,12 +122,8 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(16) float2 prob_pairs[2][kConsumerWarps][2][12];
   __shared__ MergeShared merge_state;
-  __shared__ int first_pair[kMaxStreamBatch + 1];  // exclusive prefix of page pairs over sequences
-  __shared__ int length[kMaxStreamBatch];          // clamped sequence lengths
-  __shared__ int warp_total[kConsumerWarps];
-  __shared__ int warp_longest[kConsumerWarps];
+  __shared__ WorkList work;  // units are page pairs
 
-  constexpr unsigned kFull = 0xffffffffu;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -72,44 +134,11 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   const int cta = blockIdx.x - kv_head * sp.ctas_per_head;
 
   // ---- the pair list of this launch: prefix over sequences, total, longest ----
-  {
-    int running = 0, longest = 0;
-    int before[kScanPerThread];
-#pragma unroll
-    for (int i = 0; i < kScanPerThread; ++i) {
-      const int b = tid * kScanPerThread + i;
-      int len = 0;
-      if (b < p.batch) {
-        int64_t raw = load_index(p.seq_lens, p.lens_dtype, b * p.lens_stride);
-        raw = raw < 0 ? 0 : raw;
-        len = static_cast<int>(raw > kMaxStreamLen ? kMaxStreamLen : raw);
-      }
-      length[b] = len;
-      const int pairs = (len + 2 * QF_PAGE_SIZE - 1) / (2 * QF_PAGE_SIZE);
-      before[i] = running;
-      running += pairs;
-      longest = max(longest, pairs);
-    }
-    int inclusive = running;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int up = __shfl_up_sync(kFull, inclusive, off);
-      if (lane >= off) inclusive += up;
-      longest = max(longest, __shfl_xor_sync(kFull, longest, off));
-    }
-    if (lane == 31) warp_total[warp] = inclusive, warp_longest[warp] = longest;
-    __syncthreads();
-    int base = inclusive - running;  // pairs of earlier threads of this warp
-    for (int w = 0; w < warp; ++w) base += warp_total[w];
-#pragma unroll
-    for (int i = 0; i < kScanPerThread; ++i) first_pair[tid * kScanPerThread + i] = base + before[i];
-    if (tid == kFastThreads - 1) first_pair[kMaxStreamBatch] = base + running;
-    __syncthreads();
-  }
+  const int longest =
+      build_work_list<2 * QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
+  const int* first_pair = work.first_unit;
+  const int* length = work.length;
   const int total = first_pair[kMaxStreamBatch];
-  int longest = 0;
-#pragma unroll
-  for (int w = 0; w < kConsumerWarps; ++w) longest = max(longest, warp_longest[w]);
   if (total == 0) return;
   // Pairs per CTA: an equal share, but never so small that a sequence would be cut
   // into more pieces than there are split slots.
@@ -119,16 +148,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   if (begin >= total) return;
   const int count = min(share, total - begin);
 
-  // The sequence that holds pair `begin`: the last one whose prefix is <= begin
-  // (it is not empty, because the next prefix is larger).
-  int start_seq = 0;
-  {
-    int hi = p.batch - 1;
-    while (start_seq < hi) {
-      const int mid = (start_seq + hi + 1) >> 1;
-      if (first_pair[mid] <= begin) start_seq = mid; else hi = mid - 1;
-    }
-  }
+  const int start_seq = sequence_of_unit(work, p.batch, begin);  // holds pair `begin`
   const int start_pair = begin - first_pair[start_seq];  // first pair of the share, within its sequence
 
   // ---- loads: as in the per-partition kernel, but the fetch cursor crosses sequences ----

@@ -259,29 +259,32 @@ def test_bad_page_id_is_reported_not_dereferenced(package, cuda_device):
 
 
 # ---------------------------------------------------------------------------
-# The persistent kernel behind the fused entry point (split_k >= 2): CTAs share
-# the batch's page pairs equally, so a CTA's share crosses sequence boundaries.
+# The persistent kernels behind the fused entry point (split_k >= 2): CTAs share
+# the batch's pages equally, so a CTA's share crosses sequence boundaries.  Mode 3
+# is the CUDA-core kernel (what FP8 pools use), mode 4 the tensor-core kernel.
 # ---------------------------------------------------------------------------
-def _streamed(package, dev, split_k, **kwargs):
-    package.cabi.set_tuning(force_generic=3)  # persistent kernel whatever the batch size
+PERSISTENT = pytest.mark.parametrize("mode", [3, 4], ids=["cuda_core", "tensor_core"])
+
+
+def _persistent(package, mode, dev, split_k, **kwargs):
+    package.cabi.set_tuning(force_generic=mode)  # whatever the batch size
     try:
         return package.grouped_splitk_decode_attention(*dev, split_k=split_k, **kwargs)
     finally:
         package.cabi.set_tuning()
 
 
-def _streamed_and_partitioned(package, dev, split_k):
-    streamed = _streamed(package, dev, split_k)
+def _partitioned(package, dev, split_k):
     package.cabi.set_tuning(force_generic=2)
     try:
-        partitioned = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+        return package.grouped_splitk_decode_attention(*dev, split_k=split_k)
     finally:
         package.cabi.set_tuning()
-    return streamed, partitioned
 
 
+@PERSISTENT
 @pytest.mark.parametrize("split_k", [2, 3, 10, 64])
-def test_streamed_kernel_mixed_lengths(package, oracle, cuda_device, split_k):
+def test_persistent_kernel_mixed_lengths(package, oracle, cuda_device, split_k, mode):
     """Empty, one-token, page-straddling and long sequences in one batch; the table is
     padded with -1 and the tail of every last page is NaN."""
     generator = torch.Generator().manual_seed(split_k)
@@ -289,35 +292,35 @@ def test_streamed_kernel_mixed_lengths(package, oracle, cuda_device, split_k):
         torch.randint(1, 1500, (40,), generator=generator).tolist()
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=21, poison=True)
     expected = oracle.paged_attention(*host)
-    streamed, partitioned = _streamed_and_partitioned(package, dev, split_k)
-    assert_attention_close(streamed, expected)
-    assert_attention_close(partitioned, expected)
-    assert torch.isfinite(streamed.float()).all()
-    assert (streamed[[0, 5, 11]] == 0).all()
+    out = _persistent(package, mode, dev, split_k)
+    assert_attention_close(out, expected)
+    assert_attention_close(_partitioned(package, dev, split_k), expected)
+    assert torch.isfinite(out.float()).all()
+    assert (out[[0, 5, 11]] == 0).all()
 
 
-def test_streamed_kernel_many_short_sequences(package, oracle, cuda_device):
-    """Hundreds of sequences of one or two page pairs: every CTA's share holds many
-    pieces, and most sequences fit in one."""
+@PERSISTENT
+def test_persistent_kernel_many_short_sequences(package, oracle, cuda_device, mode):
+    """Hundreds of sequences of a few pages: every CTA's share holds many pieces, and
+    most sequences fit in one."""
     generator = torch.Generator().manual_seed(5)
     lengths = torch.randint(0, 50, (700,), generator=generator).tolist()
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=22)
-    expected = oracle.paged_attention(*host)
-    streamed, _ = _streamed_and_partitioned(package, dev, 2)
-    assert_attention_close(streamed, expected)
+    assert_attention_close(_persistent(package, mode, dev, 2), oracle.paged_attention(*host))
 
 
-def test_streamed_kernel_one_long_sequence_few_slots(package, oracle, cuda_device):
+@PERSISTENT
+def test_persistent_kernel_one_long_sequence_few_slots(package, oracle, cuda_device, mode):
     """split_k = 2 with one long sequence: the share is set by the slot limit (no
     sequence may be cut into more than split_k pieces), not by the CTA count."""
     host, dev = _fast_path_inputs(cuda_device, [9000, 40, 3], seed=23)
     expected = oracle.paged_attention(*host)
     for split_k in (2, 3):
-        streamed, _ = _streamed_and_partitioned(package, dev, split_k)
-        assert_attention_close(streamed, expected)
+        assert_attention_close(_persistent(package, mode, dev, split_k), expected)
 
 
-def test_streamed_kernel_reuses_partial_buffers(package, oracle, cuda_device):
+@PERSISTENT
+def test_persistent_kernel_reuses_partial_buffers(package, oracle, cuda_device, mode):
     """End-of-sequence marks left in the partial buffers by one call must not leak
     into the next call with other lengths (and NaN-filled buffers are harmless)."""
     split_k = 6
@@ -327,21 +330,49 @@ def test_streamed_kernel_reuses_partial_buffers(package, oracle, cuda_device):
                 torch.full((4, split_k, 12), float("nan"), device=cuda_device),
                 torch.full((4, split_k, 12), float("nan"), device=cuda_device))
     for host, dev in ((first, dev_first), (second, dev_second), (first, dev_first)):
-        out = _streamed(package, dev, split_k, partials=partials)
+        out = _persistent(package, mode, dev, split_k, partials=partials)
         assert_attention_close(out, oracle.paged_attention(*host))
 
 
-@pytest.mark.parametrize("dtype,index_dtype", [(torch.bfloat16, torch.int64), (torch.float16, torch.int64)])
-def test_streamed_kernel_dtypes(package, oracle, cuda_device, dtype, index_dtype):
+@PERSISTENT
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_persistent_kernel_dtypes(package, oracle, cuda_device, dtype, mode):
     lengths = [700, 0, 33, 1200, 95]
     host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=26)
     dq, dk, dv, dtable, dlens = dev
-    out = _streamed(package, (dq, dk, dv, dtable.to(index_dtype), dlens.to(index_dtype)), 4)
+    out = _persistent(package, mode, (dq, dk, dv, dtable.long(), dlens.long()), 4)
     assert_attention_close(out, oracle.paged_attention(*host))
 
 
-def test_streamed_kernel_batch_above_prefix_capacity(package, oracle, cuda_device):
-    """More than 1024 sequences do not fit the persistent kernel's shared-memory
+@PERSISTENT
+def test_persistent_kernel_known_answers(package, cuda_device, mode):
+    """Uniform scores: the output is the plain mean of V, exactly."""
+    q, k, v, table, lens = make_paged_inputs([0, 1, 17, 1024], poison=True)
+    q.zero_()
+    v[:, :, 0] = 3
+    v[:, :, 1] = 9
+    expected = torch.zeros_like(q)
+    expected[1:, :6] = 3
+    expected[1:, 6:] = 9
+    for split_k in (2, 7):
+        out = _persistent(package, mode, _to(cuda_device, q, k, v, table, lens), split_k)
+        assert torch.equal(out.cpu(), expected)
+
+
+@PERSISTENT
+def test_persistent_kernel_large_scores(package, oracle, cuda_device, mode):
+    """Scores that grow along the sequence move the offset many times."""
+    q, k, v, table, lens = make_paged_inputs([300, 45, 2000], seed=5)
+    ramp = torch.linspace(0.0, 6.0, 16)[None, :, None, None]
+    k.mul_(ramp.half())
+    host = (q, k, v, table, lens)
+    expected = oracle.paged_attention(*host, scale=1.0)
+    out = _persistent(package, mode, _to(cuda_device, *host), 3, scale=1.0)
+    assert_attention_close(out, expected)
+
+
+def test_persistent_kernel_batch_above_prefix_capacity(package, oracle, cuda_device):
+    """More than 1024 sequences do not fit the persistent kernels' shared-memory
     prefix; the per-partition kernel takes over."""
     generator = torch.Generator().manual_seed(9)
     lengths = torch.randint(0, 40, (1100,), generator=generator).tolist()
@@ -350,13 +381,25 @@ def test_streamed_kernel_batch_above_prefix_capacity(package, oracle, cuda_devic
     assert_attention_close(out, oracle.paged_attention(*host))
 
 
-def test_streamed_kernel_bad_page_id(package, cuda_device):
+@PERSISTENT
+def test_persistent_kernel_bad_page_id(package, cuda_device, mode):
     (_, dev) = _fast_path_inputs(cuda_device, [200, 40])
     q, k, v, table, lens = dev
     table = table.clone()
     table[0, 3] = 10_000
-    out = _streamed(package, (q, k, v, table, lens), 2)
+    out = _persistent(package, mode, (q, k, v, table, lens), 2)
     torch.cuda.synchronize()
     assert torch.isfinite(out.float()).all()
     assert package.cabi.device_status() == 2
     assert package.cabi.device_status() == 0
+
+
+def test_automatic_choice_runs_persistent_kernel_on_a_wide_batch(package, oracle, cuda_device):
+    """64 sequences x split_k 10: the default path is the tensor-core kernel; it must
+    agree with the forced one bit for bit and with the oracle."""
+    generator = torch.Generator().manual_seed(3)
+    lengths = torch.randint(1, 900, (64,), generator=generator).tolist()
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=28)
+    automatic = package.grouped_splitk_decode_attention(*dev, split_k=10)
+    assert torch.equal(automatic, _persistent(package, 4, dev, 10))
+    assert_attention_close(automatic, oracle.paged_attention(*host))
