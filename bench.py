@@ -51,7 +51,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the
 # ncu capture summarised in profiles/ (same per-launch workload as a full-size launch: one
 # layer of the named workload at seed 0).  Workloads without a capture report null.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {("decode_b64", 0): 137.93e6 + 5.79e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {("decode_b64", 0, "decode_partial_kernel"): 137.93e6 + 5.79e6}
 
 
 def parse_args():
@@ -140,10 +140,12 @@ class ClockSampler:
         return result
 
 
-def partial_kernel_bytes(workload, split_k, fp8):
+def partial_kernel_bytes(package, workload, split_k, fp8, kernel, ctas_per_head):
     """Algorithmic bytes of ONE launch of the attention partial pass (one layer):
-    K+V of every attended token, the block table (and FP8 scales), Q, and what the
-    kernel writes (fp32 partials + statistics, or the fp16 result when split_k is 1)."""
+    K+V of every attended token, the block table (and FP8 scales), the sequence
+    lengths, Q, and what the kernel writes: fp32 partials + statistics of every
+    split slot it fills (all of them for the per-partition kernel, one per piece for
+    the persistent kernels), or the fp16 result when split_k is 1."""
     elem = 1 if fp8 else 2
     lengths = [int(t) for t in workload.seq_lens.tolist()]
     pages = sum(-(-t // 16) for t in lengths)
@@ -151,9 +153,15 @@ def partial_kernel_bytes(workload, split_k, fp8):
     if fp8:
         total += pages * 2 * 2 * 4
     batch = len(lengths)
-    total += batch * 12 * 128 * 2
-    total += batch * split_k * 12 * 130 * 4 if split_k > 1 else batch * 12 * 128 * 2
-    return total
+    total += batch * 12 * 128 * 2 + batch * 4
+    if split_k == 1:
+        return total + batch * 12 * 128 * 2
+    if kernel == "decode_partial_kernel":
+        return total + batch * split_k * 12 * 130 * 4
+    unit = 16 if kernel == "decode_mma_kernel" else 32
+    _, pieces = package.kv_layout.persistent_schedule(
+        lengths, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=unit)
+    return total + 2 * len(pieces) * 6 * 130 * 4
 
 
 def cpu_baseline(oracle, workload, packed_row, k_pool, v_pool, budget_seconds):
@@ -325,15 +333,18 @@ def main():
             scales = (step.k_scales[layer], step.v_scales[layer]) if step.fp8 else None
             arg_sets.append(splitk.fill_attention_args(
                 cabi, q, k_pool, v_pool, step.block_table, step.seq_lens, split_k=step.split_k,
-                scale=128 ** -0.5, partials=partials, out=out if step.split_k == 1 else None,
-                kv_scales=scales))
+                scale=128 ** -0.5, partials=partials, out=out, kv_scales=scales))
         del fp8
         lib = cabi.library()
 
+        kernel_name, ctas_per_head = cabi.fused_kernel_plan(arg_sets[0])
+
         def launch_partials():
+            # the partial pass of the fused attention call, without its combine
             stream = cabi.stream_pointer(device)
             for arg in arg_sets:
-                cabi.check(lib.qf_grouped_gqa_splitk_partial_out(ctypes.byref(arg), stream))
+                cabi.check(lib.qf_grouped_splitk_decode_attention_stages(
+                    ctypes.byref(arg), cabi.STAGE_PARTIAL, stream))
 
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
@@ -348,13 +359,14 @@ def main():
             graph.replay()
         kernel_ms = timed(graph.replay, args.steps) / args.steps / step.layers
         peak, peak_kind = measured_peak_gbs()
-        launch_bytes = partial_kernel_bytes(workload, step.split_k, step.fp8)
+        launch_bytes = partial_kernel_bytes(package, workload, step.split_k, step.fp8, kernel_name,
+                                            ctas_per_head)
         achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
         roofline = {
-            "bound": "hbm", "kernel": "decode_partial_kernel", "achieved": achieved, "peak": peak,
+            "bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed))
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed, kernel_name))
             if world == 1 and step.split_k == 10 else None,  # the captured launch used split_k 10
             "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,
             "kv_bytes_per_launch": package.kv_layout.kv_bytes_per_layer(

@@ -193,8 +193,41 @@ int qf_splitk_reduce(const float* partial_out, const float* partial_max,
  * Replaces grouped_splitk_decode_attention
  * (custom_kernels/paged_decode_grouped_splitk.py:228-334) and
  * native_grouped_splitk_decode_attention
- * (custom_kernels/paged_decode_native_grouped.py:30-88).  `out` is required. */
+ * (custom_kernels/paged_decode_native_grouped.py:30-88).  `out` is required.
+ *
+ * The partial buffers are scratch of this call: for the Qwen geometry
+ * (D = 128, page 16, six query heads per KV head, unit inner strides) with
+ * split_k >= 2, batch <= 1024 and batch * (split_k - 1) at least twice the
+ * resident CTAs per KV head, the partial pass is a persistent kernel whose CTAs
+ * share the batch's pages equally; a sequence then fills only its first few
+ * split slots (one per CTA that holds some of its pages), the slot after them
+ * carries partial_sum = -1, and split boundaries depend on the whole batch.
+ * Callers that need the reference's partitions call
+ * qf_grouped_gqa_splitk_partial_out and qf_splitk_reduce instead. */
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream);
+
+/* The two launches of qf_grouped_splitk_decode_attention separately, for callers
+ * that time or schedule them apart (no counterpart in the reference):
+ * QF_STAGE_PARTIAL runs only the partial pass, QF_STAGE_COMBINE only the combine
+ * of partials left by an earlier QF_STAGE_PARTIAL call with the same arguments;
+ * both bits are the fused call.  split_k == 1 has a single launch, which belongs
+ * to QF_STAGE_PARTIAL. */
+#define QF_STAGE_PARTIAL 1
+#define QF_STAGE_COMBINE 2
+int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* args, int32_t stages,
+                                              void* stream);
+
+/* Which partial kernel qf_grouped_splitk_decode_attention would launch for these
+ * arguments on the current device, without launching anything: *kernel is
+ * QF_KERNEL_PARTITIONED (one CTA per sequence, KV head and split; also the
+ * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math, FP8 pools) or
+ * QF_KERNEL_PERSISTENT_MMA (tensor-core math); *ctas_per_head is the number of
+ * resident CTAs that share one KV head's pages (0 for QF_KERNEL_PARTITIONED). */
+#define QF_KERNEL_PARTITIONED 0
+#define QF_KERNEL_PERSISTENT 1
+#define QF_KERNEL_PERSISTENT_MMA 2
+int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args, int32_t* kernel,
+                                            int32_t* ctas_per_head);
 
 /* The same computation as qf_grouped_splitk_decode_attention, for callers that
  * cannot provide (or allocate) the split-K partial buffers.  No counterpart in

@@ -31,8 +31,11 @@ EXPORTED_SYMBOLS = (
     "qf_quantize_kv_pages_e4m3", "qf_grouped_gqa_splitk_partial_out", "qf_splitk_reduce",
     "qf_grouped_splitk_decode_attention", "qf_grouped_gqa_splitk_diagnostics",
     "qf_grouped_gqa_splitk_profile_out", "qf_device_status", "qf_set_tuning",
-    "qf_grouped_splitk_decode_attention_static",
+    "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
+    "qf_grouped_splitk_decode_attention_plan",
 )
+KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
+STAGE_PARTIAL, STAGE_COMBINE = 1, 2
 STATIC_SCRATCH_BYTES = 16 << 20
 
 
@@ -116,6 +119,10 @@ def library():
     lib.qf_grouped_gqa_splitk_profile_out.argtypes = [POINTER(DecodeAttentionArgs), c_void_p, c_void_p]
     lib.qf_grouped_splitk_decode_attention.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
     lib.qf_grouped_splitk_decode_attention_static.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
+    lib.qf_grouped_splitk_decode_attention_plan.argtypes = [
+        POINTER(DecodeAttentionArgs), POINTER(c_int32), POINTER(c_int32)]
+    lib.qf_grouped_splitk_decode_attention_stages.argtypes = [
+        POINTER(DecodeAttentionArgs), c_int32, c_void_p]
     lib.qf_splitk_reduce.argtypes = (
         [c_void_p] * 3 + [c_int64] * 7 + [c_void_p] + [c_int64] * 3 + [c_int32] * 5 + [c_void_p])
     lib.qf_grouped_gqa_splitk_diagnostics.argtypes = [c_int32, c_int32, c_int32, POINTER(c_int64)]
@@ -189,6 +196,14 @@ class device_of:
         if self._guard is not None:
             self._guard.__exit__(*exc)
         return False
+
+
+def fused_kernel_plan(args):
+    """(kernel name, resident CTAs per KV head) the fused attention call would use."""
+    kernel, ctas = c_int32(0), c_int32(0)
+    check(library().qf_grouped_splitk_decode_attention_plan(
+        ctypes.byref(args), ctypes.byref(kernel), ctypes.byref(ctas)))
+    return KERNEL_NAMES[kernel.value], ctas.value
 
 
 def device_status(reset=True):

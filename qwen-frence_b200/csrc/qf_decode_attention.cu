@@ -589,17 +589,25 @@ int qf_splitk_reduce(const float* partial_out, const float* partial_max, const f
   return qf::launch_reduce(r, batch, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
-int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {
+int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* args, int32_t stages,
+                                              void* stream) {
   int rc = qf::validate(args, true);
   if (rc != QF_OK) return rc;
+  QF_REQUIRE(stages >= 1 && stages <= (QF_STAGE_PARTIAL | QF_STAGE_COMBINE),
+             "stages must be QF_STAGE_PARTIAL, QF_STAGE_COMBINE or both");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (args->split_k == 1) return qf::launch_partial<false>(args, true, nullptr, s);
+  if (args->split_k == 1) {
+    return (stages & QF_STAGE_PARTIAL) ? qf::launch_partial<false>(args, true, nullptr, s) : QF_OK;
+  }
   if (args->batch == 0) return QF_OK;
   const qf::FusedKernel kind = qf::choose_fused_kernel(args);
   const bool streamed = kind != qf::FusedKernel::kPartitioned;
-  rc = streamed ? qf::launch_persistent_partial(args, kind, s)
-                : qf::launch_partial<false>(args, false, nullptr, s);
-  if (rc != QF_OK) return rc;
+  if (stages & QF_STAGE_PARTIAL) {
+    rc = streamed ? qf::launch_persistent_partial(args, kind, s)
+                  : qf::launch_partial<false>(args, false, nullptr, s);
+    if (rc != QF_OK) return rc;
+  }
+  if (!(stages & QF_STAGE_COMBINE)) return QF_OK;
   qf::ReduceParams r{};
   r.po = args->partial_out, r.pm = args->partial_max, r.ps = args->partial_sum;
   const int64_t hq = args->q_heads, d = args->head_dim, k = args->split_k;
@@ -609,6 +617,26 @@ int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, voi
   r.q_heads = args->q_heads, r.head_dim = args->head_dim, r.split_k = args->split_k;
   r.seq_lens = args->seq_lens, r.lens_stride = args->lens_stride, r.lens_dtype = args->lens_dtype;
   return qf::launch_reduce(r, args->batch, args->dtype, streamed, s);
+}
+
+int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args, int32_t* kernel,
+                                            int32_t* ctas_per_head) {
+  const int rc = qf::validate(args, false);
+  if (rc != QF_OK) return rc;
+  QF_REQUIRE(kernel != nullptr && ctas_per_head != nullptr, "outputs must not be null");
+  *kernel = QF_KERNEL_PARTITIONED, *ctas_per_head = 0;
+  if (args->split_k == 1 || args->batch == 0) return QF_OK;
+  const qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  if (kind == qf::FusedKernel::kPartitioned) return QF_OK;
+  const int resident = qf::stream_ctas_on_current_device();
+  const bool mma = kind == qf::FusedKernel::kTensorCore;
+  *kernel = mma ? QF_KERNEL_PERSISTENT_MMA : QF_KERNEL_PERSISTENT;
+  *ctas_per_head = (mma ? resident / QF_MIN_CTAS : resident) / args->kv_heads;
+  return QF_OK;
+}
+
+int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {
+  return qf_grouped_splitk_decode_attention_stages(args, QF_STAGE_PARTIAL | QF_STAGE_COMBINE, stream);
 }
 
 int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_fp8, int64_t* info) {

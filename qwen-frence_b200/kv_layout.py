@@ -137,6 +137,34 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
     return int(max(1, min(wanted, cap, 65535)))
 
 
+def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SIZE):
+    """Host restatement of how the persistent partial kernels cut one KV head's work.
+
+    The sequences' units (pages for the tensor-core kernel, page pairs for the
+    CUDA-core one) are concatenated; CTA c takes units [c*share, (c+1)*share) with
+    share = max(ceil(total / ctas_per_head), ceil(longest / (split_k - 1))), so no
+    sequence is cut into more than split_k pieces.  Returns (share, pieces) where a
+    piece is (cta, sequence, first unit within the sequence, units, split slot).
+    """
+    if split_k < 2 or ctas_per_head < 1:
+        raise ValueError("the persistent kernels need split_k >= 2 and at least one CTA per head")
+    units = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
+    total, longest = sum(units), max(units, default=0)
+    if total == 0:
+        return 0, []
+    share = max(-(-total // ctas_per_head), -(-longest // (split_k - 1)))
+    pieces, first = [], 0
+    for sequence, count in enumerate(units):
+        position = first
+        while position < first + count:
+            cta = position // share
+            stop = min(first + count, (cta + 1) * share)
+            pieces.append((cta, sequence, position - first, stop - position, cta - first // share))
+            position = stop
+        first += count
+    return share, pieces
+
+
 def kv_bytes_per_layer(seq_lens, *, kv_heads=KV_HEADS, head_dim=HEAD_DIM, elem_bytes=2):
     """Unique K+V bytes one layer's attention must read: sum_b T_b * 2 * kv * D * e
     (same count as unique_bytes in

@@ -271,3 +271,35 @@ def test_partition_policies(package):
     assert sharding.shard_pages([17, 16, 1], [[0, 1], [2]]) == [3, 1]
     with pytest.raises(ValueError):
         sharding.partition_sequences(lengths, 0)
+
+
+def test_persistent_schedule_respects_split_slots(package):
+    """The share rule of the persistent kernels: pieces tile every sequence exactly,
+    CTAs get at most `share` units, and no sequence needs more than split_k slots."""
+    import random
+
+    schedule = package.kv_layout.persistent_schedule
+    rng = random.Random(7)
+    for trial in range(200):
+        batch = rng.choice([1, 2, 5, 64, 300])
+        lengths = [rng.choice([0, 1, 15, 16, 17, 500, rng.randint(0, 9000)]) for _ in range(batch)]
+        split_k = rng.choice([2, 3, 10, 64])
+        ctas = rng.choice([1, 7, 74, 148])
+        unit = rng.choice([16, 32])
+        share, pieces = schedule(lengths, split_k=split_k, ctas_per_head=ctas, unit_tokens=unit)
+        units = [-(-t // unit) for t in lengths]
+        covered = [0] * batch
+        load = {}
+        for cta, sequence, first, count, slot in pieces:
+            assert count >= 1 and first == covered[sequence] and 0 <= slot < split_k
+            assert 0 <= cta < ctas
+            covered[sequence] += count
+            load[cta] = load.get(cta, 0) + count
+        assert covered == units
+        assert all(v <= share for v in load.values())
+        slots = {}
+        for cta, sequence, first, count, slot in pieces:
+            slots.setdefault(sequence, []).append(slot)
+        assert all(s == list(range(len(s))) for s in slots.values())
+    with pytest.raises(ValueError):
+        schedule([5], split_k=1, ctas_per_head=4)
