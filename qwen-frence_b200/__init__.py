@@ -15,7 +15,8 @@ current torch stream; none has a CPU fallback):
     native_grouped_splitk_decode_attention,
     grouped_gqa_splitk_partial_out,
     native_grouped_decode_diagnostics,
-    native_grouped_stage_cycles                            custom_kernels/paged_decode_native_grouped.py
+    native_grouped_stage_cycles,
+    native_grouped_persistent_timeline                     custom_kernels/paged_decode_native_grouped.py
     quantize_kv_pool_e4m3, dequantize_kv_pool_e4m3,
     native_decode_rope_kv_write_fp8, packed_qkv_rope_cache_fp8,
     grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
@@ -42,6 +43,7 @@ _EXPORTS = {
     "grouped_gqa_splitk_partial_out": "paged_decode_native_grouped",
     "native_grouped_decode_diagnostics": "paged_decode_native_grouped",
     "native_grouped_stage_cycles": "paged_decode_native_grouped",
+    "native_grouped_persistent_timeline": "paged_decode_native_grouped",
     "quantize_kv_pool_e4m3": "fp8_paged_kv",
     "dequantize_kv_pool_e4m3": "fp8_paged_kv",
     "native_decode_rope_kv_write_fp8": "fp8_paged_kv",

@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_splitk_decode_attention", "qf_grouped_gqa_splitk_diagnostics",
     "qf_grouped_gqa_splitk_profile_out", "qf_device_status", "qf_set_tuning",
     "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
-    "qf_grouped_splitk_decode_attention_plan",
+    "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -121,6 +121,8 @@ def library():
     lib.qf_grouped_splitk_decode_attention_static.argtypes = [POINTER(DecodeAttentionArgs), c_void_p]
     lib.qf_grouped_splitk_decode_attention_plan.argtypes = [
         POINTER(DecodeAttentionArgs), POINTER(c_int32), POINTER(c_int32)]
+    lib.qf_grouped_splitk_persistent_timeline.argtypes = [
+        POINTER(DecodeAttentionArgs), c_void_p, c_void_p]
     lib.qf_grouped_splitk_decode_attention_stages.argtypes = [
         POINTER(DecodeAttentionArgs), c_int32, c_void_p]
     lib.qf_splitk_reduce.argtypes = (

@@ -32,6 +32,7 @@ int* device_status_word();
 
 // Status codes kernels may record (1 is reserved).
 constexpr int kStatusBadPageId = 2;
+constexpr int kStatusMergeTimeout = 3;  // a warp gave up waiting for an earlier piece's merge
 
 // ---- device side ---------------------------------------------------------
 #ifdef __CUDACC__

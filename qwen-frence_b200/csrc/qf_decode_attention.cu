@@ -347,9 +347,9 @@ size_t mma_smem_bytes() {
 }
 
 // One CTA per SM (its rings take most of the shared memory).
-template <typename T>
+template <typename T, bool PROFILE>
 int launch_mma(const FastParams& p, cudaStream_t stream) {
-  auto kernel = decode_mma_kernel<T>;
+  auto kernel = decode_mma_kernel<T, PROFILE>;
   const size_t smem = mma_smem_bytes();
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
@@ -461,12 +461,19 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 
-int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kind, cudaStream_t stream) {
+int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kind, cudaStream_t stream,
+                              long long* timeline = nullptr) {
   int* status = status_word_for_current_device();
   QF_REQUIRE(status != nullptr, "could not resolve the device status word");
-  const FastParams p = fast_params(a, nullptr, nullptr, status);
+  const FastParams p = fast_params(a, nullptr, timeline, status);
+  if (timeline != nullptr) {
+    QF_REQUIRE(kind == FusedKernel::kTensorCore, "only the tensor-core kernel has a timeline variant");
+    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half, true>(p, stream)
+                                    : launch_mma<__nv_bfloat16, true>(p, stream);
+  }
   if (kind == FusedKernel::kTensorCore) {
-    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half>(p, stream) : launch_mma<__nv_bfloat16>(p, stream);
+    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half, false>(p, stream)
+                                    : launch_mma<__nv_bfloat16, false>(p, stream);
   }
   if (a->kv_fp8) {
     return a->dtype == QF_DTYPE_F16 ? launch_stream<__half, true>(p, stream)
@@ -633,6 +640,19 @@ int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args
   *kernel = mma ? QF_KERNEL_PERSISTENT_MMA : QF_KERNEL_PERSISTENT;
   *ctas_per_head = (mma ? resident / QF_MIN_CTAS : resident) / args->kv_heads;
   return QF_OK;
+}
+
+int qf_grouped_splitk_persistent_timeline(const qf_decode_attention_args* args, int64_t* timeline,
+                                          void* stream) {
+  const int rc = qf::validate(args, true);
+  if (rc != QF_OK) return rc;
+  QF_REQUIRE(timeline != nullptr, "timeline must not be null");
+  QF_REQUIRE(args->split_k >= 2 && args->batch >= 1, "the persistent kernels need split_k >= 2 and a batch");
+  const qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  QF_REQUIRE(kind == qf::FusedKernel::kTensorCore,
+             "these arguments do not select the tensor-core persistent kernel");
+  return qf::launch_persistent_partial(args, kind, static_cast<cudaStream_t>(stream),
+                                       reinterpret_cast<long long*>(timeline));
 }
 
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {

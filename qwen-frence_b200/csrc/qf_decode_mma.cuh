@@ -32,7 +32,18 @@
 // registers, 32 pages per warp at a time, fetched a chunk ahead.
 //
 // Pieces, split slots and the end-of-sequence mark are those of the streamed
-// CUDA-core kernel, and so is the combine.
+// CUDA-core kernel, and so is the combine.  The merge of a piece's per-warp states
+// has no CTA-wide barrier (a barrier at every sequence boundary stalls all eight
+// copy pipelines for the spread between the fastest and the slowest warp, measured
+// at 2.2 - 2.7 us per piece): a warp that has finished its pages of a piece deposits
+// (accumulator, offset, sum) in shared memory, bumps the piece's arrival counter
+// and goes on with the next piece; the warp whose arrival completes the count
+// merges the deposits and stores the piece.  Deposits are double-buffered by piece
+// parity; before depositing piece r a warp checks that piece r - 2 has been
+// merged.  That check can only fail when the warp is two sequences ahead of the
+// slowest one; it then polls, for a bounded number of rounds, a flag that only
+// depends on warps behind it (the warp that is furthest behind never waits, so
+// the poll cannot deadlock); running out of rounds raises status 3 and goes on.
 #pragma once
 
 #include "qf_decode_stream.cuh"
@@ -45,7 +56,10 @@ constexpr int kTileBytes16 = QF_PAGE_SIZE * QF_HEAD_DIM * 2;   // K or V of one 
 constexpr int kRingTiles = 5;                                  // per warp
 constexpr int kTilesAhead = 4;                                 // in flight ahead of the math
 constexpr int kPaddedHeads = 8;
-constexpr int kMmaMergeFloats = kMmaWarps * QF_HEAD_DIM * kPaddedHeads;  // 32 KB
+constexpr int kDepositHeadStride = QF_HEAD_DIM + 8;                      // floats; the pad spreads the heads over banks
+constexpr int kDepositFloats = QF_GQA_GROUP * kDepositHeadStride;        // one warp's O^T of a piece: 3.2 KB
+constexpr int kMmaMergeFloats = 2 * kMmaWarps * kDepositFloats;          // two piece parities: 48 KB
+constexpr int kMergePollRounds = 1 << 22;                                // bound of the (rare) wait for piece r - 2
 
 template <typename T>
 struct MmaOps;
@@ -96,17 +110,38 @@ __device__ __forceinline__ void wait_tiles_ahead() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kTilesAhead - 1) : "memory");
 }
 
-template <typename T>
+__device__ __forceinline__ long long global_nanoseconds() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// PROFILE: thread 0 of every CTA with work also writes kTimelineColumns values to
+// p.cycles[kTimelineColumns * blockIdx.x ..]: ns (%globaltimer, one clock for all
+// SMs) at entry, when the work list was built, when its page ids were known, when
+// its first tile had landed, at exit (of its last warp); then the pages of its
+// share, the pieces that held pages of warp 0, and the ns warp 0 spent depositing
+// and merging piece states.
+constexpr int kTimelineColumns = 8;
+template <typename T, bool PROFILE>
 __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const StreamParams sp) {
   using Ops = MmaOps<T>;
   const FastParams& p = sp.f;
   // [kMmaWarps][kRingTiles] tiles of 4 KB, then kMmaMergeFloats of merge scratch
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ WorkList work;  // units are pages
-  __shared__ float warp_offset[kMmaWarps][kPaddedHeads];
-  __shared__ float warp_sum[kMmaWarps][kPaddedHeads];
+  // per piece parity: the warps' softmax states, the weights the merging warp gives
+  // them, how many warps have deposited, and the last piece merged
+  __shared__ float warp_offset[2][kMmaWarps][kPaddedHeads];
+  __shared__ float warp_sum[2][kMmaWarps][kPaddedHeads];
+  __shared__ float warp_weight[2][kMmaWarps][kPaddedHeads];
+  __shared__ int arrived[2];
+  __shared__ int merged[2];
 
   constexpr unsigned kFull = 0xffffffffu;
+  long long t_entry = 0, t_list = 0, t_ids = 0, t_first = 0, t_merge = 0;
+  int pieces = 0;
+  if (PROFILE) t_entry = global_nanoseconds();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -115,10 +150,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   const int kv_head = blockIdx.x / sp.ctas_per_head;
   const int cta = blockIdx.x - kv_head * sp.ctas_per_head;
 
-  // ---- the page list of this launch and this CTA's share of it ----
+  if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
+  // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----
   const int longest = build_work_list<QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
   const int* first_page = work.first_unit;
   const int total = first_page[kMaxStreamBatch];
+  if (PROFILE) t_list = global_nanoseconds();
   if (total == 0) return;
   const int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
                         (longest + p.split_k - 2) / (p.split_k - 1));
@@ -164,6 +201,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   int id_now, rows_now, id_next, rows_next;
   describe(0, id_now, rows_now);
   describe(1, id_next, rows_next);
+  if (PROFILE) t_ids = id_now + id_next > -100 ? global_nanoseconds() : 0;  // after the ids have arrived
 
   // Tile t of this warp is K (t even) or V (t odd) of its page t / 2, in ring slot t % 5.
   int fill_tile = 0, fill_slot = 0;
@@ -214,28 +252,45 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   const uint32_t v_chunk_xor = ((mat & 1) ^ (lane & 7)) << 4;
   const uint32_t ring_addr = smem_u32(ring);
 
-  uint32_t q_frag[8][2];  // B operand Q^T: [k-step][dims 2q.. | dims 8 + 2q..] of head g (0 for g >= 6)
-  auto load_q = [&](int sequence) {
+  // B operand Q^T: [k-step][dims 2q.. | dims 8 + 2q..] of head g (0 for g >= 6); the
+  // rows of the sequence this warp works on next are loaded a piece ahead.
+  uint32_t q_frag[8][2], q_ahead[8][2];
+  auto load_q = [&](int sequence, uint32_t (&frag)[8][2]) {
     const T* row = static_cast<const T*>(p.q) + sequence * p.q_sb +
                    (static_cast<int64_t>(kv_head) * QF_GQA_GROUP + (g < QF_GQA_GROUP ? g : 0)) * p.q_sh + 2 * q;
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
       const uint32_t lo = *reinterpret_cast<const uint32_t*>(row + 16 * s);
       const uint32_t hi = *reinterpret_cast<const uint32_t*>(row + 16 * s + 8);
-      q_frag[s][0] = g < QF_GQA_GROUP ? lo : 0u;
-      q_frag[s][1] = g < QF_GQA_GROUP ? hi : 0u;
+      frag[s][0] = g < QF_GQA_GROUP ? lo : 0u;
+      frag[s][1] = g < QF_GQA_GROUP ? hi : 0u;
     }
   };
 
-  float* merge = reinterpret_cast<float*>(smem + kMmaWarps * kRingTiles * kTileBytes16);
+  float* deposits = reinterpret_cast<float*>(smem + kMmaWarps * kRingTiles * kTileBytes16);
   float acc[8][4];  // O^T: [m-tile j][(dim 16j+g, head 2q) (16j+g, 2q+1) (16j+g+8, 2q) (16j+g+8, 2q+1)]
 
+  // Pieces are numbered by `rank` in the order of the sequences; every warp walks
+  // the same list but only stops at pieces that hold some of its pages.
   int piece_seq = sequence_of_unit(work, p.batch, begin);
+  int rank = 0;
   int page = begin + warp;  // global index of this warp's next page
   int read_slot = 0;
-  load_q(piece_seq);
+  // Move (piece_seq, rank) forward to the piece that holds `target` (< end).
+  auto advance_to = [&](int target) {
+    while (piece_seq < p.batch - 1 && first_page[piece_seq + 1] <= target) {
+      ++piece_seq;
+      if (first_page[piece_seq + 1] > first_page[piece_seq]) ++rank;
+    }
+  };
+  if (page < end) {
+    advance_to(page);
+    load_q(piece_seq, q_ahead);
+  }
 
-  while (true) {
+  while (page < end) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) q_frag[s][0] = q_ahead[s][0], q_frag[s][1] = q_ahead[s][1];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -244,12 +299,23 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     float sum[2] = {0.f, 0.f};                 // over this lane's tokens
     const int seq_first = first_page[piece_seq];
     const int seq_len = work.length[piece_seq];
+    const int piece_begin = max(seq_first, begin);
     const int piece_end = min(first_page[piece_seq + 1], end);
+    const int done_seq = piece_seq, done_rank = rank;
+    {
+      // Q rows of the sequence that holds this warp's first page after this piece
+      const int after = page + ((piece_end - page + kMmaWarps - 1) / kMmaWarps) * kMmaWarps;
+      if (after < end) {
+        advance_to(after);
+        load_q(piece_seq, q_ahead);
+      }
+    }
 
     for (; page < piece_end; page += kMmaWarps) {
       // ---- scores S^T = K Q^T ----
       wait_tiles_ahead();
       __syncwarp();
+      if (PROFILE && t_first == 0) t_first = global_nanoseconds();
       issue_tile();
       const uint32_t k_tile = ring_addr + read_slot * kTileBytes16 + k_row_offset;
       read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
@@ -310,84 +376,129 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       }
     }
 
-    // ---- the piece is done: where it goes, what comes next ----
-    const int done_seq = piece_seq;
-    const bool sequence_ends = first_page[done_seq + 1] <= end;
-    const int split_slot = cta - seq_first / share;
-    bool more = piece_end < end;
-    if (more) {
-      do {
-        ++piece_seq;
-      } while (piece_seq < p.batch - 1 && first_page[piece_seq + 1] == first_page[piece_seq]);
-      // A sequence without pages cannot come up while pages remain; the test keeps
-      // the loop bounded whatever the prefix holds.
-      more = first_page[piece_seq + 1] > first_page[piece_seq] && first_page[piece_seq] >= piece_end;
+    // ---- deposit this warp's state of the piece; the last warp to arrive merges ----
+    long long t_piece = 0;
+    if (PROFILE) t_piece = global_nanoseconds(), ++pieces;
+    const int parity = done_rank & 1;
+    if (lane == 0) {
+      // Piece done_rank - 2 used the same buffers: they are free once it is merged.
+      int rounds = 0;
+      while (*reinterpret_cast<volatile int*>(&merged[parity]) < done_rank - 2) {
+        if (++rounds > kMergePollRounds) {
+          atomicExch(p.status, kStatusMergeTimeout);
+          break;
+        }
+        __nanosleep(64);
+      }
+      __threadfence_block();
     }
-    if (more) load_q(piece_seq);  // in flight during the merge
-
-    // ---- merge the eight warps' states and store the piece ----
+    __syncwarp();
+    float* mine = deposits + (parity * kMmaWarps + warp) * kDepositFloats;  // [6 heads][dim]
+    if (q < QF_GQA_GROUP / 2) {
+      float* even = mine + (2 * q) * kDepositHeadStride + g;
+      float* odd = even + kDepositHeadStride;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        even[16 * j] = acc[j][0], odd[16 * j] = acc[j][1];
+        even[16 * j + 8] = acc[j][2], odd[16 * j + 8] = acc[j][3];
+      }
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float total = sum[h];
       total += __shfl_xor_sync(kFull, total, 4);
       total += __shfl_xor_sync(kFull, total, 8);
       total += __shfl_xor_sync(kFull, total, 16);
-      if (g == 0) warp_offset[warp][2 * q + h] = offset[h], warp_sum[warp][2 * q + h] = total;
+      if (g == 0) warp_offset[parity][warp][2 * q + h] = offset[h], warp_sum[parity][warp][2 * q + h] = total;
     }
-    __syncthreads();
-    float piece_offset[2], factor[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float top = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, warp_offset[w][2 * q + h]);
-      piece_offset[h] = top;
-      factor[h] = offset[h] == -INFINITY ? 0.f : fast_exp2(offset[h] - top);
+    __syncwarp();
+    // Warps with pages in the piece: consecutive pages go to consecutive warps.
+    const int piece_pages = piece_end - piece_begin;
+    const int first_warp = (piece_begin - begin) & (kMmaWarps - 1);
+    const int participants = min(piece_pages, kMmaWarps);
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&arrived[parity], 1) == participants - 1;
+      __threadfence_block();
     }
-    // scratch [warp][dim][8 heads]: a lane stores heads (2q, 2q+1) of dims 16j+g, 16j+g+8
-    float* mine = merge + warp * (QF_HEAD_DIM * kPaddedHeads);
+    last = __shfl_sync(kFull, last, 0);
+    if (last) {
+      // lane = (warp w = lane / 4, head pair q): weight of w's deposit, per head
+      const int w = lane >> 2;
+      const bool took_part = ((w - first_warp) & (kMmaWarps - 1)) < piece_pages;
+      float top[2], total[2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      *reinterpret_cast<float2*>(mine + (16 * j + g) * kPaddedHeads + 2 * q) =
-          make_float2(acc[j][0] * factor[0], acc[j][1] * factor[1]);
-      *reinterpret_cast<float2*>(mine + (16 * j + g + 8) * kPaddedHeads + 2 * q) =
-          make_float2(acc[j][2] * factor[0], acc[j][3] * factor[1]);
-    }
-    __syncthreads();
-    const bool slot_ok = split_slot >= 0 && split_slot < p.split_k;  // holds by the choice of `share`
-    const int64_t partial_row =
-        (static_cast<int64_t>(done_seq) * p.split_k + split_slot) * p.q_heads +
-        static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
-    if (slot_ok) {
-#pragma unroll
-      for (int i = 0; i < (QF_GQA_GROUP * QF_HEAD_DIM) / kFastThreads; ++i) {
-        const int e = tid + i * kFastThreads;  // (head, dim) flattened
-        const int head = e >> 7, d = e & 127;
-        float value = 0.f;
-#pragma unroll
-        for (int w = 0; w < kMmaWarps; ++w) value += merge[(w * QF_HEAD_DIM + d) * kPaddedHeads + head];
-        p.partial_out[partial_row * QF_HEAD_DIM + e] = value;
+      for (int h = 0; h < 2; ++h) {
+        const float mw = took_part ? warp_offset[parity][w][2 * q + h] : -INFINITY;
+        float best = mw;
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 4));
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 8));
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 16));
+        const float weight = mw == -INFINITY ? 0.f : fast_exp2(mw - best);
+        warp_weight[parity][w][2 * q + h] = weight;
+        float part = took_part ? warp_sum[parity][w][2 * q + h] * weight : 0.f;
+        part += __shfl_xor_sync(kFull, part, 4);
+        part += __shfl_xor_sync(kFull, part, 8);
+        part += __shfl_xor_sync(kFull, part, 16);
+        top[h] = best, total[h] = part;
       }
-      if (tid < QF_GQA_GROUP) {
-        float top = -INFINITY;
-        for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, warp_offset[w][tid]);
-        float total = 0.f;
-        for (int w = 0; w < kMmaWarps; ++w) {
-          const float mw = warp_offset[w][tid];
-          if (mw != -INFINITY) total += warp_sum[w][tid] * fast_exp2(mw - top);
+      __syncwarp();
+      const int split_slot = cta - seq_first / share;
+      const bool slot_ok = split_slot >= 0 && split_slot < p.split_k;  // holds by the choice of `share`
+      const int64_t partial_row =
+          (static_cast<int64_t>(done_seq) * p.split_k + split_slot) * p.q_heads +
+          static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
+      if (slot_ok) {
+        // A lane sums four dims (4 lane .. 4 lane + 3) of each head over the deposits.
+        const float* base = deposits + parity * kMmaWarps * kDepositFloats + 4 * lane;
+        float4 value[QF_GQA_GROUP];
+#pragma unroll
+        for (int head = 0; head < QF_GQA_GROUP; ++head) value[head] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < participants; ++k) {
+          const int ww = (first_warp + k) & (kMmaWarps - 1);
+#pragma unroll
+          for (int head = 0; head < QF_GQA_GROUP; ++head) {
+            const float weight = warp_weight[parity][ww][head];
+            const float4 part =
+                *reinterpret_cast<const float4*>(base + ww * kDepositFloats + head * kDepositHeadStride);
+            value[head].x += part.x * weight, value[head].y += part.y * weight;
+            value[head].z += part.z * weight, value[head].w += part.w * weight;
+          }
         }
-        // natural-log units, as the combine expects
-        p.partial_max[partial_row + tid] = top * kLn2;
-        p.partial_sum[partial_row + tid] = total;
-        if (sequence_ends && split_slot + 1 < p.split_k) {
-          p.partial_sum[partial_row + p.q_heads + tid] = -1.f;  // no further pieces of this sequence
+        float4* row = reinterpret_cast<float4*>(p.partial_out + partial_row * QF_HEAD_DIM) + lane;
+#pragma unroll
+        for (int head = 0; head < QF_GQA_GROUP; ++head) row[head * (QF_HEAD_DIM / 4)] = value[head];
+        if (w == 0 && q < QF_GQA_GROUP / 2) {
+          // lanes 0..2 hold (top, total) of heads (2q, 2q+1); natural-log units for the combine
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            p.partial_max[partial_row + 2 * q + h] = top[h] * kLn2;
+            p.partial_sum[partial_row + 2 * q + h] = total[h];
+            if (first_page[done_seq + 1] <= end && split_slot + 1 < p.split_k) {
+              p.partial_sum[partial_row + p.q_heads + 2 * q + h] = -1.f;  // no further pieces of this sequence
+            }
+          }
         }
       }
+      __syncwarp();
+      if (lane == 0) {
+        arrived[parity] = 0;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&merged[parity]) = done_rank;
+      }
     }
-    if (!more) break;
-    __syncthreads();  // warp_offset / warp_sum / scratch are rewritten by the next piece
+    if (PROFILE) t_merge += global_nanoseconds() - t_piece;
   }
   wait_all_copies();
+  if (PROFILE) {
+    __syncthreads();  // the CTA's exit time is that of its last warp
+    if (p.cycles != nullptr && tid == 0) {
+      long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * kTimelineColumns;
+      dst[0] = t_entry, dst[1] = t_list, dst[2] = t_ids, dst[3] = t_first, dst[4] = global_nanoseconds();
+      dst[5] = count, dst[6] = pieces, dst[7] = t_merge;
+    }
+  }
 }
 
 }  // namespace

@@ -236,3 +236,44 @@ def native_grouped_stage_cycles(
         cabi.check(cabi.library().qf_grouped_gqa_splitk_profile_out(
             ctypes.byref(args), cycles.data_ptr(), cabi.stream_pointer(q.device)))
     return cycles
+
+
+def native_grouped_persistent_timeline(
+    q, k_pool, v_pool, block_table, seq_lens, *, split_k, scale=None
+):
+    """Run the instrumented tensor-core persistent partial pass once.
+
+    Returns int64 [Hkv * ctas_per_head, 8]: per CTA {ns at entry, ns when the work
+    list was built, ns when its page ids were known, ns when its first K tile had
+    landed, ns at exit (of its last warp), pages in its share, pieces that held
+    pages of its warp 0, ns warp 0 spent depositing and merging piece states} on the
+    GPU's global timer; rows of CTAs without work stay zero.  Raises RuntimeError when these arguments
+    would not run that kernel (FP8 pools, few split slots, batch above 1024).
+    The counterpart of `native_grouped_stage_cycles` for a kernel whose CTAs are
+    not tied to one (sequence, head, split).
+    """
+    import ctypes
+
+    import torch
+
+    batch, query_heads, head_dim = _check_layout(q, k_pool, v_pool)
+    _require(isinstance(split_k, int) and split_k >= 2, "split_k must exceed one")
+    if scale is None:
+        scale = head_dim ** -0.5
+    cabi = _extension()
+    _check_metadata(torch, q, k_pool, v_pool, block_table, seq_lens)
+    partial_out = torch.empty((batch, split_k, query_heads, head_dim),
+                              dtype=torch.float32, device=q.device)
+    partial_max = torch.empty((batch, split_k, query_heads), dtype=torch.float32, device=q.device)
+    partial_sum = torch.empty_like(partial_max)
+    splitk = _sibling("paged_decode_grouped_splitk")
+    args = splitk.fill_attention_args(
+        cabi, q, k_pool, v_pool, block_table, seq_lens, split_k=split_k, scale=scale,
+        partials=(partial_out, partial_max, partial_sum), out=torch.empty_like(q))
+    with cabi.device_of(q):
+        _, ctas_per_head = cabi.fused_kernel_plan(args)
+        timeline = torch.zeros((max(ctas_per_head, 1) * k_pool.shape[2], 8), dtype=torch.int64,
+                               device=q.device)
+        cabi.check(cabi.library().qf_grouped_splitk_persistent_timeline(
+            ctypes.byref(args), timeline.data_ptr(), cabi.stream_pointer(q.device)))
+    return timeline
