@@ -29,7 +29,10 @@
 // them: no barrier inside a piece, no spin wait anywhere.  Rows past the end of a
 // sequence are written as zeros instead of copied, so that no NaN from an unused
 // cache row reaches an MMA.  Page ids, and the rows a page holds, sit in lane
-// registers, 32 pages per warp at a time, fetched a chunk ahead.
+// registers, 32 pages per warp at a time, fetched a chunk ahead.  The Q rows of a
+// sequence travel through the same ring, as one more tile in front of the warp's
+// first page of that sequence: a plain global load of Q at a sequence boundary
+// would queue behind the 128 KB of page traffic the SM has in flight.
 //
 // Pieces, split slots and the end-of-sequence mark are those of the streamed
 // CUDA-core kernel, and so is the combine.  The merge of a piece's per-warp states
@@ -56,6 +59,7 @@ constexpr int kTileBytes16 = QF_PAGE_SIZE * QF_HEAD_DIM * 2;   // K or V of one 
 constexpr int kRingTiles = 5;                                  // per warp
 constexpr int kTilesAhead = 4;                                 // in flight ahead of the math
 constexpr int kPaddedHeads = 8;
+constexpr int kQRowBytes = QF_HEAD_DIM * 2 + 16;                        // Q tile: head stride, padded against bank conflicts
 constexpr int kDepositHeadStride = QF_HEAD_DIM + 8;                      // floats; the pad spreads the heads over banks
 constexpr int kDepositFloats = QF_GQA_GROUP * kDepositHeadStride;        // one warp's O^T of a piece: 3.2 KB
 constexpr int kMmaMergeFloats = 2 * kMmaWarps * kDepositFloats;          // two piece parities: 48 KB
@@ -110,6 +114,22 @@ __device__ __forceinline__ void wait_tiles_ahead() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kTilesAhead - 1) : "memory");
 }
 
+// Shared-memory flag operations with CTA-scope release / acquire semantics.
+__device__ __forceinline__ int add_acq_rel(int* counter, int value) {
+  int old;
+  asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], %2;"
+               : "=r"(old) : "r"(smem_u32(counter)), "r"(value) : "memory");
+  return old;
+}
+__device__ __forceinline__ int load_acquire(const int* flag) {
+  int value;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(value) : "r"(smem_u32(flag)) : "memory");
+  return value;
+}
+__device__ __forceinline__ void store_release(int* flag, int value) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(flag)), "r"(value) : "memory");
+}
+
 __device__ __forceinline__ long long global_nanoseconds() {
   long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -120,9 +140,9 @@ __device__ __forceinline__ long long global_nanoseconds() {
 // p.cycles[kTimelineColumns * blockIdx.x ..]: ns (%globaltimer, one clock for all
 // SMs) at entry, when the work list was built, when its page ids were known, when
 // its first tile had landed, at exit (of its last warp); then the pages of its
-// share, the pieces that held pages of warp 0, and the ns warp 0 spent depositing
-// and merging piece states.
-constexpr int kTimelineColumns = 8;
+// share, the pieces that held pages of warp 0, the ns warp 0 spent depositing its
+// piece states, the ns it spent merging pieces, and the pieces it merged.
+constexpr int kTimelineColumns = 10;
 template <typename T, bool PROFILE>
 __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const StreamParams sp) {
   using Ops = MmaOps<T>;
@@ -139,8 +159,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   __shared__ int merged[2];
 
   constexpr unsigned kFull = 0xffffffffu;
-  long long t_entry = 0, t_list = 0, t_ids = 0, t_first = 0, t_merge = 0;
-  int pieces = 0;
+  long long t_entry = 0, t_list = 0, t_ids = 0, t_first = 0, t_deposit = 0, t_merge = 0;
+  int pieces = 0, merges = 0;
   if (PROFILE) t_entry = global_nanoseconds();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -182,10 +202,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     fill_offset[j] = r * 256 + (((lane & 15) ^ (r & 7)) << 4);
   }
 
-  // Page ids and row counts of 32 of this warp's pages at a time, one per lane.
-  auto describe = [&](int chunk, int& id, int& rows) {
+  // Page ids and row counts of 32 of this warp's pages at a time, one per lane, and
+  // the sequence whose Q rows must precede the page (-1 when the warp's previous page
+  // belongs to the same sequence).
+  auto describe = [&](int chunk, int& id, int& rows, int& q_of) {
     const int k = chunk * 32 + lane;
-    id = -1, rows = 0;
+    id = -1, rows = 0, q_of = -1;
     if (k < my_pages) {
       const int page = begin + warp + kMmaWarps * k;
       const int sequence = sequence_of_unit(work, p.batch, page);
@@ -196,46 +218,61 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
                                           : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
+      if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous page is not in this sequence
     }
   };
-  int id_now, rows_now, id_next, rows_next;
-  describe(0, id_now, rows_now);
-  describe(1, id_next, rows_next);
+  int id_now, rows_now, q_now, id_next, rows_next, q_next;
+  describe(0, id_now, rows_now, q_now);
+  describe(1, id_next, rows_next, q_next);
   if (PROFILE) t_ids = id_now + id_next > -100 ? global_nanoseconds() : 0;  // after the ids have arrived
 
-  // Tile t of this warp is K (t even) or V (t odd) of its page t / 2, in ring slot t % 5.
-  int fill_tile = 0, fill_slot = 0;
+  // The warp's tiles, in ring order: for each of its pages [Q rows, if the page is its
+  // first of a sequence,] K, V.  Tile n sits in ring slot n % 5.
+  const unsigned char* q_base = static_cast<const unsigned char*>(p.q) +
+                                (static_cast<int64_t>(kv_head) * QF_GQA_GROUP * p.q_sh) * 2;
+  int fill_page = 0, fill_stage = 0, fill_slot = 0;  // stage 0: Q, 1: K, 2: V
   auto issue_tile = [&]() {
-    const int k = fill_tile >> 1;
-    if (k < my_pages) {
-      if ((fill_tile & 1) == 0 && (k & 31) == 0 && k > 0) {
-        id_now = id_next, rows_now = rows_next;
-        describe((k >> 5) + 1, id_next, rows_next);
+    if (fill_page < my_pages) {
+      if (fill_stage == 0 && (fill_page & 31) == 0 && fill_page > 0) {
+        id_now = id_next, rows_now = rows_next, q_now = q_next;
+        describe((fill_page >> 5) + 1, id_next, rows_next, q_next);
       }
-      const int id = __shfl_sync(kFull, id_now, k & 31);
-      int rows = __shfl_sync(kFull, rows_now, k & 31);
-      if (id < 0) {
-        rows = 0;  // bad or missing id: the page reads as zeros
-        if (id == -2 && lane == 0) atomicExch(p.status, kStatusBadPageId);
-      }
-      const bool is_v = fill_tile & 1;
-      const unsigned char* src = (is_v ? v_base : k_base) +
-                                 static_cast<int64_t>(id < 0 ? 0 : id) * (is_v ? p.v_page_bytes : p.k_page_bytes);
-      const int64_t tok_bytes = is_v ? p.v_tok_bytes : p.k_tok_bytes;
+      const int id = __shfl_sync(kFull, id_now, fill_page & 31);
+      int rows = __shfl_sync(kFull, rows_now, fill_page & 31);
+      const int q_of = __shfl_sync(kFull, q_now, fill_page & 31);
+      if (fill_stage == 0 && q_of < 0) fill_stage = 1;
       unsigned char* dst = ring + fill_slot * kTileBytes16;
+      if (fill_stage == 0) {
+        // 6 heads x 256 bytes = 96 chunks: three per lane
+        const unsigned char* src = q_base + static_cast<int64_t>(q_of) * p.q_sb * 2;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int r = 2 * j + (lane >> 4);
-        unsigned char* to = dst + fill_offset[j & 3] + (j >> 2) * (8 * 256);
-        if (r < rows) {
-          copy_chunk_async<false>(to, src + r * tok_bytes);
-        } else {
-          *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < 3; ++j) {
+          const int chunk = lane + 32 * j, head = chunk >> 4, c = chunk & 15;
+          copy_chunk_async<false>(dst + head * kQRowBytes + c * 16, src + head * p.q_sh * 2 + c * 16);
+        }
+      } else {
+        if (id < 0) {
+          rows = 0;  // bad or missing id: the page reads as zeros
+          if (id == -2 && lane == 0) atomicExch(p.status, kStatusBadPageId);
+        }
+        const bool is_v = fill_stage == 2;
+        const unsigned char* src = (is_v ? v_base : k_base) +
+                                   static_cast<int64_t>(id < 0 ? 0 : id) * (is_v ? p.v_page_bytes : p.k_page_bytes);
+        const int64_t tok_bytes = is_v ? p.v_tok_bytes : p.k_tok_bytes;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = 2 * j + (lane >> 4);
+          unsigned char* to = dst + fill_offset[j & 3] + (j >> 2) * (8 * 256);
+          if (r < rows) {
+            copy_chunk_async<false>(to, src + r * tok_bytes);
+          } else {
+            *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
       }
+      if (++fill_stage > 2) fill_stage = 0, ++fill_page;
     }
     commit_copies();  // always, so that group counting stays uniform
-    ++fill_tile;
     fill_slot = fill_slot == kRingTiles - 1 ? 0 : fill_slot + 1;
   };
 #pragma unroll
@@ -252,20 +289,10 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   const uint32_t v_chunk_xor = ((mat & 1) ^ (lane & 7)) << 4;
   const uint32_t ring_addr = smem_u32(ring);
 
-  // B operand Q^T: [k-step][dims 2q.. | dims 8 + 2q..] of head g (0 for g >= 6); the
-  // rows of the sequence this warp works on next are loaded a piece ahead.
-  uint32_t q_frag[8][2], q_ahead[8][2];
-  auto load_q = [&](int sequence, uint32_t (&frag)[8][2]) {
-    const T* row = static_cast<const T*>(p.q) + sequence * p.q_sb +
-                   (static_cast<int64_t>(kv_head) * QF_GQA_GROUP + (g < QF_GQA_GROUP ? g : 0)) * p.q_sh + 2 * q;
-#pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      const uint32_t lo = *reinterpret_cast<const uint32_t*>(row + 16 * s);
-      const uint32_t hi = *reinterpret_cast<const uint32_t*>(row + 16 * s + 8);
-      frag[s][0] = g < QF_GQA_GROUP ? lo : 0u;
-      frag[s][1] = g < QF_GQA_GROUP ? hi : 0u;
-    }
-  };
+  // B operand Q^T: [k-step][dims 2q.. | dims 8 + 2q..] of head g (0 for g >= 6), read
+  // from the Q tile at the head of each piece.
+  uint32_t q_frag[8][2];
+  const uint32_t q_lane_offset = (g < QF_GQA_GROUP ? g : 0) * kQRowBytes + 4 * q;
 
   float* deposits = reinterpret_cast<float*>(smem + kMmaWarps * kRingTiles * kTileBytes16);
   float acc[8][4];  // O^T: [m-tile j][(dim 16j+g, head 2q) (16j+g, 2q+1) (16j+g+8, 2q) (16j+g+8, 2q+1)]
@@ -283,14 +310,25 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       if (first_page[piece_seq + 1] > first_page[piece_seq]) ++rank;
     }
   };
-  if (page < end) {
-    advance_to(page);
-    load_q(piece_seq, q_ahead);
-  }
 
   while (page < end) {
+    advance_to(page);  // the piece that holds this warp's next page
+    {
+      // ---- the piece's Q tile ----
+      wait_tiles_ahead();
+      __syncwarp();
+      if (PROFILE && t_first == 0) t_first = global_nanoseconds();
+      issue_tile();
+      const unsigned char* q_tile = ring + read_slot * kTileBytes16 + q_lane_offset;
+      read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) q_frag[s][0] = q_ahead[s][0], q_frag[s][1] = q_ahead[s][1];
+      for (int s = 0; s < 8; ++s) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s);
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s + 16);
+        q_frag[s][0] = g < QF_GQA_GROUP ? lo : 0u;
+        q_frag[s][1] = g < QF_GQA_GROUP ? hi : 0u;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -302,20 +340,11 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     const int piece_begin = max(seq_first, begin);
     const int piece_end = min(first_page[piece_seq + 1], end);
     const int done_seq = piece_seq, done_rank = rank;
-    {
-      // Q rows of the sequence that holds this warp's first page after this piece
-      const int after = page + ((piece_end - page + kMmaWarps - 1) / kMmaWarps) * kMmaWarps;
-      if (after < end) {
-        advance_to(after);
-        load_q(piece_seq, q_ahead);
-      }
-    }
 
     for (; page < piece_end; page += kMmaWarps) {
       // ---- scores S^T = K Q^T ----
       wait_tiles_ahead();
       __syncwarp();
-      if (PROFILE && t_first == 0) t_first = global_nanoseconds();
       issue_tile();
       const uint32_t k_tile = ring_addr + read_slot * kTileBytes16 + k_row_offset;
       read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
@@ -383,14 +412,13 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     if (lane == 0) {
       // Piece done_rank - 2 used the same buffers: they are free once it is merged.
       int rounds = 0;
-      while (*reinterpret_cast<volatile int*>(&merged[parity]) < done_rank - 2) {
+      while (load_acquire(&merged[parity]) < done_rank - 2) {
         if (++rounds > kMergePollRounds) {
           atomicExch(p.status, kStatusMergeTimeout);
           break;
         }
         __nanosleep(64);
       }
-      __threadfence_block();
     }
     __syncwarp();
     float* mine = deposits + (parity * kMmaWarps + warp) * kDepositFloats;  // [6 heads][dim]
@@ -417,12 +445,10 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     const int first_warp = (piece_begin - begin) & (kMmaWarps - 1);
     const int participants = min(piece_pages, kMmaWarps);
     int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = atomicAdd(&arrived[parity], 1) == participants - 1;
-      __threadfence_block();
-    }
+    if (lane == 0) last = add_acq_rel(&arrived[parity], 1) == participants - 1;
     last = __shfl_sync(kFull, last, 0);
+    long long t_arrived = 0;
+    if (PROFILE) t_arrived = global_nanoseconds(), t_deposit += t_arrived - t_piece;
     if (last) {
       // lane = (warp w = lane / 4, head pair q): weight of w's deposit, per head
       const int w = lane >> 2;
@@ -484,11 +510,10 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       __syncwarp();
       if (lane == 0) {
         arrived[parity] = 0;
-        __threadfence_block();
-        *reinterpret_cast<volatile int*>(&merged[parity]) = done_rank;
+        store_release(&merged[parity], done_rank);
       }
     }
-    if (PROFILE) t_merge += global_nanoseconds() - t_piece;
+    if (PROFILE && last) t_merge += global_nanoseconds() - t_arrived, ++merges;
   }
   wait_all_copies();
   if (PROFILE) {
@@ -496,7 +521,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     if (p.cycles != nullptr && tid == 0) {
       long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * kTimelineColumns;
       dst[0] = t_entry, dst[1] = t_list, dst[2] = t_ids, dst[3] = t_first, dst[4] = global_nanoseconds();
-      dst[5] = count, dst[6] = pieces, dst[7] = t_merge;
+      dst[5] = count, dst[6] = pieces, dst[7] = t_deposit, dst[8] = t_merge, dst[9] = merges;
     }
   }
 }

@@ -243,11 +243,12 @@ def native_grouped_persistent_timeline(
 ):
     """Run the instrumented tensor-core persistent partial pass once.
 
-    Returns int64 [Hkv * ctas_per_head, 8]: per CTA {ns at entry, ns when the work
+    Returns int64 [Hkv * ctas_per_head, 10]: per CTA {ns at entry, ns when the work
     list was built, ns when its page ids were known, ns when its first K tile had
     landed, ns at exit (of its last warp), pages in its share, pieces that held
-    pages of its warp 0, ns warp 0 spent depositing and merging piece states} on the
-    GPU's global timer; rows of CTAs without work stay zero.  Raises RuntimeError when these arguments
+    pages of its warp 0, ns warp 0 spent depositing its piece states, ns warp 0
+    spent merging pieces, pieces warp 0 merged} on the GPU's global timer (256 ns
+    steps on B200); rows of CTAs without work stay zero.  Raises RuntimeError when these arguments
     would not run that kernel (FP8 pools, few split slots, batch above 1024).
     The counterpart of `native_grouped_stage_cycles` for a kernel whose CTAs are
     not tied to one (sequence, head, split).
@@ -272,7 +273,7 @@ def native_grouped_persistent_timeline(
         partials=(partial_out, partial_max, partial_sum), out=torch.empty_like(q))
     with cabi.device_of(q):
         _, ctas_per_head = cabi.fused_kernel_plan(args)
-        timeline = torch.zeros((max(ctas_per_head, 1) * k_pool.shape[2], 8), dtype=torch.int64,
+        timeline = torch.zeros((max(ctas_per_head, 1) * k_pool.shape[2], 10), dtype=torch.int64,
                                device=q.device)
         cabi.check(cabi.library().qf_grouped_splitk_persistent_timeline(
             ctypes.byref(args), timeline.data_ptr(), cabi.stream_pointer(q.device)))
