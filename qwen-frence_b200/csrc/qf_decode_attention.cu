@@ -278,6 +278,61 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
   }
 }
 
+// Combine for split_k <= 32: two memory round trips and no block-wide barrier.
+// Every warp reads the split_k statistics once (lane k holds slot k), derives the
+// number of filled slots, the top offset, the weights and the total with warp
+// shuffles, and then each thread sums its head dimension over the filled slots
+// with independent loads.
+constexpr int kSmallReduceSlots = 32;
+
+template <typename T, bool STREAMED>
+__global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReduceParams p) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int sequence = blockIdx.x / p.q_heads;
+  const int head = blockIdx.x - sequence * p.q_heads;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const float* pm = p.pm + sequence * p.pm_sb + head * p.pm_sh;
+  const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
+  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + tid * p.po_sd;
+  T* out = static_cast<T*>(p.out) + sequence * p.o_sb + head * p.o_sh + tid * p.o_sd;
+
+  // round trip 1: length (streamed partials only) and the statistics, all independent
+  int64_t length = 1;
+  if (STREAMED) length = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
+  float sum = 0.f, offset = -INFINITY;
+  if (lane < p.split_k) sum = ps[lane * p.pm_sk], offset = pm[lane * p.pm_sk];
+  if (STREAMED && length <= 0) {
+    if (tid < p.head_dim) *out = from_float<T>(0.f);  // no tokens: no slot was written
+    return;
+  }
+  int filled = p.split_k;
+  if (STREAMED) {
+    // the slot after a sequence's last piece carries sum = -1
+    const unsigned marks = __ballot_sync(kFull, lane < p.split_k && sum < 0.f);
+    if (marks != 0) filled = __ffs(marks) - 1;
+  }
+  const bool used = lane < filled && sum > 0.f;
+  float top = used ? offset : -INFINITY;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
+  const float weight = used ? expf(offset - top) : 0.f;
+  float total = sum * weight;  // 0 for unused slots (weight 0; sum finite or, unused, ignored)
+  if (!used) total = 0.f;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(kFull, total, off);
+
+  // round trip 2: this thread's head dimension of every filled slot
+  float acc = 0.f;
+  if (tid < p.head_dim) {
+#pragma unroll 4
+    for (int k = 0; k < filled; ++k) {
+      const float w = __shfl_sync(kFull, weight, k);
+      if (w != 0.f) acc += po[k * p.po_sk] * w;
+    }
+    *out = from_float<T>(acc / (total > 0.f ? total : 1.f));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -536,19 +591,30 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
   return QF_OK;
 }
 
+template <typename T>
+void launch_reduce_typed(const ReduceParams& r, unsigned blocks, int threads, bool streamed,
+                         cudaStream_t stream) {
+  // head_dim is a multiple of 32 on this path, so whole warps take part in the shuffles
+  const bool small = r.split_k <= kSmallReduceSlots && (r.head_dim & 31) == 0;
+  if (small && streamed) {
+    splitk_reduce_small_kernel<T, true><<<blocks, threads, 0, stream>>>(r);
+  } else if (small) {
+    splitk_reduce_small_kernel<T, false><<<blocks, threads, 0, stream>>>(r);
+  } else if (streamed) {
+    splitk_reduce_kernel<T, true><<<blocks, threads, 0, stream>>>(r);
+  } else {
+    splitk_reduce_kernel<T, false><<<blocks, threads, 0, stream>>>(r);
+  }
+}
+
 int launch_reduce(const ReduceParams& r, int batch, int dtype, bool streamed, cudaStream_t stream) {
   if (batch == 0) return QF_OK;
   const unsigned blocks = static_cast<unsigned>(static_cast<int64_t>(batch) * r.q_heads);
   const int threads = ((r.head_dim + 31) / 32) * 32;
-  if (streamed) {
-    if (dtype == QF_DTYPE_F16)
-      splitk_reduce_kernel<__half, true><<<blocks, threads, 0, stream>>>(r);
-    else
-      splitk_reduce_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(r);
-  } else if (dtype == QF_DTYPE_F16) {
-    splitk_reduce_kernel<__half, false><<<blocks, threads, 0, stream>>>(r);
+  if (dtype == QF_DTYPE_F16) {
+    launch_reduce_typed<__half>(r, blocks, threads, streamed, stream);
   } else {
-    splitk_reduce_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(r);
+    launch_reduce_typed<__nv_bfloat16>(r, blocks, threads, streamed, stream);
   }
   QF_CUDA(cudaGetLastError());
   return QF_OK;

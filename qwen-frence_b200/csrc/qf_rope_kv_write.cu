@@ -77,6 +77,62 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(const RopeParams p,
   const int live_rows = p.valid_tokens ? min(*p.valid_tokens, p.rows) : p.rows;
   const bool live = row < live_rows;
 
+  const int lanes_per_segment = p.head_dim >> 4;  // 8 + 8 elements per thread
+  const int segments = (p.rotate_q ? p.q_heads : 0) + 2 * p.kv_heads;
+  const int work = segments * lanes_per_segment;
+
+  // Which segment (Q head, K head or V head) and which 8 + 8 elements an item covers.
+  enum Kind { kQ, kK, kV };
+  struct Item {
+    Kind kind;
+    int head, d0;  // first-half element offset; the second half starts at d0 + half
+    const T* src;
+    int64_t src_sd;
+  };
+  auto locate = [&](int item) {
+    Item it;
+    int segment = item / lanes_per_segment;
+    it.d0 = (item - segment * lanes_per_segment) * 8;
+    if (p.rotate_q && segment < p.q_heads) {
+      it.kind = kQ;
+      it.head = segment;
+    } else {
+      if (p.rotate_q) segment -= p.q_heads;
+      it.kind = segment < p.kv_heads ? kK : kV;
+      it.head = segment < p.kv_heads ? segment : segment - p.kv_heads;
+    }
+    if (it.kind == kQ) {
+      it.src = static_cast<const T*>(p.q) + row * p.q_sr + it.head * p.q_sh;
+      it.src_sd = p.q_sd;
+    } else if (it.kind == kK) {
+      it.src = static_cast<const T*>(p.k) + row * p.k_sr + it.head * p.k_sh;
+      it.src_sd = p.k_sd;
+    } else {
+      it.src = static_cast<const T*>(p.v) + row * p.v_sr + it.head * p.v_sh;
+      it.src_sd = p.v_sd;
+    }
+    return it;
+  };
+
+  // Everything the row needs from memory is requested before the sin / cos phase,
+  // so that its latency overlaps that arithmetic: the slot, the position (below),
+  // and, on the vector path, this thread's first item.
+  int64_t slot = 0;
+  bool slot_ok = false;
+  if (live) {
+    slot = load_index(p.slots, p.slot_dtype, row * p.slot_stride);
+    slot_ok = slot >= 0 && slot < p.num_slots;
+  }
+  uint32_t early_first[4] = {0u, 0u, 0u, 0u}, early_second[4] = {0u, 0u, 0u, 0u};
+  const bool early = VEC && live && static_cast<int>(threadIdx.x) < work;
+  if constexpr (VEC) {
+    if (early) {
+      const Item it = locate(threadIdx.x);
+      *reinterpret_cast<uint4*>(early_first) = *reinterpret_cast<const uint4*>(it.src + it.d0);
+      *reinterpret_cast<uint4*>(early_second) = *reinterpret_cast<const uint4*>(it.src + it.d0 + half);
+    }
+  }
+
   if (live && threadIdx.x < half) {
     const float position = load_position(p.positions, p.pos_dtype, row * p.pos_stride);
     const float angle = __fmul_rn(position, freq.v[threadIdx.x]);
@@ -85,33 +141,10 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(const RopeParams p,
   }
   __syncthreads();
 
-  const int lanes_per_segment = p.head_dim >> 4;  // 8 + 8 elements per thread
-  const int segments = (p.rotate_q ? p.q_heads : 0) + 2 * p.kv_heads;
-  const int work = segments * lanes_per_segment;
-
-  int64_t slot = 0;
-  bool slot_ok = false;
-  if (live) {
-    slot = load_index(p.slots, p.slot_dtype, row * p.slot_stride);
-    slot_ok = slot >= 0 && slot < p.num_slots;
-  }
-
   for (int item = threadIdx.x; item < work; item += blockDim.x) {
-    int segment = item / lanes_per_segment;
-    const int chunk = item - segment * lanes_per_segment;
-    const int d0 = chunk * 8;  // first-half element offset; second half at d0 + half
-
-    // Resolve the segment: Q head, K head or V head.
-    enum { kQ, kK, kV } kind;
-    int head;
-    if (p.rotate_q && segment < p.q_heads) {
-      kind = kQ;
-      head = segment;
-    } else {
-      if (p.rotate_q) segment -= p.q_heads;
-      kind = segment < p.kv_heads ? kK : kV;
-      head = segment < p.kv_heads ? segment : segment - p.kv_heads;
-    }
+    const Item it = locate(item);
+    const Kind kind = it.kind;
+    const int head = it.head, d0 = it.d0;
 
     if (!live) {
       // Padded rows of a captured token bucket: deterministic zero queries,
@@ -127,23 +160,17 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(const RopeParams p,
     }
     if (kind != kQ && !slot_ok) continue;
 
-    const T* src;
-    int64_t src_sd;
-    if (kind == kQ) {
-      src = static_cast<const T*>(p.q) + row * p.q_sr + head * p.q_sh;
-      src_sd = p.q_sd;
-    } else if (kind == kK) {
-      src = static_cast<const T*>(p.k) + row * p.k_sr + head * p.k_sh;
-      src_sd = p.k_sd;
-    } else {
-      src = static_cast<const T*>(p.v) + row * p.v_sr + head * p.v_sh;
-      src_sd = p.v_sd;
-    }
-
+    const T* src = it.src;
+    const int64_t src_sd = it.src_sd;
     uint32_t first[4], second[4];  // 8 + 8 packed 16-bit elements
     if constexpr (VEC) {
-      *reinterpret_cast<uint4*>(first) = *reinterpret_cast<const uint4*>(src + d0);
-      *reinterpret_cast<uint4*>(second) = *reinterpret_cast<const uint4*>(src + d0 + half);
+      if (early && item == static_cast<int>(threadIdx.x)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) first[j] = early_first[j], second[j] = early_second[j];
+      } else {
+        *reinterpret_cast<uint4*>(first) = *reinterpret_cast<const uint4*>(src + d0);
+        *reinterpret_cast<uint4*>(second) = *reinterpret_cast<const uint4*>(src + d0 + half);
+      }
     } else {
       T* f = reinterpret_cast<T*>(first);
       T* s = reinterpret_cast<T*>(second);
