@@ -51,7 +51,14 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the
 # ncu capture summarised in profiles/ (same per-launch workload as a full-size launch: one
 # layer of the named workload at seed 0).  Workloads without a capture report null.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {("decode_b64", 0, "decode_partial_kernel"): 137.93e6 + 5.79e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {
+    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.04e6,
+    ("decode_b64", 0, "decode_partial_kernel"): 137.92e6 + 5.0e6,
+}
+
+
+# --kernel -> qf_set_tuning mode: profiling and A/B runs of the other partial-pass kernels
+KERNEL_MODES = {"auto": 0, "partitioned": 2, "persistent_cuda_core": 3, "persistent_mma": 4}
 
 
 def parse_args():
@@ -67,6 +74,8 @@ def parse_args():
     parser.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--kernel", choices=tuple(KERNEL_MODES), default="auto",
+                        help="partial-pass kernel of the fused attention call (auto: the library's choice)")
     return parser.parse_args()
 
 
@@ -275,6 +284,7 @@ def main():
     workload = package.workloads.build_workload(
         args.workload, rank=rank, world_size=world, scaling=args.scaling, seed=args.seed,
         layers=args.layers or None)
+    package.cabi.set_tuning(force_generic=KERNEL_MODES[args.kernel])  # read at launch (and capture) time
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
     step.load_packed_rows()
     step.capture(warmup=2)
@@ -399,6 +409,7 @@ def main():
                 "workload": args.workload, "doc": workload.meta["doc"], "global_batch": global_batch,
                 "batch_per_gpu": workload.batch, "layers": step.layers, "page_size": 16,
                 "heads": "12q/2kv x 128", "split_k": step.split_k, "parallelism": f"by-sequence x{world}",
+                "kernel": args.kernel,
                 "l2": "inputs exceed L2: each step reads %.2f GB of K/V from %d per-layer pools (L2 is 126 MB)"
                       % (step.layers * package.kv_layout.kv_bytes_per_layer(
                           workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2) / 1e9, 2 * step.layers),
