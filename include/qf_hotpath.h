@@ -284,20 +284,27 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 /* Instrumented partial pass.  Replaces grouped_gqa_splitk_profile_out
  * (native_grouped_decode.cu:405-459): same outputs as the partial pass plus
  * cycles [batch, kv_heads, split_k, 4] (device int64): clock64() cycles one
- * consumer warp of each CTA spent {waiting for pages, in QK, in softmax, in PV}. */
+ * warp of each CTA of the per-partition kernel spent {waiting for pages, in the
+ * whole page loop, in the set-up before it, in the merge after it} (loads overlap
+ * the math, so there is no separate QK / softmax / PV stage to time). */
 int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
                                       int64_t* cycles, void* stream);
 
-/* Device-side status word of the kernels on the current device: 0, or 2 when a
+/* Device-side status word of the kernels on the current device: 0; 2 when a
  * kernel met a page id outside the pool (such a page is never dereferenced; it
- * reads as zeros).  The kernels contain no spin wait.  Synchronises the device;
- * for tests and debugging only.  `reset` != 0 clears it after reading. */
+ * reads as zeros); 3 when a warp of the tensor-core persistent kernel gave up its
+ * bounded poll for an earlier sequence's merge (the one wait in the library that
+ * is not a hardware wait_group or barrier; the result of that call is then
+ * unreliable).  Synchronises the device; for tests and debugging only.
+ * `reset` != 0 clears it after reading. */
 int qf_device_status(int32_t* status, int32_t reset);
 
-/* Switches for experiments.  force_generic != 0 routes every attention call
- * through the stride-generic kernel.  `stages` is accepted and recorded but the
- * fast kernel's shared-memory ring has a fixed depth (four page pairs, three in
- * flight), chosen at compile time. */
+/* Switches for tests and experiments (process-wide, read at launch time).
+ * force_generic: 0 automatic choice; 1 every attention call goes through the
+ * stride-generic kernel; 2 fast per-partition kernel only, no persistent kernel;
+ * 3 / 4 the persistent CUDA-core / tensor-core kernel whenever the layout allows,
+ * whatever the number of split slots.  `stages` is accepted and recorded but the
+ * kernels' shared-memory rings have fixed depths chosen at compile time. */
 int qf_set_tuning(int32_t stages, int32_t force_generic);
 
 #ifdef __cplusplus
