@@ -19,6 +19,9 @@ def partition_sequences(lengths, world_size, policy="snake"):
     policy "snake": sort by length (longest first) and deal 0..w-1, w-1..0, ...
     so every rank receives nearly the same number of KV pages; a log-uniform
     length mix dealt in blocks leaves the heaviest rank bounding the step time.
+    Within a rank the sequences keep their order in the batch: a rank's batch sorted
+    by length would put all its shortest sequences in the shares of a few CTAs of
+    the persistent attention kernels, which pay a fixed cost per sequence.
     Returns a list of `world_size` lists of indices into `lengths`; every index
     appears exactly once.
     """
@@ -36,7 +39,7 @@ def partition_sequences(lengths, world_size, policy="snake"):
         lap, offset = divmod(position, world_size)
         rank = offset if lap % 2 == 0 else world_size - 1 - offset
         shards[rank].append(index)
-    return shards
+    return [sorted(shard) for shard in shards]
 
 
 def shard_pages(lengths, shards, page_size=16):
