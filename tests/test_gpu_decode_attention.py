@@ -423,3 +423,33 @@ def test_persistent_timeline(package, cuda_device):
     assert (seen_by_warp0 >= 1).all() and (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()
     with pytest.raises(RuntimeError, match="tensor-core persistent kernel"):
         package.native_grouped_persistent_timeline(*[t[:2] if t.shape[0] == 64 else t for t in dev], split_k=2)
+
+
+def test_stages_and_plan_entry_points(package, oracle, cuda_device):
+    """The fused call's two launches run separately give the fused result bit for bit;
+    the plan names the kernel the fused call uses."""
+    import ctypes
+
+    generator = torch.Generator().manual_seed(6)
+    lengths = torch.randint(1, 700, (48,), generator=generator).tolist()
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=31)
+    cabi = package.cabi
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    for split_k, kernel in ((8, "decode_mma_kernel"), (2, "decode_partial_kernel")):
+        fused = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+        partials = (torch.empty(48, split_k, 12, 128, device=cuda_device),
+                    torch.empty(48, split_k, 12, device=cuda_device),
+                    torch.empty(48, split_k, 12, device=cuda_device))
+        out = torch.full_like(dev[0], float("nan"))
+        args = splitk.fill_attention_args(cabi, *dev, split_k=split_k, scale=128 ** -0.5,
+                                          partials=partials, out=out)
+        assert cabi.fused_kernel_plan(args)[0] == kernel
+        stream = cabi.stream_pointer(cuda_device)
+        lib = cabi.library()
+        cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_PARTIAL, stream))
+        torch.cuda.synchronize()
+        assert torch.isnan(out.float()).all()  # the partial pass alone writes no output
+        cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_COMBINE, stream))
+        assert torch.equal(out, fused)
+        assert_attention_close(out, oracle.paged_attention(*host))
+        assert lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), 0, stream) == -1
