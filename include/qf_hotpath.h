@@ -299,6 +299,16 @@ int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
  * `reset` != 0 clears it after reading. */
 int qf_device_status(int32_t* status, int32_t reset);
 
+/* Programmatic dependent launch (on by default).  The RoPE / KV-write kernel, the
+ * tensor-core partial pass and the combine for split_k <= 32 are launched with
+ * cudaLaunchAttributeProgrammaticStreamSerialization: each may become resident
+ * while the previous kernel of the stream is still running, does its index set-up
+ * then, and waits (griddepcontrol.wait) for that kernel to complete and flush
+ * before it reads any tensor or writes anything.  Kernels of other libraries before
+ * or after them on the stream are ordered as usual.  enabled == 0 launches
+ * everything the ordinary way (process-wide, read at launch and capture time). */
+int qf_set_dependent_launch(int32_t enabled);
+
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the
  * stride-generic kernel; 2 fast per-partition kernel only, no persistent kernel;

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_gqa_splitk_profile_out", "qf_device_status", "qf_set_tuning",
     "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
+    "qf_set_dependent_launch",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -130,6 +131,7 @@ def library():
     lib.qf_grouped_gqa_splitk_diagnostics.argtypes = [c_int32, c_int32, c_int32, POINTER(c_int64)]
     lib.qf_device_status.argtypes = [POINTER(c_int32), c_int32]
     lib.qf_set_tuning.argtypes = [c_int32, c_int32]
+    lib.qf_set_dependent_launch.argtypes = [c_int32]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32
@@ -198,6 +200,11 @@ class device_of:
         if self._guard is not None:
             self._guard.__exit__(*exc)
         return False
+
+
+def set_dependent_launch(enabled=True):
+    """Programmatic dependent launch of the hot kernels on (default) or off."""
+    check(library().qf_set_dependent_launch(1 if enabled else 0))
 
 
 def fused_kernel_plan(args):

@@ -12,7 +12,11 @@ namespace qf {
 namespace {
 thread_local char g_error[512] = "";
 __device__ int g_status_word = 0;
+int g_dependent_launch = 1;
 }  // namespace
+
+int dependent_launch_enabled() { return g_dependent_launch; }
+void disable_dependent_launch() { g_dependent_launch = 0; }
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -41,6 +45,11 @@ extern "C" {
 int qf_abi_version(void) { return QF_ABI_VERSION; }
 
 const char* qf_last_error(void) { return qf::g_error; }
+
+int qf_set_dependent_launch(int32_t enabled) {
+  qf::g_dependent_launch = enabled ? 1 : 0;
+  return QF_OK;
+}
 
 int qf_device_status(int32_t* status, int32_t reset) {
   QF_REQUIRE(status != nullptr, "status must not be null");

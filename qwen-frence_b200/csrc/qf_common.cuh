@@ -30,6 +30,11 @@ int cuda_fail(cudaError_t err, const char* what);
 // Address of the per-device status word (file-scope __device__ int).
 int* device_status_word();
 
+// Whether launch_chained() asks for programmatic stream serialization (1, default) or
+// launches the ordinary way (0); see qf_set_dependent_launch.
+int dependent_launch_enabled();
+void disable_dependent_launch();
+
 // Status codes kernels may record (1 is reserved).
 constexpr int kStatusBadPageId = 2;
 constexpr int kStatusMergeTimeout = 3;  // a warp gave up waiting for an earlier piece's merge
@@ -100,10 +105,45 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch (the kernels of one decode layer run back to back
+// on one stream): a kernel launched through launch_chained() may become resident
+// while its predecessor still runs.  It must call dependency_wait() before it reads
+// anything an earlier kernel wrote and before its own first global write; what it
+// does earlier (index arithmetic, reads of step metadata that no kernel writes)
+// overlaps the predecessor's tail.  release_dependents() lets the next kernel of the
+// stream be scheduled as soon as resources free up.  Both are no-ops in a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Launch `kernel` so that it may overlap the tail of the previous kernel of `stream`
+// (the kernel itself orders its memory accesses with dependency_wait()).  Falls back
+// to an ordinary launch, for good, if the driver refuses the attribute.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid, config.blockDim = block;
+  config.dynamicSmemBytes = smem, config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
+  if (err == cudaErrorNotSupported && config.numAttrs != 0) {
+    (void)cudaGetLastError();
+    disable_dependent_launch();
+    config.numAttrs = 0;
+    err = cudaLaunchKernelEx(&config, kernel, args...);
+  }
+  return err;
 }
 
 #endif  // __CUDACC__

@@ -288,6 +288,8 @@ constexpr int kSmallReduceSlots = 32;
 template <typename T, bool STREAMED>
 __global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReduceParams p) {
   constexpr unsigned kFull = 0xffffffffu;
+  release_dependents();
+  dependency_wait();  // the partials come from the kernel before this one
   const int sequence = blockIdx.x / p.q_heads;
   const int head = blockIdx.x - sequence * p.q_heads;
   const int tid = threadIdx.x, lane = tid & 31;
@@ -411,7 +413,8 @@ int launch_mma(const FastParams& p, cudaStream_t stream) {
   const int resident = stream_ctas_on_current_device() / QF_MIN_CTAS;
   QF_REQUIRE(resident >= p.kv_heads, "could not size the tensor-core kernel for this device");
   StreamParams sp{p, resident / p.kv_heads};
-  kernel<<<static_cast<unsigned>(sp.ctas_per_head * p.kv_heads), kFastThreads, smem, stream>>>(sp);
+  QF_CUDA(launch_chained(kernel, dim3(static_cast<unsigned>(sp.ctas_per_head * p.kv_heads)),
+                         dim3(kFastThreads), smem, stream, sp));
   QF_CUDA(cudaGetLastError());
   return QF_OK;
 }
@@ -597,9 +600,9 @@ void launch_reduce_typed(const ReduceParams& r, unsigned blocks, int threads, bo
   // head_dim is a multiple of 32 on this path, so whole warps take part in the shuffles
   const bool small = r.split_k <= kSmallReduceSlots && (r.head_dim & 31) == 0;
   if (small && streamed) {
-    splitk_reduce_small_kernel<T, true><<<blocks, threads, 0, stream>>>(r);
+    (void)launch_chained(splitk_reduce_small_kernel<T, true>, dim3(blocks), dim3(threads), 0, stream, r);
   } else if (small) {
-    splitk_reduce_small_kernel<T, false><<<blocks, threads, 0, stream>>>(r);
+    (void)launch_chained(splitk_reduce_small_kernel<T, false>, dim3(blocks), dim3(threads), 0, stream, r);
   } else if (streamed) {
     splitk_reduce_kernel<T, true><<<blocks, threads, 0, stream>>>(r);
   } else {

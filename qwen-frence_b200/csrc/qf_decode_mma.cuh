@@ -170,17 +170,27 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   const int kv_head = blockIdx.x / sp.ctas_per_head;
   const int cta = blockIdx.x - kv_head * sp.ctas_per_head;
 
+  // The combine after this kernel may be scheduled as CTAs exit.  Until
+  // dependency_wait() below, only the sequence lengths and the block table are read
+  // (step metadata that no kernel of the layer writes) and nothing is written.
+  release_dependents();
   if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
   // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----
   const int longest = build_work_list<QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
   const int* first_page = work.first_unit;
   const int total = first_page[kMaxStreamBatch];
   if (PROFILE) t_list = global_nanoseconds();
-  if (total == 0) return;
+  if (total == 0) {
+    dependency_wait();  // keeps the chain of completions intact even without work
+    return;
+  }
   const int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
                         (longest + p.split_k - 2) / (p.split_k - 1));
   const int begin = cta * share;
-  if (begin >= total) return;
+  if (begin >= total) {
+    dependency_wait();
+    return;
+  }
   const int count = min(share, total - begin);
   const int end = begin + count;
   // This warp's pages: begin + warp + 8 k, k = 0 .. my_pages - 1.
@@ -275,6 +285,9 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     commit_copies();  // always, so that group counting stays uniform
     fill_slot = fill_slot == kRingTiles - 1 ? 0 : fill_slot + 1;
   };
+  // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
+  // newest K/V rows) and writes the partial buffers the previous combine read.
+  dependency_wait();
 #pragma unroll
   for (int i = 0; i < kTilesAhead; ++i) issue_tile();
 

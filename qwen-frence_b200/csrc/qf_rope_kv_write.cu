@@ -72,6 +72,10 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(const RopeParams p,
   __shared__ float s_cos[kMaxHalf];
   __shared__ float s_sin[kMaxHalf];
 
+  // The rows come from the kernel before this one (the QKV projection), so nothing is
+  // read ahead of it; the attention kernel after this one may start its set-up now.
+  release_dependents();
+  dependency_wait();
   const int row = blockIdx.x;
   const int half = p.head_dim >> 1;
   const int live_rows = p.valid_tokens ? min(*p.valid_tokens, p.rows) : p.rows;
@@ -385,18 +389,19 @@ int launch_rope(const qf_rope_kv_write_args* a, const float* k_scale, const floa
   if (threads > 256) threads = 256;
   const dim3 grid(a->rows);
 
+  cudaError_t err = cudaSuccess;
 #define QF_LAUNCH_ROPE(T)                                                                   \
   do {                                                                                      \
     if (fp8) {                                                                              \
       if (vec)                                                                              \
-        rope_kv_write_kernel<T, true, true><<<grid, threads, 0, stream>>>(p, freq);         \
+        err = launch_chained(rope_kv_write_kernel<T, true, true>, grid, dim3(threads), 0, stream, p, freq);   \
       else                                                                                  \
-        rope_kv_write_kernel<T, false, true><<<grid, threads, 0, stream>>>(p, freq);        \
+        err = launch_chained(rope_kv_write_kernel<T, false, true>, grid, dim3(threads), 0, stream, p, freq);  \
     } else {                                                                                \
       if (vec)                                                                              \
-        rope_kv_write_kernel<T, true, false><<<grid, threads, 0, stream>>>(p, freq);        \
+        err = launch_chained(rope_kv_write_kernel<T, true, false>, grid, dim3(threads), 0, stream, p, freq);  \
       else                                                                                  \
-        rope_kv_write_kernel<T, false, false><<<grid, threads, 0, stream>>>(p, freq);       \
+        err = launch_chained(rope_kv_write_kernel<T, false, false>, grid, dim3(threads), 0, stream, p, freq); \
     }                                                                                       \
   } while (0)
 
@@ -406,6 +411,7 @@ int launch_rope(const qf_rope_kv_write_args* a, const float* k_scale, const floa
     QF_LAUNCH_ROPE(__nv_bfloat16);
   }
 #undef QF_LAUNCH_ROPE
+  QF_CUDA(err);
   QF_CUDA(cudaGetLastError());
   return QF_OK;
 }

@@ -154,3 +154,32 @@ def test_files_load_the_way_kernel_dispatch_loads_them(package, oracle, cuda_dev
         scale=None, partials=None, split_k=config["split_k"])
     _check_layer(oracle, step, 0, out)
     assert torch.equal(native, out)
+
+
+def test_dependent_launch_on_and_off_agree(package, cuda_device):
+    """The chained (programmatic dependent) launches and ordinary launches of the layer's
+    three kernels give bit-identical pools and outputs, eagerly and in a replayed graph."""
+    workload = package.workloads.build_workload("decode_b64", layers=3, batch=48)
+    results = []
+    for enabled in (True, False, True):
+        package.cabi.set_dependent_launch(enabled)
+        try:
+            step = package.decode_step.DecodeStep(workload, cuda_device, package=package)
+            eager = step.step().clone()
+            step.capture()
+            for _ in range(3):
+                replayed = step.replay()
+            torch.cuda.synchronize()
+            replayed = replayed.clone()
+            live = workload.live_pages.to(cuda_device)  # the rest of a pool is never written or read
+            pools = [pool[live] for pool in step.k_pools] + [pool[live] for pool in step.v_pools]
+        finally:
+            package.cabi.set_dependent_launch(True)
+        assert torch.equal(eager, replayed)
+        assert torch.isfinite(eager.float()).all()
+        results.append((eager, pools))
+    for eager, pools in results[1:]:
+        assert torch.equal(eager, results[0][0])
+        for a, b in zip(pools, results[0][1]):
+            assert torch.equal(a, b)
+    assert package.cabi.device_status() == 0
