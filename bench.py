@@ -167,9 +167,10 @@ def partial_kernel_bytes(package, workload, split_k, fp8, kernel, ctas_per_head)
         return total + batch * 12 * 128 * 2
     if kernel == "decode_partial_kernel":
         return total + batch * split_k * 12 * 130 * 4
-    unit = 16 if kernel == "decode_mma_kernel" else 32
+    tensor_core = kernel == "decode_mma_kernel"
     _, pieces = package.kv_layout.persistent_schedule(
-        lengths, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=unit)
+        lengths, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=16 if tensor_core else 32,
+        overhead_units=package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD if tensor_core else 0)
     return total + 2 * len(pieces) * 6 * 130 * 4
 
 

@@ -232,8 +232,8 @@ int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args
 /* Instrumented run of the tensor-core persistent partial pass (QF_EINVAL when the
  * arguments select another kernel): timeline [kv_heads * ctas_per_head][10] int64,
  * per CTA {ns at entry, ns when the work list was built, ns when its page ids were
- * known, ns when its first K tile had landed, ns at exit (of its last warp), pages
- * in its share, pieces that held pages of its warp 0, ns warp 0 spent depositing
+ * known, ns when its first K tile had landed, ns at exit (of its last warp), units
+ * in its share (pages plus up to six empty units per sequence), pieces that held pages of its warp 0, ns warp 0 spent depositing
  * its piece states, ns warp 0 spent merging pieces, pieces warp 0 merged}; times
  * from %globaltimer (one clock for all SMs, 256 ns steps on B200);
  * CTAs without work leave their row untouched.  Plays the role of

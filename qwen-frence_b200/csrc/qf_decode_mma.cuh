@@ -35,7 +35,12 @@
 // would queue behind the 128 KB of page traffic the SM has in flight.
 //
 // Pieces, split slots and the end-of-sequence mark are those of the streamed
-// CUDA-core kernel, and so is the combine.  The merge of a piece's per-warp states
+// CUDA-core kernel, and so is the combine, with one difference: the list the CTAs
+// share is in "units", a sequence being up to kPieceOverhead empty units followed by
+// its pages.  A CTA whose share holds many short sequences then gets fewer pages than
+// one whose share is a stretch of one long sequence, and they finish together (with
+// equal page counts the former finished up to 10 us later).  A warp owns units
+// begin + warp, begin + warp + 8, ... and simply skips the empty ones.  The merge of a piece's per-warp states
 // has no CTA-wide barrier (a barrier at every sequence boundary stalls all eight
 // copy pipelines for the spread between the fastest and the slowest warp, measured
 // at 2.2 - 2.7 us per piece): a warp that has finished its pages of a piece deposits
@@ -59,6 +64,12 @@ constexpr int kTileBytes16 = QF_PAGE_SIZE * QF_HEAD_DIM * 2;   // K or V of one 
 constexpr int kRingTiles = 5;                                  // per warp
 constexpr int kTilesAhead = 4;                                 // in flight ahead of the math
 constexpr int kPaddedHeads = 8;
+// What a sequence costs a CTA besides its pages (Q tile, deposit, merge, store),
+// in pages: shares are equal in pages + min(kPieceOverhead, pages / 4) per sequence.
+#ifndef QF_PIECE_OVERHEAD
+#define QF_PIECE_OVERHEAD 6
+#endif
+constexpr int kPieceOverhead = QF_PIECE_OVERHEAD;
 constexpr int kQRowBytes = QF_HEAD_DIM * 2 + 16;                        // Q tile: head stride, padded against bank conflicts
 constexpr int kDepositHeadStride = QF_HEAD_DIM + 8;                      // floats; the pad spreads the heads over banks
 constexpr int kDepositFloats = QF_GQA_GROUP * kDepositHeadStride;        // one warp's O^T of a piece: 3.2 KB
@@ -176,8 +187,9 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   release_dependents();
   if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
   // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----
-  const int longest = build_work_list<QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
-  const int* first_page = work.first_unit;
+  const int longest =
+      build_work_list<QF_PAGE_SIZE, kPieceOverhead>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
+  const int* first_page = work.first_unit;  // first unit of a sequence; its pages follow its empty units
   const int total = first_page[kMaxStreamBatch];
   if (PROFILE) t_list = global_nanoseconds();
   if (total == 0) {
@@ -193,7 +205,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   }
   const int count = min(share, total - begin);
   const int end = begin + count;
-  // This warp's pages: begin + warp + 8 k, k = 0 .. my_pages - 1.
+  // This warp's units: begin + warp + 8 k, k = 0 .. my_pages - 1 (pages, or empty units).
   const int my_pages = count > warp ? (count - warp + kMmaWarps - 1) / kMmaWarps : 0;
 
   // ---- loads ----
@@ -212,23 +224,29 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     fill_offset[j] = r * 256 + (((lane & 15) ^ (r & 7)) << 4);
   }
 
-  // Page ids and row counts of 32 of this warp's pages at a time, one per lane, and
-  // the sequence whose Q rows must precede the page (-1 when the warp's previous page
-  // belongs to the same sequence).
+  // Page ids and row counts of 32 of this warp's units at a time, one per lane (id -3:
+  // an empty unit, nothing to load), and the sequence whose Q rows must precede the
+  // page (-1 unless it is the warp's first page of the sequence in this share).
   auto describe = [&](int chunk, int& id, int& rows, int& q_of) {
     const int k = chunk * 32 + lane;
     id = -1, rows = 0, q_of = -1;
     if (k < my_pages) {
-      const int page = begin + warp + kMmaWarps * k;
-      const int sequence = sequence_of_unit(work, p.batch, page);
-      const int in_sequence = page - first_page[sequence];
+      const int unit = begin + warp + kMmaWarps * k;
+      const int sequence = sequence_of_unit(work, p.batch, unit);
+      const int in_sequence = unit - first_page[sequence] -
+                              sequence_overhead<kPieceOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
+      // page index within the sequence; < 0: an empty unit
+      if (in_sequence < 0) {
+        id = -3;
+        return;
+      }
       const unsigned char* at =
           table_base + (sequence * p.bt_sb + static_cast<int64_t>(in_sequence) * p.bt_sp) * table_elem;
       const int64_t raw = table_elem == 8 ? *reinterpret_cast<const int64_t*>(at)
                                           : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
-      if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous page is not in this sequence
+      if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous unit is no page of this sequence
     }
   };
   int id_now, rows_now, q_now, id_next, rows_next, q_next;
@@ -242,12 +260,17 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
                                 (static_cast<int64_t>(kv_head) * QF_GQA_GROUP * p.q_sh) * 2;
   int fill_page = 0, fill_stage = 0, fill_slot = 0;  // stage 0: Q, 1: K, 2: V
   auto issue_tile = [&]() {
-    if (fill_page < my_pages) {
+    int id = -3;
+    while (fill_page < my_pages) {
       if (fill_stage == 0 && (fill_page & 31) == 0 && fill_page > 0) {
         id_now = id_next, rows_now = rows_next, q_now = q_next;
         describe((fill_page >> 5) + 1, id_next, rows_next, q_next);
       }
-      const int id = __shfl_sync(kFull, id_now, fill_page & 31);
+      id = __shfl_sync(kFull, id_now, fill_page & 31);
+      if (id != -3) break;
+      ++fill_page;  // an empty unit (only met at stage 0): nothing to load
+    }
+    if (fill_page < my_pages) {
       int rows = __shfl_sync(kFull, rows_now, fill_page & 31);
       const int q_of = __shfl_sync(kFull, q_now, fill_page & 31);
       if (fill_stage == 0 && q_of < 0) fill_stage = 1;
@@ -314,18 +337,29 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   // the same list but only stops at pieces that hold some of its pages.
   int piece_seq = sequence_of_unit(work, p.batch, begin);
   int rank = 0;
-  int page = begin + warp;  // global index of this warp's next page
+  int page = begin + warp;  // this warp's next unit
   int read_slot = 0;
-  // Move (piece_seq, rank) forward to the piece that holds `target` (< end).
+  // Move (piece_seq, rank) forward to the sequence that holds unit `target` (< end).  Only
+  // sequences with a page inside the share count as pieces.
+  auto first_data_unit = [&](int sequence) {
+    return first_page[sequence] +
+           sequence_overhead<kPieceOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
+  };
   auto advance_to = [&](int target) {
     while (piece_seq < p.batch - 1 && first_page[piece_seq + 1] <= target) {
       ++piece_seq;
-      if (first_page[piece_seq + 1] > first_page[piece_seq]) ++rank;
+      if (first_page[piece_seq + 1] > first_page[piece_seq] && first_data_unit(piece_seq) < end) ++rank;
     }
   };
 
   while (page < end) {
-    advance_to(page);  // the piece that holds this warp's next page
+    advance_to(page);
+    const int seq_first = first_data_unit(piece_seq);  // unit of the sequence's first page
+    if (page < seq_first) {
+      // empty units: on to this warp's first unit that is a page (maybe of a later sequence)
+      page += ((seq_first - page + kMmaWarps - 1) / kMmaWarps) * kMmaWarps;
+      continue;
+    }
     {
       // ---- the piece's Q tile ----
       wait_tiles_ahead();
@@ -348,9 +382,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     float offset[2] = {-INFINITY, -INFINITY};  // of heads 2q, 2q+1 (log2 units), equal in all lanes of a q
     float sum[2] = {0.f, 0.f};                 // over this lane's tokens
-    const int seq_first = first_page[piece_seq];
     const int seq_len = work.length[piece_seq];
-    const int piece_begin = max(seq_first, begin);
+    const int piece_begin = max(seq_first, begin);  // first page of the piece (as a unit)
     const int piece_end = min(first_page[piece_seq + 1], end);
     const int done_seq = piece_seq, done_rank = rank;
 

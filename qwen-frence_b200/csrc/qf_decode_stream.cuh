@@ -58,8 +58,19 @@ struct WorkList {
 
 // Every thread of a kFastThreads-wide CTA calls this once (it has two CTA-wide
 // barriers); returns the longest sequence in units.  The total is
-// list.first_unit[kMaxStreamBatch].
-template <int kUnitTokens>
+// list.first_unit[kMaxStreamBatch].  A sequence with tokens counts
+// sequence_overhead<kOverheadUnits>(data units) extra units in front of its data
+// units: they stand for the fixed cost a CTA pays per sequence, so that equal shares
+// of units are equal shares of time.
+// Empty units in front of a sequence of `data_units`: kOverheadUnits, but at most a
+// quarter of the sequence (short sequences cost less than the flat figure, and a
+// run of mostly empty units would leave some warps of a CTA without pages).
+template <int kOverheadUnits>
+__host__ __device__ __forceinline__ int sequence_overhead(int data_units) {
+  return kOverheadUnits < data_units / 4 ? kOverheadUnits : data_units / 4;
+}
+
+template <int kUnitTokens, int kOverheadUnits = 0>
 __device__ __forceinline__ int build_work_list(WorkList& list, const void* seq_lens, int lens_dtype,
                                                int64_t lens_stride, int batch) {
   constexpr unsigned kFull = 0xffffffffu;
@@ -76,7 +87,8 @@ __device__ __forceinline__ int build_work_list(WorkList& list, const void* seq_l
       len = static_cast<int>(raw > kMaxStreamLen ? kMaxStreamLen : raw);
     }
     list.length[b] = len;
-    const int units = (len + kUnitTokens - 1) / kUnitTokens;
+    const int data_units = (len + kUnitTokens - 1) / kUnitTokens;
+    const int units = data_units + sequence_overhead<kOverheadUnits>(data_units);
     before[i] = running;
     running += units;
     longest = max(longest, units);

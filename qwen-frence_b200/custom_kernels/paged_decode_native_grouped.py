@@ -245,7 +245,8 @@ def native_grouped_persistent_timeline(
 
     Returns int64 [Hkv * ctas_per_head, 10]: per CTA {ns at entry, ns when the work
     list was built, ns when its page ids were known, ns when its first K tile had
-    landed, ns at exit (of its last warp), pages in its share, pieces that held
+    landed, ns at exit (of its last warp), units in its share (pages plus the empty
+    units the kernel counts per sequence), pieces that held
     pages of its warp 0, ns warp 0 spent depositing its piece states, ns warp 0
     spent merging pieces, pieces warp 0 merged} on the GPU's global timer (256 ns
     steps on B200); rows of CTAs without work stay zero.  Raises RuntimeError when these arguments

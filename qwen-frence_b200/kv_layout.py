@@ -137,31 +137,50 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
     return int(max(1, min(wanted, cap, 65535)))
 
 
-def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SIZE):
+# Empty units the tensor-core persistent kernel counts per sequence when it cuts the
+# shares: min(TENSOR_CORE_PIECE_OVERHEAD, pages // 4) (kPieceOverhead and
+# sequence_overhead() in csrc/; the per-CTA timeline test pins the two).
+TENSOR_CORE_PIECE_OVERHEAD = 6
+
+
+def sequence_overhead(data_units, overhead_units):
+    """Empty units in front of a sequence of `data_units` in a persistent kernel's list."""
+    return min(overhead_units, data_units // 4)
+
+
+def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SIZE, overhead_units=0):
     """Host restatement of how the persistent partial kernels cut one KV head's work.
 
-    The sequences' units (pages for the tensor-core kernel, page pairs for the
-    CUDA-core one) are concatenated; CTA c takes units [c*share, (c+1)*share) with
+    A sequence with tokens is `sequence_overhead(units, overhead_units)` empty units
+    (the fixed cost a CTA pays per sequence; 0 for the CUDA-core kernel) followed by
+    its data units (pages for
+    the tensor-core kernel, page pairs for the CUDA-core one).  The sequences are
+    concatenated; CTA c takes units [c*share, (c+1)*share) with
     share = max(ceil(total / ctas_per_head), ceil(longest / (split_k - 1))), so no
     sequence is cut into more than split_k pieces.  Returns (share, pieces) where a
-    piece is (cta, sequence, first unit within the sequence, units, split slot).
+    piece is (cta, sequence, first data unit within the sequence, data units, split
+    slot); slots count from the CTA that holds the sequence's first data unit.
     """
     if split_k < 2 or ctas_per_head < 1:
         raise ValueError("the persistent kernels need split_k >= 2 and at least one CTA per head")
-    units = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
+    data = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
+    empty = [sequence_overhead(count, overhead_units) for count in data]
+    units = [count + extra for count, extra in zip(data, empty)]
     total, longest = sum(units), max(units, default=0)
     if total == 0:
         return 0, []
     share = max(-(-total // ctas_per_head), -(-longest // (split_k - 1)))
     pieces, first = [], 0
-    for sequence, count in enumerate(units):
-        position = first
-        while position < first + count:
-            cta = position // share
-            stop = min(first + count, (cta + 1) * share)
-            pieces.append((cta, sequence, position - first, stop - position, cta - first // share))
-            position = stop
-        first += count
+    for sequence, count in enumerate(data):
+        if count:
+            start = first + empty[sequence]  # the sequence's first data unit
+            position = start
+            while position < start + count:
+                cta = position // share
+                stop = min(start + count, (cta + 1) * share)
+                pieces.append((cta, sequence, position - start, stop - position, cta - start // share))
+                position = stop
+        first += units[sequence]
     return share, pieces
 
 

@@ -416,8 +416,11 @@ def test_persistent_timeline(package, cuda_device):
     assert len(busy) >= 2
     for earlier, later in ((0, 1), (1, 2), (2, 3), (3, 4)):
         assert (busy[:, earlier] <= busy[:, later]).all()
-    assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) for n in lengths)
-    _, pieces = package.kv_layout.persistent_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2)
+    overhead = package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD  # empty units per sequence, as in the kernel
+    empty = package.kv_layout.sequence_overhead
+    assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) + empty(-(-n // 16), overhead) for n in lengths)
+    _, pieces = package.kv_layout.persistent_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2,
+                                                      overhead_units=overhead)
     per_cta = torch.bincount(torch.tensor([piece[0] for piece in pieces]), minlength=len(timeline) // 2)
     seen_by_warp0 = busy[:, 6].reshape(2, -1)  # pieces that held pages of warp 0
     assert (seen_by_warp0 >= 1).all() and (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()

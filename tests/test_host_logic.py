@@ -286,7 +286,9 @@ def test_persistent_schedule_respects_split_slots(package):
         split_k = rng.choice([2, 3, 10, 64])
         ctas = rng.choice([1, 7, 74, 148])
         unit = rng.choice([16, 32])
-        share, pieces = schedule(lengths, split_k=split_k, ctas_per_head=ctas, unit_tokens=unit)
+        overhead = rng.choice([0, 0, 6])
+        share, pieces = schedule(lengths, split_k=split_k, ctas_per_head=ctas, unit_tokens=unit,
+                                 overhead_units=overhead)
         units = [-(-t // unit) for t in lengths]
         covered = [0] * batch
         load = {}
