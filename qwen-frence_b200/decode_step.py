@@ -12,7 +12,9 @@ metadata buffers at fixed addresses, partial buffers), can capture the whole
 step in a CUDA graph as the reference engine does
 (engine/graph/paged_graph_decoder.py:124-142), and offers `run_from_host`,
 the end-to-end call that takes pinned host buffers, copies them in, replays
-and copies the result out.
+and copies the result out.  `capture_from_host` records that whole call as one
+graph in which the host-to-device copy of layer l + 1's rows runs on a second
+stream while layer l computes.
 """
 
 from __future__ import annotations
@@ -70,6 +72,7 @@ class DecodeStep:
                 torch.empty((b, k, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
             )
         self.graph = None
+        self.host_graph = None
         self._host = None
 
     # ------------------------------------------------------------------ setup
@@ -189,11 +192,68 @@ class DecodeStep:
         host = self.host_buffers()
         return host["out"].numel() * host["out"].element_size()
 
+    def capture_from_host(self, warmup=2):
+        """Record the end-to-end call as ONE graph with the copies pipelined: a copy
+        stream brings in the metadata and then the packed rows a few layers at a time,
+        the compute stream waits only for the rows of the layer it is about to run, and
+        the result goes back to pinned memory at the end.  Same reads and writes as the
+        sequential `run_from_host`; the host buffers are read when the graph replays."""
+        if self.batch == 0:
+            return None
+        host = self.host_buffers()
+        main = torch.cuda.Stream(self.device)
+        copier = torch.cuda.Stream(self.device)
+
+        # Rows travel in a few copies of growing size (1, 2, 4, ... layers): the first one
+        # is short, so the first layer starts early, and there are few cross-stream
+        # dependencies, each of which costs the waiting kernel its early start.
+        chunks, first = [], 0
+        while first < self.layers:
+            size = min(max(1, len(chunks) and 2 * chunks[-1][1]), self.layers - first)
+            chunks.append((first, size))
+            first += size
+
+        def record():
+            copier.wait_stream(main)  # fork
+            with torch.cuda.stream(copier):
+                for key in ("positions", "seq_lens", "slot_mapping", "block_table"):
+                    getattr(self, key).copy_(host[key], non_blocking=True)
+                arrived = {}
+                for start, size in chunks:
+                    self.packed[start:start + size].copy_(host["packed"][start:start + size], non_blocking=True)
+                    arrived[start] = torch.cuda.Event()
+                    arrived[start].record(copier)
+            out = None
+            for index in range(self.layers):
+                if index in arrived:
+                    main.wait_event(arrived[index])  # metadata was copied before the first rows
+                out = self.layer(index)
+            main.wait_stream(copier)  # join
+            self.result = out
+            host["out"].copy_(out, non_blocking=True)
+
+        main.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(main):
+            for _ in range(warmup):
+                record()
+        main.synchronize()
+        copier.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=main):
+            record()
+        torch.cuda.current_stream(self.device).wait_stream(main)
+        self.host_graph = graph
+        return graph
+
     def run_from_host(self):
         """Host inputs in, result out: H2D copies of the step's inputs from pinned
-        memory, the step (graph replay when captured), D2H of the last layer's
-        attention output.  Asynchronous on the current stream; the caller synchronises."""
+        memory, the step, D2H of the last layer's attention output.  One pipelined
+        graph when `capture_from_host` was called, else copies, `replay`, copy.
+        Asynchronous on the current stream; the caller synchronises."""
         host = self.host_buffers()
+        if self.host_graph is not None:
+            self.host_graph.replay()
+            return host["out"]
         for key in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"):
             getattr(self, key).copy_(host[key], non_blocking=True)
         result = self.replay()

@@ -52,6 +52,20 @@ def test_cpu_runnable_configuration(package, oracle, cuda_device):
         host_out = step.run_from_host()
         torch.cuda.synchronize()
         assert torch.equal(host_out.to(cuda_device), eager)
+        # the same call as one graph with the copies pipelined against the layers;
+        # new host contents are picked up at replay
+        step.capture_from_host()
+        host = step.host_buffers()
+        host["out"].zero_()
+        assert torch.equal(step.run_from_host().to(cuda_device), eager)
+        torch.cuda.synchronize()
+        host["packed"].mul_(0.5)
+        step.run_from_host()
+        torch.cuda.synchronize()  # the call is asynchronous; the result is in pinned host memory now
+        halved = host["out"].clone()
+        host["packed"].mul_(2.0)
+        assert not torch.equal(halved.to(cuda_device), eager)
+        assert torch.equal(step.run_from_host().to(cuda_device), eager)
         assert step.h2d_bytes() == 8 * 2048 * 2 + 8 * (4 + 4 + 8) + 8 * 33 * 4
         assert step.d2h_bytes() == 8 * 12 * 128 * 2
 
