@@ -53,7 +53,7 @@ FALLBACK_HBM_GBS = 6650.0
 # ncu capture summarised in profiles/ (same per-launch workload as a full-size launch: one
 # layer of the named workload at seed 0).  Workloads without a capture report null.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.04e6,
+    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.00e6,
     ("decode_b64", 0, "decode_partial_kernel"): 137.92e6 + 5.0e6,
 }
 
@@ -105,7 +105,7 @@ class ClockSampler:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
@@ -320,6 +320,13 @@ def main():
         step.replay()
     with ClockSampler(local_rank) as sampler:
         total_ms = timed(step.replay, args.steps)
+        # The timed region lasts a few tens of milliseconds, less than a sampling period
+        # or two: keep the identical load running (untimed) until the sampler has seen it.
+        deadline = time.perf_counter() + 0.5
+        while time.perf_counter() < deadline:
+            for _ in range(20):
+                step.replay()
+            torch.cuda.synchronize(device)
     clocks = sampler.summary()
     ms_per_step = total_ms / args.steps
 
@@ -417,6 +424,7 @@ def main():
                       % (step.layers * package.kv_layout.kv_bytes_per_layer(
                           workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2) / 1e9, 2 * step.layers),
                 "timing": "CUDA graph replay, CUDA events on the launching stream, max over ranks",
+                "clock_sampling": "nvidia-smi every 50 ms over the timed region and 0.5 s more of the same replays",
             },
             "hot_path_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
