@@ -220,8 +220,9 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
 /* Which partial kernel qf_grouped_splitk_decode_attention would launch for these
  * arguments on the current device, without launching anything: *kernel is
  * QF_KERNEL_PARTITIONED (one CTA per sequence, KV head and split; also the
- * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math, FP8 pools) or
- * QF_KERNEL_PERSISTENT_MMA (tensor-core math); *ctas_per_head is the number of
+ * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math; only when forced
+ * with qf_set_tuning) or QF_KERNEL_PERSISTENT_MMA (tensor-core math, 16-bit and FP8
+ * pools); *ctas_per_head is the number of
  * resident CTAs that share one KV head's pages (0 for QF_KERNEL_PARTITIONED). */
 #define QF_KERNEL_PARTITIONED 0
 #define QF_KERNEL_PERSISTENT 1
@@ -229,8 +230,8 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
 int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args, int32_t* kernel,
                                             int32_t* ctas_per_head);
 
-/* Instrumented run of the tensor-core persistent partial pass (QF_EINVAL when the
- * arguments select another kernel): timeline [kv_heads * ctas_per_head][10] int64,
+/* Instrumented run of the tensor-core persistent partial pass, 16-bit or FP8 pools
+ * (QF_EINVAL when the arguments select another kernel): timeline [kv_heads * ctas_per_head][10] int64,
  * per CTA {ns at entry, ns when the work list was built, ns when its page ids were
  * known, ns when its first K tile had landed, ns at exit (of its last warp), units
  * in its share (pages plus up to six empty units per sequence), pieces that held pages of its warp 0, ns warp 0 spent depositing

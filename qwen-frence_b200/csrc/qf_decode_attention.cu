@@ -4,9 +4,9 @@
 // The fast partial kernels (sm_100a, cp.async ring, Qwen geometry) live in
 // qf_decode_partial.cuh (one CTA per partition, the reference's balanced
 // partitions), qf_decode_stream.cuh (persistent CTAs that share the batch's
-// pages equally, CUDA-core math; the fused entry point's kernel for FP8 pools)
-// and qf_decode_mma.cuh (the same scheduling with tensor-core math; the fused
-// entry point's kernel for fp16 / bf16 pools).
+// pages equally, CUDA-core math; kept for comparison) and qf_decode_mma.cuh (the
+// same scheduling with tensor-core math; the fused entry point's kernel for
+// fp16 / bf16 and for FP8 pools).
 //
 // A stride-generic kernel covers every other layout and geometry the
 // reference accepts (custom_kernels/paged_decode_grouped_splitk.py:228-334):
@@ -399,15 +399,16 @@ int launch_stream(const FastParams& p, cudaStream_t stream) {
   return QF_OK;
 }
 
-size_t mma_smem_bytes() {
-  return static_cast<size_t>(kMmaWarps) * kRingTiles * kTileBytes16 + kMmaMergeFloats * sizeof(float);
+size_t mma_smem_bytes(bool fp8) {
+  const size_t ring = fp8 ? RingShape<true>::kWarpBytes : RingShape<false>::kWarpBytes;
+  return static_cast<size_t>(kMmaWarps) * ring + kMmaMergeFloats * sizeof(float);
 }
 
 // One CTA per SM (its rings take most of the shared memory).
-template <typename T, bool PROFILE>
+template <typename T, bool FP8, bool PROFILE>
 int launch_mma(const FastParams& p, cudaStream_t stream) {
-  auto kernel = decode_mma_kernel<T, PROFILE>;
-  const size_t smem = mma_smem_bytes();
+  auto kernel = decode_mma_kernel<T, FP8, PROFILE>;
+  const size_t smem = mma_smem_bytes(FP8);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
   const int resident = stream_ctas_on_current_device() / QF_MIN_CTAS;
@@ -417,6 +418,11 @@ int launch_mma(const FastParams& p, cudaStream_t stream) {
                          dim3(kFastThreads), smem, stream, sp));
   QF_CUDA(cudaGetLastError());
   return QF_OK;
+}
+
+template <typename T, bool PROFILE>
+int launch_mma_for_pools(const FastParams& p, bool fp8, cudaStream_t stream) {
+  return fp8 ? launch_mma<T, true, PROFILE>(p, stream) : launch_mma<T, false, PROFILE>(p, stream);
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
@@ -498,8 +504,9 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
 // a CTA's share is at least longest / (split_k - 1) units, and with few sequences
 // and few slots that would leave most resident CTAs without work.  The lengths
 // live on the device, so the test uses what the host knows: batch * (split_k - 1)
-// slots per KV head against twice the resident CTAs per KV head.  fp16 / bf16
-// pools take the tensor-core kernel, FP8 pools the CUDA-core one.
+// slots per KV head against twice the resident CTAs per KV head.  The tensor-core
+// kernel serves 16-bit and FP8 pools; the CUDA-core persistent kernel stays
+// selectable for tests and comparisons.
 enum class FusedKernel { kPartitioned, kStreamed, kTensorCore };
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
@@ -510,8 +517,7 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return FusedKernel::kPartitioned;
   const int resident = stream_ctas_on_current_device();  // two per SM
   if (resident / QF_MIN_CTAS < a->kv_heads) return FusedKernel::kPartitioned;
-  const bool tensor_core = !a->kv_fp8 && mode != 3;
-  if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
+  const bool tensor_core = mode != 3;
   const int64_t per_head = (tensor_core ? resident / QF_MIN_CTAS : resident) / a->kv_heads;
   if (mode == 0 && static_cast<int64_t>(a->batch) * (a->split_k - 1) < 2 * per_head) {
     return FusedKernel::kPartitioned;
@@ -526,12 +532,12 @@ int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kin
   const FastParams p = fast_params(a, nullptr, timeline, status);
   if (timeline != nullptr) {
     QF_REQUIRE(kind == FusedKernel::kTensorCore, "only the tensor-core kernel has a timeline variant");
-    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half, true>(p, stream)
-                                    : launch_mma<__nv_bfloat16, true>(p, stream);
+    return a->dtype == QF_DTYPE_F16 ? launch_mma_for_pools<__half, true>(p, a->kv_fp8 != 0, stream)
+                                    : launch_mma_for_pools<__nv_bfloat16, true>(p, a->kv_fp8 != 0, stream);
   }
   if (kind == FusedKernel::kTensorCore) {
-    return a->dtype == QF_DTYPE_F16 ? launch_mma<__half, false>(p, stream)
-                                    : launch_mma<__nv_bfloat16, false>(p, stream);
+    return a->dtype == QF_DTYPE_F16 ? launch_mma_for_pools<__half, false>(p, a->kv_fp8 != 0, stream)
+                                    : launch_mma_for_pools<__nv_bfloat16, false>(p, a->kv_fp8 != 0, stream);
   }
   if (a->kv_fp8) {
     return a->dtype == QF_DTYPE_F16 ? launch_stream<__half, true>(p, stream)

@@ -54,15 +54,27 @@
 // the poll cannot deadlock); running out of rounds raises status 3 and goes on.
 #pragma once
 
+#include <type_traits>
+
 #include "qf_decode_stream.cuh"
 
 namespace qf {
 namespace {
 
 constexpr int kMmaWarps = kFastThreads / 32;                   // 8
-constexpr int kTileBytes16 = QF_PAGE_SIZE * QF_HEAD_DIM * 2;   // K or V of one page and KV head: 4 KB
-constexpr int kRingTiles = 5;                                  // per warp
-constexpr int kTilesAhead = 4;                                 // in flight ahead of the math
+// Ring geometry.  16-bit pools: K or V of one page and KV head is 4 KB, five slots per
+// warp, four tiles in flight.  FP8 pools: a tile is 2 KB plus its fp32 scale (the
+// slot keeps 64 more bytes for it), nine slots, eight tiles in flight: the same bytes
+// in flight, twice the pages.
+template <bool FP8>
+struct RingShape {
+  static constexpr int kRowBytes = FP8 ? QF_HEAD_DIM : 2 * QF_HEAD_DIM;
+  static constexpr int kTileBytes = QF_PAGE_SIZE * kRowBytes;
+  static constexpr int kSlotBytes = FP8 ? kTileBytes + 64 : kTileBytes;
+  static constexpr int kSlots = FP8 ? 9 : 5;
+  static constexpr int kAhead = kSlots - 1;
+  static constexpr int kWarpBytes = ((kSlots * kSlotBytes + 127) / 128) * 128;
+};
 constexpr int kPaddedHeads = 8;
 // What a sequence costs a CTA besides its pages (Q tile, deposit, merge, store),
 // in pages: shares are equal in pages + min(kPieceOverhead, pages / 4) per sequence.
@@ -121,8 +133,19 @@ __device__ __forceinline__ uint32_t transpose_8x8(uint32_t x) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
   return y;
 }
+template <int kAhead>
 __device__ __forceinline__ void wait_tiles_ahead() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(kTilesAhead - 1) : "memory");
+  asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
+}
+// Two e4m3 bytes (low 16 bits of x) -> two f16.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x & 0xffffu), __NV_E4M3);
+  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+}
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+  const __half2 h = __floats2half2_rn(f.x, f.y);
+  return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 // Shared-memory flag operations with CTA-scope release / acquire semantics.
@@ -154,11 +177,20 @@ __device__ __forceinline__ long long global_nanoseconds() {
 // share, the pieces that held pages of warp 0, the ns warp 0 spent depositing its
 // piece states, the ns it spent merging pieces, and the pieces it merged.
 constexpr int kTimelineColumns = 10;
-template <typename T, bool PROFILE>
+// FP8: the pools are e4m3 bytes with one fp32 scale per (page, KV head).  A tile is
+// converted to f16 in registers after ldmatrix and the MMAs are the f16 ones whatever
+// T is (bf16 queries are converted once per piece; they are exact in f16 unless
+// beyond its range).  The K scale multiplies the scores, the V scale the
+// probabilities (relative to the scale of the warp's first page of the piece, which
+// multiplies the accumulator once at the end, so that probabilities keep their
+// magnitude in f16; the reference moves up when a page's scale exceeds it 16 times).
+template <typename T, bool FP8, bool PROFILE>
 __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const StreamParams sp) {
-  using Ops = MmaOps<T>;
+  using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
+  using Ring = RingShape<FP8>;
+  constexpr int kAhead = Ring::kAhead;
   const FastParams& p = sp.f;
-  // [kMmaWarps][kRingTiles] tiles of 4 KB, then kMmaMergeFloats of merge scratch
+  // [kMmaWarps] rings of Ring::kSlots slots, then kMmaMergeFloats of merge scratch
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ WorkList work;  // units are pages
   // per piece parity: the warps' softmax states, the weights the merging warp gives
@@ -212,16 +244,20 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   const int pool_pages = static_cast<int>(p.num_pages);
   const int table_elem = p.table_dtype == QF_INDEX_I64 ? 8 : 4;
   const unsigned char* table_base = static_cast<const unsigned char*>(p.block_table);
-  const unsigned char* k_base = p.k_pool + kv_head * p.k_head_bytes + (lane & 15) * 16;
-  const unsigned char* v_base = p.v_pool + kv_head * p.v_head_bytes + (lane & 15) * 16;
-  unsigned char* ring = smem + warp * (kRingTiles * kTileBytes16);
-  // A lane copies the 16-byte chunk (lane % 16) of rows 2j + lane / 16, j = 0..7; chunk c
-  // of row r is stored at chunk c ^ (r % 8) of the row's 256 bytes.
+  // A row is 16 chunks of 16 bytes (8 for FP8): a lane copies chunk lane % 16 (lane % 8)
+  // of rows 2j + lane / 16, j = 0..7 (4j + lane / 8, j = 0..3); chunk c of row r is
+  // stored at chunk c ^ (r % 8) of the row.
+  constexpr int kChunksPerRow = Ring::kRowBytes / 16;
+  constexpr int kRowsPerPass = 32 / kChunksPerRow;
+  const int copy_chunk = lane & (kChunksPerRow - 1), copy_row = lane / kChunksPerRow;
+  const unsigned char* k_base = p.k_pool + kv_head * p.k_head_bytes + copy_chunk * 16;
+  const unsigned char* v_base = p.v_pool + kv_head * p.v_head_bytes + copy_chunk * 16;
+  unsigned char* ring = smem + warp * Ring::kWarpBytes;
   int fill_offset[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const int r = 2 * j + (lane >> 4);
-    fill_offset[j] = r * 256 + (((lane & 15) ^ (r & 7)) << 4);
+    const int r = kRowsPerPass * j + copy_row;
+    fill_offset[j] = r * Ring::kRowBytes + ((copy_chunk ^ (r & 7)) << 4);
   }
 
   // Page ids and row counts of 32 of this warp's units at a time, one per lane (id -3:
@@ -274,7 +310,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       int rows = __shfl_sync(kFull, rows_now, fill_page & 31);
       const int q_of = __shfl_sync(kFull, q_now, fill_page & 31);
       if (fill_stage == 0 && q_of < 0) fill_stage = 1;
-      unsigned char* dst = ring + fill_slot * kTileBytes16;
+      unsigned char* dst = ring + fill_slot * Ring::kSlotBytes;
       if (fill_stage == 0) {
         // 6 heads x 256 bytes = 96 chunks: three per lane
         const unsigned char* src = q_base + static_cast<int64_t>(q_of) * p.q_sb * 2;
@@ -292,46 +328,78 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
         const unsigned char* src = (is_v ? v_base : k_base) +
                                    static_cast<int64_t>(id < 0 ? 0 : id) * (is_v ? p.v_page_bytes : p.k_page_bytes);
         const int64_t tok_bytes = is_v ? p.v_tok_bytes : p.k_tok_bytes;
+        if constexpr (FP8) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int r = 2 * j + (lane >> 4);
-          unsigned char* to = dst + fill_offset[j & 3] + (j >> 2) * (8 * 256);
-          if (r < rows) {
-            copy_chunk_async<false>(to, src + r * tok_bytes);
-          } else {
-            *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+          for (int j = 0; j < 4; ++j) {
+            const int r = 4 * j + copy_row;
+            unsigned char* to = dst + fill_offset[j];
+            if (r < rows) {
+              copy_chunk_async<false>(to, src + r * tok_bytes);
+            } else {
+              *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          if (lane == 0) {
+            // the tile's scale rides behind it
+            float* scale_slot = reinterpret_cast<float*>(dst + Ring::kTileBytes);
+            if (id >= 0) {
+              const float* scale = (is_v ? p.v_scale : p.k_scale) + static_cast<int64_t>(id) * p.kv_heads + kv_head;
+              asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(scale_slot)), "l"(scale)
+                           : "memory");
+            } else {
+              *scale_slot = 1.f;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int r = 2 * j + copy_row;
+            unsigned char* to = dst + fill_offset[j & 3] + (j >> 2) * (8 * 256);
+            if (r < rows) {
+              copy_chunk_async<false>(to, src + r * tok_bytes);
+            } else {
+              *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+            }
           }
         }
       }
       if (++fill_stage > 2) fill_stage = 0, ++fill_page;
     }
     commit_copies();  // always, so that group counting stays uniform
-    fill_slot = fill_slot == kRingTiles - 1 ? 0 : fill_slot + 1;
+    fill_slot = fill_slot == Ring::kSlots - 1 ? 0 : fill_slot + 1;
   };
   // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
   // newest K/V rows) and writes the partial buffers the previous combine read.
   dependency_wait();
 #pragma unroll
-  for (int i = 0; i < kTilesAhead; ++i) issue_tile();
+  for (int i = 0; i < kAhead; ++i) issue_tile();
 
   // ---- fragments ----
-  // ldmatrix row addresses inside a tile.  K (A = K tile, k-step s covers dims 16 s ..):
-  // matrix i = lane / 8 holds rows 8 (i & 1) .., chunk 2 s + (i >> 1).  V (A = V^T, m-tile j
-  // covers dims 16 j ..): matrix i holds token rows 8 (i >> 1) .., chunk 2 j + (i & 1).
+  // ldmatrix row addresses inside a tile; matrix i = lane / 8.
+  // 16-bit pools.  K (A = K tile, k-step s covers dims 16 s ..): matrix i holds rows
+  // 8 (i & 1) .., chunk 2 s + (i >> 1).  V (A = V^T, m-tile j covers dims 16 j ..): matrix
+  // i holds token rows 8 (i >> 1) .., chunk 2 j + (i & 1).
+  // FP8 pools (a 16-byte chunk is 16 dims): for K and for V alike matrix i holds token
+  // rows 8 (i & 1) .., chunk 2 s + (i >> 1); one ldmatrix.x4 feeds two k-steps (m-tiles).
   const int mat = lane >> 3;
-  const uint32_t k_row_offset = ((lane & 7) + 8 * (mat & 1)) * 256;
+  const uint32_t k_row_offset = ((lane & 7) + 8 * (mat & 1)) * Ring::kRowBytes;
   const uint32_t k_chunk_xor = ((mat >> 1) ^ (lane & 7)) << 4;
-  const uint32_t v_row_offset = ((lane & 7) + 8 * (mat >> 1)) * 256;
-  const uint32_t v_chunk_xor = ((mat & 1) ^ (lane & 7)) << 4;
+  const uint32_t v_row_offset = FP8 ? k_row_offset : ((lane & 7) + 8 * (mat >> 1)) * Ring::kRowBytes;
+  const uint32_t v_chunk_xor = FP8 ? k_chunk_xor : ((mat & 1) ^ (lane & 7)) << 4;
   const uint32_t ring_addr = smem_u32(ring);
 
-  // B operand Q^T: [k-step][dims 2q.. | dims 8 + 2q..] of head g (0 for g >= 6), read
-  // from the Q tile at the head of each piece.
+  // B operand Q^T of head g (0 for g >= 6), read from the Q tile at the head of each
+  // piece.  16-bit pools: [k-step s][dims 16 s + 2q, +1 | 16 s + 8 + 2q, +1].  FP8 pools:
+  // [k-step s][dims 16 s + 4q, +1 | 16 s + 4q + 2, +3], the order in which ldmatrix on
+  // the byte view hands out a row's dims; an MMA does not care which dim sits at
+  // which k as long as both operands agree.
   uint32_t q_frag[8][2];
-  const uint32_t q_lane_offset = (g < QF_GQA_GROUP ? g : 0) * kQRowBytes + 4 * q;
+  const uint32_t q_lane_offset = (g < QF_GQA_GROUP ? g : 0) * kQRowBytes + (FP8 ? 8 : 4) * q;
 
-  float* deposits = reinterpret_cast<float*>(smem + kMmaWarps * kRingTiles * kTileBytes16);
-  float acc[8][4];  // O^T: [m-tile j][(dim 16j+g, head 2q) (16j+g, 2q+1) (16j+g+8, 2q) (16j+g+8, 2q+1)]
+  float* deposits = reinterpret_cast<float*>(smem + kMmaWarps * Ring::kWarpBytes);
+  // O^T: [m-tile j][(dim a, head 2q) (a, 2q+1) (b, 2q) (b, 2q+1)] with (a, b) = (16j + g,
+  // 16j + g + 8) for 16-bit pools and (16j + 2g, 16j + 2g + 1) for FP8 pools
+  float acc[8][4];
 
   // Pieces are numbered by `rank` in the order of the sequences; every warp walks
   // the same list but only stops at pieces that hold some of its pages.
@@ -362,16 +430,23 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     }
     {
       // ---- the piece's Q tile ----
-      wait_tiles_ahead();
+      wait_tiles_ahead<kAhead>();
       __syncwarp();
       if (PROFILE && t_first == 0) t_first = global_nanoseconds();
       issue_tile();
-      const unsigned char* q_tile = ring + read_slot * kTileBytes16 + q_lane_offset;
-      read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
+      const unsigned char* q_tile = ring + read_slot * Ring::kSlotBytes + q_lane_offset;
+      read_slot = read_slot == Ring::kSlots - 1 ? 0 : read_slot + 1;
 #pragma unroll
       for (int s = 0; s < 8; ++s) {
-        const uint32_t lo = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s);
-        const uint32_t hi = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s + 16);
+        uint32_t lo, hi;
+        if constexpr (FP8) {
+          const uint2 both = *reinterpret_cast<const uint2*>(q_tile + 32 * s);
+          lo = both.x, hi = both.y;
+          if constexpr (std::is_same<T, __nv_bfloat16>::value) lo = bf16x2_to_f16x2(lo), hi = bf16x2_to_f16x2(hi);
+        } else {
+          lo = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s);
+          hi = *reinterpret_cast<const uint32_t*>(q_tile + 32 * s + 16);
+        }
         q_frag[s][0] = g < QF_GQA_GROUP ? lo : 0u;
         q_frag[s][1] = g < QF_GQA_GROUP ? hi : 0u;
       }
@@ -382,6 +457,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     float offset[2] = {-INFINITY, -INFINITY};  // of heads 2q, 2q+1 (log2 units), equal in all lanes of a q
     float sum[2] = {0.f, 0.f};                 // over this lane's tokens
+    float v_reference = 0.f, v_reference_inverse = 0.f;  // FP8: V scale of the warp's first page of the piece
     const int seq_len = work.length[piece_seq];
     const int piece_begin = max(seq_first, begin);  // first page of the piece (as a unit)
     const int piece_end = min(first_page[piece_seq + 1], end);
@@ -389,17 +465,37 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
 
     for (; page < piece_end; page += kMmaWarps) {
       // ---- scores S^T = K Q^T ----
-      wait_tiles_ahead();
+      wait_tiles_ahead<kAhead>();
       __syncwarp();
       issue_tile();
-      const uint32_t k_tile = ring_addr + read_slot * kTileBytes16 + k_row_offset;
-      read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
+      const uint32_t k_tile = ring_addr + read_slot * Ring::kSlotBytes + k_row_offset;
+      float k_scale = 1.f;
+      if constexpr (FP8) {
+        k_scale = *reinterpret_cast<const float*>(ring + read_slot * Ring::kSlotBytes + Ring::kTileBytes);
+      }
+      read_slot = read_slot == Ring::kSlots - 1 ? 0 : read_slot + 1;
       float s_even[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (FP8) {
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        uint32_t a[4];
-        ldmatrix_x4(a, k_tile + ((32u * s) ^ k_chunk_xor));
-        Ops::mma((s & 1) ? s_odd : s_even, a, q_frag[s][0], q_frag[s][1]);
+        for (int s = 0; s < 4; ++s) {
+          // bytes of r[.]: this lane's dims 4q .. 4q+3 of the 16-dim chunk; r[0], r[1]: tokens
+          // g, g + 8 of chunk 2s; r[2], r[3]: of chunk 2s + 1
+          uint32_t r[4];
+          ldmatrix_x4(r, k_tile + ((32u * s) ^ k_chunk_xor));
+          const uint32_t first[4] = {e4m3x2_to_f16x2(r[0]), e4m3x2_to_f16x2(r[1]),
+                                     e4m3x2_to_f16x2(r[0] >> 16), e4m3x2_to_f16x2(r[1] >> 16)};
+          const uint32_t second[4] = {e4m3x2_to_f16x2(r[2]), e4m3x2_to_f16x2(r[3]),
+                                      e4m3x2_to_f16x2(r[2] >> 16), e4m3x2_to_f16x2(r[3] >> 16)};
+          Ops::mma(s_even, first, q_frag[2 * s][0], q_frag[2 * s][1]);
+          Ops::mma(s_odd, second, q_frag[2 * s + 1][0], q_frag[2 * s + 1][1]);
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          uint32_t a[4];
+          ldmatrix_x4(a, k_tile + ((32u * s) ^ k_chunk_xor));
+          Ops::mma((s & 1) ? s_odd : s_even, a, q_frag[s][0], q_frag[s][1]);
+        }
       }
       // score[i]: i = 0 (token g, head 2q), 1 (g, 2q+1), 2 (g+8, 2q), 3 (g+8, 2q+1)
       float score[4];
@@ -407,7 +503,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
       const bool valid_lo = g < rows, valid_hi = g + 8 < rows;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        score[i] = (s_even[i] + s_odd[i]) * p.scale_log2;
+        score[i] = (s_even[i] + s_odd[i]) * (FP8 ? p.scale_log2 * k_scale : p.scale_log2);
         if (!(i < 2 ? valid_lo : valid_hi)) score[i] = -INFINITY;
       }
       const bool grow = fmaxf(score[0], score[2]) > offset[0] + kOffsetSlack ||
@@ -433,22 +529,67 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
         prob[i] = (i < 2 ? valid_lo : valid_hi) ? fast_exp2(score[i] - offset[i & 1]) : 0.f;
         sum[i & 1] += prob[i];
       }
-      // P^T as B operand: [k = tokens 2q.. | 8 + 2q..][n = head g]
-      const uint32_t p_lo = transpose_8x8(Ops::pack(prob[0], prob[1]));
-      const uint32_t p_hi = transpose_8x8(Ops::pack(prob[2], prob[3]));
-
       // ---- values O^T += V^T P^T ----
-      wait_tiles_ahead();
+      wait_tiles_ahead<kAhead>();
       __syncwarp();
       issue_tile();
-      const uint32_t v_tile = ring_addr + read_slot * kTileBytes16 + v_row_offset;
-      read_slot = read_slot == kRingTiles - 1 ? 0 : read_slot + 1;
+      const uint32_t v_tile = ring_addr + read_slot * Ring::kSlotBytes + v_row_offset;
+      float v_weight = 1.f;
+      if constexpr (FP8) {
+        const float v_scale = *reinterpret_cast<const float*>(ring + read_slot * Ring::kSlotBytes + Ring::kTileBytes);
+        if (v_reference == 0.f) {
+          v_reference = v_scale, v_reference_inverse = 1.f / v_scale;
+        } else if (v_scale > 16.f * v_reference) {
+          // a page far larger than the reference: move the reference up (rare; the same
+          // for all lanes), so that weighted probabilities stay well inside f16
+          const float down = v_reference * (1.f / v_scale);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a, v_tile + ((32u * j) ^ v_chunk_xor));
-        Ops::mma(acc[j], a, p_lo, p_hi);
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j][i] *= down;
+          v_reference = v_scale, v_reference_inverse = 1.f / v_scale;
+        }
+        v_weight = v_scale * v_reference_inverse;
       }
+      read_slot = read_slot == Ring::kSlots - 1 ? 0 : read_slot + 1;
+      // P^T as B operand: [k = tokens 2q.. | 8 + 2q..][n = head g]
+      const uint32_t p_lo = transpose_8x8(Ops::pack(prob[0] * v_weight, prob[1] * v_weight));
+      const uint32_t p_hi = transpose_8x8(Ops::pack(prob[2] * v_weight, prob[3] * v_weight));
+      if constexpr (FP8) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // r[.] after the transpose: bytes (token 2q: dims 2g, 2g+1 | token 2q+1: dims 2g,
+          // 2g+1) of a 16-dim chunk; r[0], r[1]: tokens 0-7, 8-15 of chunk 2j; r[2], r[3]: of
+          // chunk 2j + 1.  Bytes (0, 2) are dim 2g of both tokens, bytes (1, 3) dim 2g + 1.
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, v_tile + ((32u * j) ^ v_chunk_xor));
+          const uint32_t first[4] = {e4m3x2_to_f16x2(__byte_perm(r[0], 0u, 0x0020)),
+                                     e4m3x2_to_f16x2(__byte_perm(r[0], 0u, 0x0031)),
+                                     e4m3x2_to_f16x2(__byte_perm(r[1], 0u, 0x0020)),
+                                     e4m3x2_to_f16x2(__byte_perm(r[1], 0u, 0x0031))};
+          const uint32_t second[4] = {e4m3x2_to_f16x2(__byte_perm(r[2], 0u, 0x0020)),
+                                      e4m3x2_to_f16x2(__byte_perm(r[2], 0u, 0x0031)),
+                                      e4m3x2_to_f16x2(__byte_perm(r[3], 0u, 0x0020)),
+                                      e4m3x2_to_f16x2(__byte_perm(r[3], 0u, 0x0031))};
+          Ops::mma(acc[2 * j], first, p_lo, p_hi);
+          Ops::mma(acc[2 * j + 1], second, p_lo, p_hi);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, v_tile + ((32u * j) ^ v_chunk_xor));
+          Ops::mma(acc[j], a, p_lo, p_hi);
+        }
+      }
+    }
+    if constexpr (FP8) {
+      // back to absolute V scale (v_reference is 0 only if the warp had no page, and
+      // then the accumulator is 0 too)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] *= v_reference;
     }
 
     // ---- deposit this warp's state of the piece; the last warp to arrive merges ----
@@ -469,12 +610,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     __syncwarp();
     float* mine = deposits + (parity * kMmaWarps + warp) * kDepositFloats;  // [6 heads][dim]
     if (q < QF_GQA_GROUP / 2) {
-      float* even = mine + (2 * q) * kDepositHeadStride + g;
+      float* even = mine + (2 * q) * kDepositHeadStride + (FP8 ? 2 * g : g);
       float* odd = even + kDepositHeadStride;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         even[16 * j] = acc[j][0], odd[16 * j] = acc[j][1];
-        even[16 * j + 8] = acc[j][2], odd[16 * j + 8] = acc[j][3];
+        even[16 * j + (FP8 ? 1 : 8)] = acc[j][2], odd[16 * j + (FP8 ? 1 : 8)] = acc[j][3];
       }
     }
 #pragma unroll

@@ -56,10 +56,13 @@ class DecodeStep:
         # Static buffers: a captured graph reads these addresses on every replay.
         b = self.batch
         self.packed = torch.zeros((self.layers, b, 2048), dtype=dtype, device=self.device)
-        self.positions = workload.positions.to(self.device)
-        self.seq_lens = workload.seq_lens.to(self.device)
-        self.slot_mapping = workload.slot_mapping.to(self.device)
-        self.block_table = workload.block_table.to(self.device)
+        # The four metadata tensors are views of ONE byte buffer (slot mapping first: it is
+        # the 8-byte type), so that the end-to-end call brings them in with one copy.
+        self._metadata = self._pack_metadata(workload, self.device)
+        self.positions, self.seq_lens, self.slot_mapping, self.block_table = self._metadata_views(
+            self._metadata, workload)
+        for name in ("positions", "seq_lens", "slot_mapping", "block_table"):
+            getattr(self, name).copy_(getattr(workload, name))
         # attention output of the last layer (what the step hands on); under capture
         # it lives at a fixed address in the graph's private pool
         self.result = torch.zeros((b, kv_layout.Q_HEADS, kv_layout.HEAD_DIM), dtype=dtype, device=self.device)
@@ -76,6 +79,34 @@ class DecodeStep:
         self._host = None
 
     # ------------------------------------------------------------------ setup
+    @staticmethod
+    def _metadata_layout(workload):
+        """(name, dtype, shape, byte offset) of the metadata tensors inside one buffer."""
+        layout, offset = [], 0
+        for name in ("slot_mapping", "positions", "seq_lens", "block_table"):
+            tensor = getattr(workload, name)
+            size = tensor.numel() * tensor.element_size()
+            layout.append((name, tensor.dtype, tuple(tensor.shape), offset))
+            offset += -(-size // 8) * 8
+        return layout, max(offset, 8)
+
+    @classmethod
+    def _pack_metadata(cls, workload, device, pin=False):
+        _, size = cls._metadata_layout(workload)
+        return torch.zeros(size, dtype=torch.uint8, device=device, pin_memory=pin)
+
+    @classmethod
+    def _metadata_views(cls, buffer, workload):
+        layout, _ = cls._metadata_layout(workload)
+        views = {}
+        for name, dtype, shape, offset in layout:
+            count = 1
+            for extent in shape:
+                count *= extent
+            size = count * torch.empty((), dtype=dtype).element_size()
+            views[name] = buffer[offset:offset + size].view(dtype).view(shape)
+        return views["positions"], views["seq_lens"], views["slot_mapping"], views["block_table"]
+
     def _fill_pools(self):
         """Random N(0,1)*0.5 K/V in the live pages (the rest of the pool is never
         read); FP8 pools are quantised page by page with the library's quantiser."""
@@ -171,12 +202,12 @@ class DecodeStep:
         """Pinned host staging: the step's inputs and its result."""
         if self._host is None:
             pin = dict(pin_memory=True)
+            metadata = self._pack_metadata(self.workload, "cpu", pin=True)
+            positions, seq_lens, slot_mapping, block_table = self._metadata_views(metadata, self.workload)
             self._host = dict(
                 packed=torch.empty(self.packed.shape, dtype=self.dtype, **pin),
-                positions=torch.empty(self.positions.shape, dtype=self.positions.dtype, **pin),
-                seq_lens=torch.empty(self.seq_lens.shape, dtype=self.seq_lens.dtype, **pin),
-                slot_mapping=torch.empty(self.slot_mapping.shape, dtype=self.slot_mapping.dtype, **pin),
-                block_table=torch.empty(self.block_table.shape, dtype=self.block_table.dtype, **pin),
+                metadata=metadata, positions=positions, seq_lens=seq_lens, slot_mapping=slot_mapping,
+                block_table=block_table,
                 out=torch.empty(self.result.shape, dtype=self.dtype, **pin),
             )
             for key in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"):
@@ -184,9 +215,8 @@ class DecodeStep:
         return self._host
 
     def h2d_bytes(self):
-        host = self.host_buffers()
-        return sum(host[k].numel() * host[k].element_size()
-                   for k in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"))
+        host = self.host_buffers()  # what run_from_host copies: the rows and the metadata buffer
+        return sum(host[k].numel() * host[k].element_size() for k in ("packed", "metadata"))
 
     def d2h_bytes(self):
         host = self.host_buffers()
@@ -216,8 +246,7 @@ class DecodeStep:
         def record():
             copier.wait_stream(main)  # fork
             with torch.cuda.stream(copier):
-                for key in ("positions", "seq_lens", "slot_mapping", "block_table"):
-                    getattr(self, key).copy_(host[key], non_blocking=True)
+                self._metadata.copy_(host["metadata"], non_blocking=True)  # all four tensors at once
                 arrived = {}
                 for start, size in chunks:
                     self.packed[start:start + size].copy_(host["packed"][start:start + size], non_blocking=True)
@@ -254,8 +283,8 @@ class DecodeStep:
         if self.host_graph is not None:
             self.host_graph.replay()
             return host["out"]
-        for key in ("packed", "positions", "seq_lens", "slot_mapping", "block_table"):
-            getattr(self, key).copy_(host[key], non_blocking=True)
+        self.packed.copy_(host["packed"], non_blocking=True)
+        self._metadata.copy_(host["metadata"], non_blocking=True)
         result = self.replay()
         host["out"].copy_(result, non_blocking=True)
         return host["out"]

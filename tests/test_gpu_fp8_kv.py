@@ -110,3 +110,42 @@ def test_fp8_fixed_scale_write(package, oracle, cuda_device):
         p[..., 1792:].view(batch, 1, 2, 128).transpose(1, 2),
         positions.to(dev), slots.to(dev), k8_b, v8_b, k_scale.to(dev), v_scale.to(dev))
     assert torch.equal(k8_b, k8_dev) and torch.equal(v8_b, v8_dev)
+
+
+@pytest.mark.parametrize("mode", [3, 4], ids=["cuda_core", "tensor_core"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fp8_persistent_kernels(package, oracle, cuda_device, mode, dtype):
+    """Both persistent kernels on FP8 pools (forced, whatever the batch size): mixed
+    lengths with empty and one-token sequences, NaN bytes in the unused tail of every
+    last page, per-page scales that differ by orders of magnitude, a bad page id."""
+    generator = torch.Generator().manual_seed(17)
+    lengths = [0, 1, 15, 16, 17, 33, 700, 0, 2500] + torch.randint(1, 600, (30,), generator=generator).tolist()
+    q, k, v, table, lens = make_paged_inputs(lengths, seed=33, value_scale=0.5, dtype=dtype)
+    # pages whose magnitudes differ: the scales span 1e-3 .. 1e1
+    page_gain = torch.logspace(-1, 1.3, k.shape[0])[torch.randperm(k.shape[0], generator=generator)]
+    k = (k.float() * page_gain[:, None, None, None].clamp(max=4.0)).to(dtype)
+    v = (v.float() * page_gain[:, None, None, None]).to(dtype)
+    dev = cuda_device
+    k8, ks = package.quantize_kv_pool_e4m3(k.to(dev))
+    v8, vs = package.quantize_kv_pool_e4m3(v.to(dev))
+    # poison the unused rows of every last page with the e4m3 NaN byte
+    for row, length in enumerate(lengths):
+        if length % 16:
+            page = table[row, (length - 1) // 16].item()
+            k8[page, length % 16:] = 0x7F
+            v8[page, length % 16:] = 0x7F
+    expected = oracle.paged_attention(q, oracle.dequantize_pages(k8.cpu(), ks.cpu(), dtype=dtype),
+                                      oracle.dequantize_pages(v8.cpu(), vs.cpu(), dtype=dtype), table, lens)
+    for split_k in (2, 5):
+        package.cabi.set_tuning(force_generic=mode)
+        try:
+            out = package.grouped_splitk_decode_attention_fp8(
+                q.to(dev), k8, v8, ks, vs, table.to(dev), lens.to(dev), split_k=split_k)
+        finally:
+            package.cabi.set_tuning()
+        assert torch.isfinite(out.float()).all()
+        # relative to the magnitude of the values (up to ~20 here)
+        scale = expected.float().abs().amax(dim=-1, keepdim=True).clamp(min=1.0)
+        error = ((out.cpu().float() - expected.float()).abs() / scale).max().item()
+        assert error <= (2e-2 if dtype == torch.bfloat16 else 4e-3), error
+    assert package.cabi.device_status() == 0
