@@ -517,7 +517,12 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return FusedKernel::kPartitioned;
   const int resident = stream_ctas_on_current_device();  // two per SM
   if (resident / QF_MIN_CTAS < a->kv_heads) return FusedKernel::kPartitioned;
-  const bool tensor_core = mode != 3;
+  // the tensor-core kernel uses one set of row offsets for both pools
+  const bool same_strides = a->k_stride_page == a->v_stride_page && a->k_stride_tok == a->v_stride_tok &&
+                            a->k_stride_head == a->v_stride_head &&
+                            a->k_stride_tok * (a->kv_fp8 ? 1 : 2) * QF_PAGE_SIZE < (1LL << 31);
+  const bool tensor_core = mode != 3 && same_strides;
+  if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
   const int64_t per_head = (tensor_core ? resident / QF_MIN_CTAS : resident) / a->kv_heads;
   if (mode == 0 && static_cast<int64_t>(a->batch) * (a->split_k - 1) < 2 * per_head) {
     return FusedKernel::kPartitioned;

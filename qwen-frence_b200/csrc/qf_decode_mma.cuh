@@ -259,6 +259,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
     const int r = kRowsPerPass * j + copy_row;
     fill_offset[j] = r * Ring::kRowBytes + ((copy_chunk ^ (r & 7)) << 4);
   }
+  // Byte offset, inside a page, of the row each of the lane's copies reads (K and V
+  // pools share their strides), and the page stride.
+  int row_source[FP8 ? 4 : 8];
+#pragma unroll
+  for (int j = 0; j < (FP8 ? 4 : 8); ++j) row_source[j] = (kRowsPerPass * j + copy_row) * static_cast<int>(p.k_tok_bytes);
+  const int64_t page_bytes = p.k_page_bytes;
 
   // Page ids and row counts of 32 of this warp's units at a time, one per lane (id -3:
   // an empty unit, nothing to load), and the sequence whose Q rows must precede the
@@ -324,41 +330,39 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
           rows = 0;  // bad or missing id: the page reads as zeros
           if (id == -2 && lane == 0) atomicExch(p.status, kStatusBadPageId);
         }
-        const bool is_v = fill_stage == 2;
-        const unsigned char* src = (is_v ? v_base : k_base) +
-                                   static_cast<int64_t>(id < 0 ? 0 : id) * (is_v ? p.v_page_bytes : p.k_page_bytes);
-        const int64_t tok_bytes = is_v ? p.v_tok_bytes : p.k_tok_bytes;
-        if constexpr (FP8) {
+        // K and V pools have the same strides here (the host checks), so one set of row
+        // offsets serves both.  A page whose 16 rows all exist (every page but a
+        // sequence's last) takes the branch-free copies.
+        const unsigned char* src = (fill_stage == 2 ? v_base : k_base) + static_cast<int64_t>(id < 0 ? 0 : id) * page_bytes;
+        constexpr int kPasses = FP8 ? 4 : 8;
+        if (rows >= QF_PAGE_SIZE) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int r = 4 * j + copy_row;
-            unsigned char* to = dst + fill_offset[j];
+          for (int j = 0; j < kPasses; ++j) {
+            copy_chunk_async<false>(dst + fill_offset[j & 3] + (FP8 ? 0 : (j >> 2) * (8 * 256)), src + row_source[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kPasses; ++j) {
+            const int r = kRowsPerPass * j + copy_row;
+            unsigned char* to = dst + fill_offset[j & 3] + (FP8 ? 0 : (j >> 2) * (8 * 256));
             if (r < rows) {
-              copy_chunk_async<false>(to, src + r * tok_bytes);
+              copy_chunk_async<false>(to, src + row_source[j]);
             } else {
               *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
             }
           }
+        }
+        if constexpr (FP8) {
           if (lane == 0) {
             // the tile's scale rides behind it
             float* scale_slot = reinterpret_cast<float*>(dst + Ring::kTileBytes);
             if (id >= 0) {
-              const float* scale = (is_v ? p.v_scale : p.k_scale) + static_cast<int64_t>(id) * p.kv_heads + kv_head;
+              const float* scale =
+                  (fill_stage == 2 ? p.v_scale : p.k_scale) + static_cast<int64_t>(id) * p.kv_heads + kv_head;
               asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(scale_slot)), "l"(scale)
                            : "memory");
             } else {
               *scale_slot = 1.f;
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int r = 2 * j + copy_row;
-            unsigned char* to = dst + fill_offset[j & 3] + (j >> 2) * (8 * 256);
-            if (r < rows) {
-              copy_chunk_async<false>(to, src + r * tok_bytes);
-            } else {
-              *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
             }
           }
         }
