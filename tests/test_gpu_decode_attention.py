@@ -20,7 +20,7 @@ def _to(device, *tensors):
 
 
 def _fast_path_inputs(device, lengths, **kwargs):
-    """Contiguous Qwen-geometry inputs (the TMA kernel's layout) on the device."""
+    """Contiguous Qwen-geometry inputs (the fast kernels' layout) on the device."""
     q, k, v, table, lens = make_paged_inputs(lengths, **kwargs)
     return (q, k, v, table, lens), _to(device, q, k, v, table, lens)
 
@@ -29,7 +29,7 @@ def _fast_path_inputs(device, lengths, **kwargs):
 def test_golden_cases_every_split(package, attention_golden, cuda_device, split_k):
     """Reference outputs for ragged / strided / NaN-poisoned / boundary / adversarial
     inputs.  Strided cases are re-strided on the device (generic kernel); the
-    contiguous ones take the TMA kernel."""
+    contiguous ones take the fast kernels."""
     for name in attention_golden.names:
         fields = attention_golden.case(name)
         q, k, v, table, lens, scale, expected = attention_case_tensors(fields)
@@ -44,7 +44,7 @@ def test_golden_cases_every_split(package, attention_golden, cuda_device, split_
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("split_k", [1, 3, 8])
 def test_fast_kernel_ragged_poisoned(package, oracle, cuda_device, dtype, split_k):
-    """Contiguous layout -> TMA kernel.  Lengths straddle page boundaries, the tail
+    """Contiguous layout -> fast kernels.  Lengths straddle page boundaries, the tail
     of every last page is NaN, the table is padded with -1."""
     lengths = [0, 1, 15, 16, 17, 31, 32, 33, 81, 100, 129, 513, 1000]
     host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=42, poison=True)
