@@ -196,12 +196,12 @@ int qf_splitk_reduce(const float* partial_out, const float* partial_max,
  * (custom_kernels/paged_decode_native_grouped.py:30-88).  `out` is required.
  *
  * The partial buffers are scratch of this call: for the Qwen geometry
- * (D = 128, page 16, six query heads per KV head, unit inner strides) with
- * split_k >= 2, batch <= 1024 and batch * (split_k - 1) at least twice the
- * resident CTAs per KV head, the partial pass is a persistent kernel whose CTAs
- * share the batch's pages equally; a sequence then fills only its first few
- * split slots (one per CTA that holds some of its pages), the slot after them
- * carries partial_sum = -1, and split boundaries depend on the whole batch.
+ * (D = 128, page 16, six query heads per KV head, unit inner strides, K and V pools
+ * with equal strides) with split_k >= 2 and batch <= 1024 the partial pass is a
+ * persistent kernel whose CTAs share the batch's pages equally; a sequence then
+ * fills only its first few split slots (one per CTA that holds some of its pages),
+ * the slot after them carries partial_sum = -1, and split boundaries depend on the
+ * whole batch.
  * Callers that need the reference's partitions call
  * qf_grouped_gqa_splitk_partial_out and qf_splitk_reduce instead. */
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream);

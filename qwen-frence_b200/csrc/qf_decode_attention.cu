@@ -498,15 +498,15 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
   return p;
 }
 
-// A persistent kernel serves the fused attention entry point when the layout is
-// the fast one, the batch's prefix fits in shared memory, and the split slots
-// cannot become the limit: a sequence may be cut into at most split_k pieces, so
-// a CTA's share is at least longest / (split_k - 1) units, and with few sequences
-// and few slots that would leave most resident CTAs without work.  The lengths
-// live on the device, so the test uses what the host knows: batch * (split_k - 1)
-// slots per KV head against twice the resident CTAs per KV head.  The tensor-core
-// kernel serves 16-bit and FP8 pools; the CUDA-core persistent kernel stays
-// selectable for tests and comparisons.
+// The tensor-core persistent kernel serves the fused attention entry point whenever
+// the layout is the fast one, split_k >= 2, the batch's prefix fits in its shared
+// memory and both pools share their strides.  A sequence may be cut into at most
+// split_k pieces, so a CTA's share is at least longest / (split_k - 1) units and a
+// batch of few sequences with few slots leaves resident CTAs without work; the
+// per-partition kernel has the same limit (split_k CTAs per sequence and head) and
+// half the speed per page, so the persistent one is used regardless (measured from
+// batch 1 x 4096 tokens, split_k 22: 9.3 us against 12.3 us, upwards).  The CUDA-core
+// persistent kernel is only used when forced (tests, comparisons).
 enum class FusedKernel { kPartitioned, kStreamed, kTensorCore };
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
@@ -523,10 +523,7 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
                             a->k_stride_tok * (a->kv_fp8 ? 1 : 2) * QF_PAGE_SIZE < (1LL << 31);
   const bool tensor_core = mode != 3 && same_strides;
   if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
-  const int64_t per_head = (tensor_core ? resident / QF_MIN_CTAS : resident) / a->kv_heads;
-  if (mode == 0 && static_cast<int64_t>(a->batch) * (a->split_k - 1) < 2 * per_head) {
-    return FusedKernel::kPartitioned;
-  }
+  if (!tensor_core && mode == 0) return FusedKernel::kPartitioned;  // pools with different strides
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 

@@ -250,7 +250,7 @@ def native_grouped_persistent_timeline(
     pages of its warp 0, ns warp 0 spent depositing its piece states, ns warp 0
     spent merging pieces, pieces warp 0 merged} on the GPU's global timer (256 ns
     steps on B200); rows of CTAs without work stay zero.  Raises RuntimeError when these arguments
-    would not run that kernel (few split slots, batch above 1024).
+    would not run that kernel (batch above 1024, K and V pools with different strides).
     The counterpart of `native_grouped_stage_cycles` for a kernel whose CTAs are
     not tied to one (sequence, head, split).
     """

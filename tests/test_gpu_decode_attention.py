@@ -424,8 +424,12 @@ def test_persistent_timeline(package, cuda_device):
     per_cta = torch.bincount(torch.tensor([piece[0] for piece in pieces]), minlength=len(timeline) // 2)
     seen_by_warp0 = busy[:, 6].reshape(2, -1)  # pieces that held pages of warp 0
     assert (seen_by_warp0 >= 1).all() and (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()
-    with pytest.raises(RuntimeError, match="tensor-core persistent kernel"):
-        package.native_grouped_persistent_timeline(*[t[:2] if t.shape[0] == 64 else t for t in dev], split_k=2)
+    package.cabi.set_tuning(force_generic=2)  # the per-partition kernel has no timeline
+    try:
+        with pytest.raises(RuntimeError, match="tensor-core persistent kernel"):
+            package.native_grouped_persistent_timeline(*dev, split_k=10)
+    finally:
+        package.cabi.set_tuning()
 
 
 def test_stages_and_plan_entry_points(package, oracle, cuda_device):
@@ -438,21 +442,26 @@ def test_stages_and_plan_entry_points(package, oracle, cuda_device):
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=31)
     cabi = package.cabi
     splitk = package.kernel_module("paged_decode_grouped_splitk")
-    for split_k, kernel in ((8, "decode_mma_kernel"), (2, "decode_partial_kernel")):
-        fused = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
-        partials = (torch.empty(48, split_k, 12, 128, device=cuda_device),
-                    torch.empty(48, split_k, 12, device=cuda_device),
-                    torch.empty(48, split_k, 12, device=cuda_device))
-        out = torch.full_like(dev[0], float("nan"))
-        args = splitk.fill_attention_args(cabi, *dev, split_k=split_k, scale=128 ** -0.5,
-                                          partials=partials, out=out)
-        assert cabi.fused_kernel_plan(args)[0] == kernel
-        stream = cabi.stream_pointer(cuda_device)
-        lib = cabi.library()
-        cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_PARTIAL, stream))
-        torch.cuda.synchronize()
-        assert torch.isnan(out.float()).all()  # the partial pass alone writes no output
-        cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_COMBINE, stream))
+    for split_k, mode, kernel in ((8, 0, "decode_mma_kernel"), (2, 0, "decode_mma_kernel"),
+                                  (4, 2, "decode_partial_kernel"), (4, 3, "decode_stream_kernel")):
+        cabi.set_tuning(force_generic=mode)
+        try:
+            fused = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+            partials = (torch.empty(48, split_k, 12, 128, device=cuda_device),
+                        torch.empty(48, split_k, 12, device=cuda_device),
+                        torch.empty(48, split_k, 12, device=cuda_device))
+            out = torch.full_like(dev[0], float("nan"))
+            args = splitk.fill_attention_args(cabi, *dev, split_k=split_k, scale=128 ** -0.5,
+                                              partials=partials, out=out)
+            assert cabi.fused_kernel_plan(args)[0] == kernel
+            stream = cabi.stream_pointer(cuda_device)
+            lib = cabi.library()
+            cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_PARTIAL, stream))
+            torch.cuda.synchronize()
+            assert torch.isnan(out.float()).all()  # the partial pass alone writes no output
+            cabi.check(lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), cabi.STAGE_COMBINE, stream))
+        finally:
+            cabi.set_tuning()
         assert torch.equal(out, fused)
         assert_attention_close(out, oracle.paged_attention(*host))
         assert lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), 0, stream) == -1
