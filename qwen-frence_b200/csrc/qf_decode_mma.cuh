@@ -1,13 +1,15 @@
 // Tensor-core split-K partial kernel of GQA paged decode attention for sm_100a:
 // persistent CTAs over the batch's page list (the scheduling of
-// qf_decode_stream.cuh, in units of pages), warp-level MMA for the math.
+// qf_decode_stream.cuh, in units of pages), warp-level MMA for the math.  Serves
+// fp16 / bf16 pools and FP8-e4m3 pools with per-page scales.
 //
 // Why tensor cores for a bandwidth-bound op.  On CUDA cores one page pair costs
 // about 3 400 warp instructions (fp16 -> fp32 conversions, packed FMAs, the
 // shuffle reduction), and once the per-partition set-up latencies are gone that
 // instruction stream, not HBM, is the limit.  Here a page of one KV head costs
-// about a hundred: the arithmetic intensity is still 6 flop/byte, the MMA only
-// takes the conversions and FMAs off the issue slots.
+// about 430, most of them copy issue and address arithmetic: the arithmetic
+// intensity is still 6 flop/byte, the MMA only takes the conversions and FMAs off
+// the issue slots.
 //
 // Shapes.  The GQA group has 6 query heads, so heads cannot fill an MMA's M = 16;
 // tokens can.  A warp computes, for one page (16 tokens) at a time,
@@ -21,37 +23,43 @@
 // so the online softmax rescale needs no shuffle; its offset only moves when a
 // score exceeds it by 2^8, as in the CUDA-core kernels.
 //
-// Loads.  Every warp owns pages begin + warp, begin + warp + 8, ... of the CTA's
-// share and a private ring of five 4 KB tiles (K and V tiles of consecutive pages
-// alternate), filled by 16-byte cp.async with an XOR swizzle so that ldmatrix is
-// bank-conflict free; four tiles (16 KB per warp, 128 KB per SM) are in flight
-// ahead of the math, and nothing but cp.async.wait_group and __syncwarp orders
-// them: no barrier inside a piece, no spin wait anywhere.  Rows past the end of a
+// Work.  The list the CTAs of a KV head share is in "units": a sequence is up to
+// kPieceOverhead empty units followed by its pages, so a CTA whose share holds
+// many short sequences gets fewer pages than one whose share is a stretch of one
+// long sequence, and they finish together (with equal page counts the former
+// finished up to 10 us later: every sequence costs a Q tile, deposits, a merge
+// and a store).  Warp w owns units begin + w, begin + w + 8, ... of the CTA's share
+// and skips the empty ones.  Pieces, split slots and the end-of-sequence mark are
+// those of the streamed CUDA-core kernel, and so is the combine.
+//
+// Loads.  Every warp has a private ring of five 4 KB tiles (K and V tiles of its
+// consecutive pages alternate), filled by 16-byte cp.async with an XOR swizzle so
+// that ldmatrix is bank-conflict free; four tiles (16 KB per warp, 128 KB per SM)
+// are in flight ahead of the math, and nothing but cp.async.wait_group and
+// __syncwarp orders them: no barrier inside a piece.  Rows past the end of a
 // sequence are written as zeros instead of copied, so that no NaN from an unused
 // cache row reaches an MMA.  Page ids, and the rows a page holds, sit in lane
-// registers, 32 pages per warp at a time, fetched a chunk ahead.  The Q rows of a
+// registers, 32 units per warp at a time, fetched a chunk ahead.  The Q rows of a
 // sequence travel through the same ring, as one more tile in front of the warp's
 // first page of that sequence: a plain global load of Q at a sequence boundary
 // would queue behind the 128 KB of page traffic the SM has in flight.
 //
-// Pieces, split slots and the end-of-sequence mark are those of the streamed
-// CUDA-core kernel, and so is the combine, with one difference: the list the CTAs
-// share is in "units", a sequence being up to kPieceOverhead empty units followed by
-// its pages.  A CTA whose share holds many short sequences then gets fewer pages than
-// one whose share is a stretch of one long sequence, and they finish together (with
-// equal page counts the former finished up to 10 us later).  A warp owns units
-// begin + warp, begin + warp + 8, ... and simply skips the empty ones.  The merge of a piece's per-warp states
-// has no CTA-wide barrier (a barrier at every sequence boundary stalls all eight
-// copy pipelines for the spread between the fastest and the slowest warp, measured
-// at 2.2 - 2.7 us per piece): a warp that has finished its pages of a piece deposits
-// (accumulator, offset, sum) in shared memory, bumps the piece's arrival counter
-// and goes on with the next piece; the warp whose arrival completes the count
-// merges the deposits and stores the piece.  Deposits are double-buffered by piece
-// parity; before depositing piece r a warp checks that piece r - 2 has been
-// merged.  That check can only fail when the warp is two sequences ahead of the
-// slowest one; it then polls, for a bounded number of rounds, a flag that only
-// depends on warps behind it (the warp that is furthest behind never waits, so
-// the poll cannot deadlock); running out of rounds raises status 3 and goes on.
+// Merging a piece has no CTA-wide barrier (a barrier at every sequence boundary
+// stalls all eight copy pipelines for the spread between the fastest and the
+// slowest warp, measured at 2.2 - 2.7 us per piece): a warp that has finished its
+// pages of a piece deposits (accumulator, offset, sum) in shared memory, bumps the
+// piece's arrival counter and goes on with the next piece; the warp whose arrival
+// completes the count merges the deposits and stores the piece.  Deposits are
+// double-buffered by piece parity; before depositing piece r a warp checks that
+// piece r - 2 has been merged.  That check can only fail when the warp is two
+// sequences ahead of the slowest one; it then polls, for a bounded number of
+// rounds, a flag that only depends on warps behind it (the warp that is furthest
+// behind never waits, so the poll cannot deadlock); running out of rounds raises
+// status 3 and goes on.
+//
+// The kernel is launched chained to its predecessor (launch_chained): everything up
+// to dependency_wait() - the work list, the share, the page ids - runs while the
+// RoPE / KV-write kernel before it is still running.
 #pragma once
 
 #include <type_traits>
