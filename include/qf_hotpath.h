@@ -153,7 +153,9 @@ typedef struct qf_decode_attention_args {
   const void* v_pool;
   int64_t k_stride_page, k_stride_tok, k_stride_head, k_stride_d;
   int64_t v_stride_page, v_stride_tok, v_stride_head, v_stride_d;
-  const void* block_table; /* device [batch, table_width] */
+  const void* block_table; /* device [batch, table_width]; a seq_lens entry beyond
+                              table_width * page_size tokens is cut to that, so no
+                              kernel reads past a table row */
   int32_t table_dtype;     /* QF_INDEX_I32 / I64 */
   int64_t table_stride_b, table_stride_p;
   int64_t table_width;

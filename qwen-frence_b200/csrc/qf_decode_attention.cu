@@ -53,6 +53,7 @@ struct GenericParams {
   int* status;
   int table_dtype, lens_dtype;
   int batch, q_heads, kv_heads, head_dim, page_size, split_k;
+  int64_t max_tokens;  // table_width * page_size: a longer sequence length is cut to this
   float scale;
 };
 
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(kGenericWarps * 32)
 
   int64_t seq_len = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
   if (seq_len < 0) seq_len = 0;
+  if (seq_len > p.max_tokens) seq_len = p.max_tokens;  // never read past the table row
   const int64_t total_pages = (seq_len + p.page_size - 1) / p.page_size;
   const int64_t start_page = split * total_pages / p.split_k;
   const int64_t end_page = (static_cast<int64_t>(split) + 1) * total_pages / p.split_k;
@@ -189,6 +191,7 @@ struct ReduceParams {
   const void* seq_lens;
   int64_t lens_stride;
   int lens_dtype;
+  int64_t max_tokens;  // as in the partial pass: lengths are cut to the table's capacity
 };
 
 constexpr int kReduceChunk = 256;  // partitions whose weights are staged at a time
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
 
   int split_k = p.split_k;
   if (STREAMED) {
-    if (load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) <= 0) {
+    if (min(load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride), p.max_tokens) <= 0) {
       if (tid < p.head_dim) {
         static_cast<T*>(p.out)[sequence * p.o_sb + head * p.o_sh + tid * p.o_sd] = from_float<T>(0.f);
       }
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReducePa
 
   // round trip 1: length (streamed partials only) and the statistics, all independent
   int64_t length = 1;
-  if (STREAMED) length = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
+  if (STREAMED) length = min(load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride), p.max_tokens);
   float sum = 0.f, offset = -INFINITY;
   if (lane < p.split_k) sum = ps[lane * p.pm_sk], offset = pm[lane * p.pm_sk];
   if (STREAMED && length <= 0) {
@@ -494,6 +497,8 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
   p.status = status;
   p.table_dtype = a->table_dtype, p.lens_dtype = a->lens_dtype;
   p.batch = a->batch, p.q_heads = a->q_heads, p.kv_heads = a->kv_heads, p.split_k = a->split_k;
+  const int64_t capacity = a->table_width * a->page_size;
+  p.max_tokens = static_cast<int>(capacity > kMaxStreamLen ? kMaxStreamLen : capacity);
   p.scale_log2 = a->scale * kLog2e;
   return p;
 }
@@ -585,6 +590,7 @@ int launch_partial(const qf_decode_attention_args* a, bool direct_out, long long
   g.table_dtype = a->table_dtype, g.lens_dtype = a->lens_dtype;
   g.batch = a->batch, g.q_heads = a->q_heads, g.kv_heads = a->kv_heads, g.head_dim = a->head_dim;
   g.page_size = a->page_size, g.split_k = a->split_k;
+  g.max_tokens = a->table_width * a->page_size;
   g.scale = a->scale;
   const unsigned blocks = static_cast<unsigned>(static_cast<int64_t>(a->batch) * a->q_heads * a->split_k);
   const int threads = kGenericWarps * 32;
@@ -700,6 +706,7 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
   r.out = args->out, r.o_sb = args->o_stride_b, r.o_sh = args->o_stride_h, r.o_sd = args->o_stride_d;
   r.q_heads = args->q_heads, r.head_dim = args->head_dim, r.split_k = args->split_k;
   r.seq_lens = args->seq_lens, r.lens_stride = args->lens_stride, r.lens_dtype = args->lens_dtype;
+  r.max_tokens = args->table_width * args->page_size;
   return qf::launch_reduce(r, args->batch, args->dtype, streamed, s);
 }
 

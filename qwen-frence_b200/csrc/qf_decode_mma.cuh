@@ -228,7 +228,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const Strea
   if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
   // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----
   const int longest =
-      build_work_list<QF_PAGE_SIZE, kPieceOverhead>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
+      build_work_list<QF_PAGE_SIZE, kPieceOverhead>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch,
+                                                    p.max_tokens);
   const int* first_page = work.first_unit;  // first unit of a sequence; its pages follow its empty units
   const int total = first_page[kMaxStreamBatch];
   if (PROFILE) t_list = global_nanoseconds();

@@ -76,6 +76,7 @@ struct FastParams {
   int* status;
   int table_dtype, lens_dtype;
   int batch, q_heads, kv_heads, split_k;
+  int max_tokens;    // table_width * page size: a longer sequence length is cut to this
   float scale_log2;  // softmax scale * log2(e)
 };
 
@@ -404,7 +405,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
   {
     int64_t raw = load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride);
     raw = raw < 0 ? 0 : raw;
-    seq_len = static_cast<int>(raw > 0x7ffffff0 ? 0x7ffffff0 : raw);
+    seq_len = static_cast<int>(raw > p.max_tokens ? p.max_tokens : raw);  // never read past the table row
   }
   const int total_pages = (seq_len + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE;
   const int start_page = static_cast<int>(static_cast<int64_t>(split) * total_pages / p.split_k);

@@ -72,7 +72,7 @@ __host__ __device__ __forceinline__ int sequence_overhead(int data_units) {
 
 template <int kUnitTokens, int kOverheadUnits = 0>
 __device__ __forceinline__ int build_work_list(WorkList& list, const void* seq_lens, int lens_dtype,
-                                               int64_t lens_stride, int batch) {
+                                               int64_t lens_stride, int batch, int max_tokens) {
   constexpr unsigned kFull = 0xffffffffu;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int running = 0, longest = 0;
@@ -84,7 +84,7 @@ __device__ __forceinline__ int build_work_list(WorkList& list, const void* seq_l
     if (b < batch) {
       int64_t raw = load_index(seq_lens, lens_dtype, b * lens_stride);
       raw = raw < 0 ? 0 : raw;
-      len = static_cast<int>(raw > kMaxStreamLen ? kMaxStreamLen : raw);
+      len = static_cast<int>(raw > max_tokens ? max_tokens : raw);  // never read past the table row
     }
     list.length[b] = len;
     const int data_units = (len + kUnitTokens - 1) / kUnitTokens;
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
 
   // ---- the pair list of this launch: prefix over sequences, total, longest ----
   const int longest =
-      build_work_list<2 * QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch);
+      build_work_list<2 * QF_PAGE_SIZE>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch, p.max_tokens);
   const int* first_pair = work.first_unit;
   const int* length = work.length;
   const int total = first_pair[kMaxStreamBatch];

@@ -465,3 +465,27 @@ def test_stages_and_plan_entry_points(package, oracle, cuda_device):
         assert torch.equal(out, fused)
         assert_attention_close(out, oracle.paged_attention(*host))
         assert lib.qf_grouped_splitk_decode_attention_stages(ctypes.byref(args), 0, stream) == -1
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3], ids=["default", "generic", "partitioned", "cuda_core_persistent"])
+def test_length_beyond_the_table_is_cut_not_followed(package, oracle, cuda_device, mode):
+    """A sequence length larger than its block-table row can hold is cut to the row's
+    capacity: the kernels never read table entries that do not exist."""
+    lengths = [200, 64, 31]
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=35)
+    q, k, v, table, lens = dev
+    capacity = table.shape[1] * 16
+    too_long = lens.clone()
+    too_long[1] = capacity + 1000  # row 1 only has 4 real pages; the rest of the row is -1 padding
+    package.cabi.set_tuning(force_generic=mode)
+    try:
+        out = package.grouped_splitk_decode_attention(q, k, v, table, too_long, split_k=3)
+    finally:
+        package.cabi.set_tuning()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    # rows 0 and 2 are untouched by the bad length
+    expected = oracle.paged_attention(*host)
+    assert_attention_close(out[[0, 2]], expected[[0, 2]])
+    # the padded entries of row 1 (-1) are reported as bad page ids, never dereferenced
+    assert package.cabi.device_status() == 2
