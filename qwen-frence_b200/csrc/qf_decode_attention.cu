@@ -402,19 +402,25 @@ int launch_stream(const FastParams& p, cudaStream_t stream) {
   return QF_OK;
 }
 
+// Resident CTAs of the tensor-core kernel on the current device.
+int mma_ctas_on_current_device(bool fp8) {
+  const int sms = stream_ctas_on_current_device() / QF_MIN_CTAS;
+  return sms * (fp8 ? RingShape<true>::kCtasPerSm : RingShape<false>::kCtasPerSm);
+}
+
 size_t mma_smem_bytes(bool fp8) {
   const size_t ring = fp8 ? RingShape<true>::kWarpBytes : RingShape<false>::kWarpBytes;
   return static_cast<size_t>(kMmaWarps) * ring + kMmaMergeFloats * sizeof(float);
 }
 
-// One CTA per SM (its rings take most of the shared memory).
+// One CTA per SM for 16-bit pools (its rings take most of the shared memory), two for FP8.
 template <typename T, bool FP8, bool PROFILE>
 int launch_mma(const FastParams& p, cudaStream_t stream) {
   auto kernel = decode_mma_kernel<T, FP8, PROFILE>;
   const size_t smem = mma_smem_bytes(FP8);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
-  const int resident = stream_ctas_on_current_device() / QF_MIN_CTAS;
+  const int resident = mma_ctas_on_current_device(FP8);
   QF_REQUIRE(resident >= p.kv_heads, "could not size the tensor-core kernel for this device");
   StreamParams sp{p, resident / p.kv_heads};
   QF_CUDA(launch_chained(kernel, dim3(static_cast<unsigned>(sp.ctas_per_head * p.kv_heads)),
@@ -722,7 +728,7 @@ int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args
   const int resident = qf::stream_ctas_on_current_device();
   const bool mma = kind == qf::FusedKernel::kTensorCore;
   *kernel = mma ? QF_KERNEL_PERSISTENT_MMA : QF_KERNEL_PERSISTENT;
-  *ctas_per_head = (mma ? resident / QF_MIN_CTAS : resident) / args->kv_heads;
+  *ctas_per_head = (mma ? qf::mma_ctas_on_current_device(args->kv_fp8 != 0) : resident) / args->kv_heads;
   return QF_OK;
 }
 

@@ -71,15 +71,19 @@ namespace {
 
 constexpr int kMmaWarps = kFastThreads / 32;                   // 8
 // Ring geometry.  16-bit pools: K or V of one page and KV head is 4 KB, five slots per
-// warp, four tiles in flight.  FP8 pools: a tile is 2 KB plus its fp32 scale (the
-// slot keeps 64 more bytes for it), nine slots, eight tiles in flight: the same bytes
-// in flight, twice the pages.
+// warp, four tiles in flight, one CTA per SM.  FP8 pools: a tile is 2 KB plus its fp32
+// scale (the slot keeps 64 more bytes for it), three slots, two tiles in flight, and
+// TWO CTAs per SM: with e4m3 tiles the kernel is bound by instruction latency (the
+// conversions make a page cost more instructions, and a page is half the bytes), and
+// sixteen warps per SM hide it where eight could not; the FP8 variant compiles to 128
+// registers, and 2 x (8 x 3 slots + deposits) fits the shared memory.
 template <bool FP8>
 struct RingShape {
   static constexpr int kRowBytes = FP8 ? QF_HEAD_DIM : 2 * QF_HEAD_DIM;
   static constexpr int kTileBytes = QF_PAGE_SIZE * kRowBytes;
   static constexpr int kSlotBytes = FP8 ? kTileBytes + 64 : kTileBytes;
-  static constexpr int kSlots = FP8 ? 9 : 5;
+  static constexpr int kSlots = FP8 ? 3 : 5;
+  static constexpr int kCtasPerSm = FP8 ? 2 : 1;
   static constexpr int kAhead = kSlots - 1;
   static constexpr int kWarpBytes = ((kSlots * kSlotBytes + 127) / 128) * 128;
 };
@@ -193,7 +197,7 @@ constexpr int kTimelineColumns = 10;
 // multiplies the accumulator once at the end, so that probabilities keep their
 // magnitude in f16; the reference moves up when a page's scale exceeds it 16 times).
 template <typename T, bool FP8, bool PROFILE>
-__global__ void __launch_bounds__(kFastThreads, 1) decode_mma_kernel(const StreamParams sp) {
+__global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) decode_mma_kernel(const StreamParams sp) {
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
   using Ring = RingShape<FP8>;
   constexpr int kAhead = Ring::kAhead;
