@@ -149,10 +149,12 @@ template <int kAhead>
 __device__ __forceinline__ void wait_tiles_ahead() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
 }
-// Two e4m3 bytes (low 16 bits of x) -> two f16.
-__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
-  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x & 0xffffu), __NV_E4M3);
-  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+// Four e4m3 bytes -> 2 x two f16: `lo` from bytes 0, 1 and `hi` from bytes 2, 3 (one
+// conversion instruction each).
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(x));
 }
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x) {
   const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
@@ -499,10 +501,11 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
           // g, g + 8 of chunk 2s; r[2], r[3]: of chunk 2s + 1
           uint32_t r[4];
           ldmatrix_x4(r, k_tile + ((32u * s) ^ k_chunk_xor));
-          const uint32_t first[4] = {e4m3x2_to_f16x2(r[0]), e4m3x2_to_f16x2(r[1]),
-                                     e4m3x2_to_f16x2(r[0] >> 16), e4m3x2_to_f16x2(r[1] >> 16)};
-          const uint32_t second[4] = {e4m3x2_to_f16x2(r[2]), e4m3x2_to_f16x2(r[3]),
-                                      e4m3x2_to_f16x2(r[2] >> 16), e4m3x2_to_f16x2(r[3] >> 16)};
+          uint32_t first[4], second[4];  // a0 a1 a2 a3 of the two k-steps
+          e4m3x4_to_f16x2x2(r[0], first[0], first[2]);
+          e4m3x4_to_f16x2x2(r[1], first[1], first[3]);
+          e4m3x4_to_f16x2x2(r[2], second[0], second[2]);
+          e4m3x4_to_f16x2x2(r[3], second[1], second[3]);
           Ops::mma(s_even, first, q_frag[2 * s][0], q_frag[2 * s][1]);
           Ops::mma(s_odd, second, q_frag[2 * s + 1][0], q_frag[2 * s + 1][1]);
         }
@@ -580,14 +583,13 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
           // chunk 2j + 1.  Bytes (0, 2) are dim 2g of both tokens, bytes (1, 3) dim 2g + 1.
           uint32_t r[4];
           ldmatrix_x4_trans(r, v_tile + ((32u * j) ^ v_chunk_xor));
-          const uint32_t first[4] = {e4m3x2_to_f16x2(__byte_perm(r[0], 0u, 0x0020)),
-                                     e4m3x2_to_f16x2(__byte_perm(r[0], 0u, 0x0031)),
-                                     e4m3x2_to_f16x2(__byte_perm(r[1], 0u, 0x0020)),
-                                     e4m3x2_to_f16x2(__byte_perm(r[1], 0u, 0x0031))};
-          const uint32_t second[4] = {e4m3x2_to_f16x2(__byte_perm(r[2], 0u, 0x0020)),
-                                      e4m3x2_to_f16x2(__byte_perm(r[2], 0u, 0x0031)),
-                                      e4m3x2_to_f16x2(__byte_perm(r[3], 0u, 0x0020)),
-                                      e4m3x2_to_f16x2(__byte_perm(r[3], 0u, 0x0031))};
+          // one byte permute per register puts (dim 2g: tokens 2q, 2q+1) in the low half and
+          // (dim 2g+1: tokens 2q, 2q+1) in the high half
+          uint32_t first[4], second[4];
+          e4m3x4_to_f16x2x2(__byte_perm(r[0], 0u, 0x3120), first[0], first[1]);
+          e4m3x4_to_f16x2x2(__byte_perm(r[1], 0u, 0x3120), first[2], first[3]);
+          e4m3x4_to_f16x2x2(__byte_perm(r[2], 0u, 0x3120), second[0], second[1]);
+          e4m3x4_to_f16x2x2(__byte_perm(r[3], 0u, 0x3120), second[2], second[3]);
           Ops::mma(acc[2 * j], first, p_lo, p_hi);
           Ops::mma(acc[2 * j + 1], second, p_lo, p_hi);
         }
