@@ -149,3 +149,19 @@ def test_fp8_persistent_kernels(package, oracle, cuda_device, mode, dtype):
         error = ((out.cpu().float() - expected.float()).abs() / scale).max().item()
         assert error <= (2e-2 if dtype == torch.bfloat16 else 4e-3), error
     assert package.cabi.device_status() == 0
+
+
+def test_fp8_tensor_core_long_share(package, oracle, cuda_device):
+    """One long sequence and two split slots: a CTA's share is hundreds of pages, so every
+    warp walks several 32-page descriptor chunks and the ring wraps many times."""
+    q, k, v, table, lens = make_paged_inputs([20000, 300], seed=37, value_scale=0.5)
+    dev = cuda_device
+    k8, ks = package.quantize_kv_pool_e4m3(k.to(dev))
+    v8, vs = package.quantize_kv_pool_e4m3(v.to(dev))
+    expected = oracle.paged_attention(q, oracle.dequantize_pages(k8.cpu(), ks.cpu()),
+                                      oracle.dequantize_pages(v8.cpu(), vs.cpu()), table, lens)
+    for split_k in (2, 9):
+        out = package.grouped_splitk_decode_attention_fp8(
+            q.to(dev), k8, v8, ks, vs, table.to(dev), lens.to(dev), split_k=split_k)
+        assert_attention_close(out, expected)
+    assert package.cabi.device_status() == 0
