@@ -307,10 +307,50 @@ int qf_device_status(int32_t* status, int32_t reset);
  * cudaLaunchAttributeProgrammaticStreamSerialization: each may become resident
  * while the previous kernel of the stream is still running, does its index set-up
  * then, and waits (griddepcontrol.wait) for that kernel to complete and flush
- * before it reads any tensor or writes anything.  Kernels of other libraries before
- * or after them on the stream are ordered as usual.  enabled == 0 launches
- * everything the ordinary way (process-wide, read at launch and capture time). */
+ * before it reads any tensor or writes anything.  The one exception: the partial
+ * pass reads seq_lens and the block table during that set-up, i.e. possibly before
+ * the kernel launched two places earlier on the stream has flushed.  Step metadata
+ * that arrives by a copy (the usual case) is ordered as usual; metadata that a
+ * KERNEL updates in place on the same stream must be followed by
+ * qf_order_next_launch() (qf_advance_decode_metadata does that itself).
+ * enabled == 0 launches everything the ordinary way (process-wide, read at launch
+ * and capture time). */
 int qf_set_dependent_launch(int32_t enabled);
+
+/* The next kernel this library launches from the calling process is launched the
+ * ordinary way (it starts after everything earlier on its stream has completed and
+ * flushed), whatever qf_set_dependent_launch says; later launches chain again.
+ * Call it after a kernel of your own has written positions, seq_lens, the slot
+ * mapping or the block table in place on the stream. */
+int qf_order_next_launch(void);
+
+/* ------------------------------------------------------------------------
+ * Device-side advance of the step metadata of a stable decode cohort, in place,
+ * so that consecutive decode steps (or the K steps of an unrolled graph) need no
+ * host rebuild and no host-to-device copy.  Replaces the torch ops of
+ * IterationLoop::advance_decode_state (engine/cpp/src/iteration_loop.cpp:500-528;
+ * the per-step tensors of engine/graph/unrolled_graph_decoder.py:92-130 are its
+ * K-fold application).  For every b < batch:
+ *   positions[b] += 1;  seq_lens[b] += 1;
+ *   slot_mapping[b] = block_table[b, positions[b] / page_size] * page_size
+ *                     + positions[b] % page_size          (the NEW position)
+ * The table is immutable for the cohort (requests reserve their whole page
+ * sequence at admission).  A position whose logical page lies beyond table_width,
+ * or whose page id is outside [0, num_pages), gets slot -1 -- which the KV-write
+ * kernel skips -- and the device status word becomes 4 / 2; the reference's
+ * gather would fault there.  positions, seq_lens, slot_mapping: int32 or int64,
+ * contiguous; block_table int32 or int64 with strides in elements.
+ * Ends with qf_order_next_launch(). */
+#define QF_STATUS_BAD_PAGE_ID 2
+#define QF_STATUS_MERGE_TIMEOUT 3
+#define QF_STATUS_POSITION_PAST_TABLE 4
+int qf_advance_decode_metadata(void* positions, int32_t positions_dtype,
+                               void* seq_lens, int32_t lens_dtype,
+                               void* slot_mapping, int32_t slot_dtype,
+                               const void* block_table, int32_t table_dtype,
+                               int64_t table_stride_b, int64_t table_stride_p,
+                               int64_t table_width, int64_t num_pages,
+                               int32_t batch, int32_t page_size, void* stream);
 
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the

@@ -262,6 +262,23 @@ def decode_step_inputs(cur_lens, block_tables, max_blocks, page_size=16):
             np.asarray(slots, dtype=np.int64))
 
 
+def advance_decode_state(positions, seq_lens, block_table, page_size=16):
+    """numpy restatement of IterationLoop::advance_decode_state
+    (engine/cpp/src/iteration_loop.cpp:500-528): positions + 1, lengths + 1, and
+    slot = table[b, p // page] * page + p % page at the NEW position p (the same
+    relation engine/cpp/tests/test_iteration_loop.py:545-551 asserts between
+    consecutive decode rows).  Returns new (positions, seq_lens, slot_mapping int64);
+    a position beyond the table is an IndexError, as the reference's gather."""
+    positions = np.asarray(positions).astype(np.int64) + 1
+    seq_lens = np.asarray(seq_lens).astype(np.int64) + 1
+    table = np.asarray(block_table).astype(np.int64)
+    logical = positions // page_size
+    if len(positions) and (logical.max() >= table.shape[1] or positions.min() < 0):
+        raise IndexError("position beyond the block table")
+    pages = table[np.arange(len(positions)), logical] if len(positions) else np.zeros(0, np.int64)
+    return positions, seq_lens, pages * page_size + positions % page_size
+
+
 def ulp_distance_fp16(actual, expected, reference_magnitude=None):
     """|actual - expected| in units of the fp16 spacing at max(|expected|,
     reference_magnitude): cancellation in x1*c - x2*s can leave a result far

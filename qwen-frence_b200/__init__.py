@@ -20,6 +20,7 @@ current torch stream; none has a CPU fallback):
     quantize_kv_pool_e4m3, dequantize_kv_pool_e4m3,
     native_decode_rope_kv_write_fp8, packed_qkv_rope_cache_fp8,
     grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
+    advance_decode_state                                   custom_kernels/decode_state.py
 """
 
 from __future__ import annotations
@@ -49,6 +50,7 @@ _EXPORTS = {
     "native_decode_rope_kv_write_fp8": "fp8_paged_kv",
     "packed_qkv_rope_cache_fp8": "fp8_paged_kv",
     "grouped_splitk_decode_attention_fp8": "fp8_paged_kv",
+    "advance_decode_state": "decode_state",
 }
 _LOCAL = {"cabi": "_cabi", "build": "build", "kv_layout": "kv_layout", "workloads": "workloads",
           "decode_step": "decode_step", "sharding": "sharding"}

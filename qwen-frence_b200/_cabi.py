@@ -33,7 +33,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_gqa_splitk_profile_out", "qf_device_status", "qf_set_tuning",
     "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
-    "qf_set_dependent_launch",
+    "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -132,6 +132,9 @@ def library():
     lib.qf_device_status.argtypes = [POINTER(c_int32), c_int32]
     lib.qf_set_tuning.argtypes = [c_int32, c_int32]
     lib.qf_set_dependent_launch.argtypes = [c_int32]
+    lib.qf_order_next_launch.argtypes = []
+    lib.qf_advance_decode_metadata.argtypes = (
+        [c_void_p, c_int32] * 4 + [c_int64] * 4 + [c_int32, c_int32, c_void_p])
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32
@@ -207,6 +210,12 @@ def set_dependent_launch(enabled=True):
     check(library().qf_set_dependent_launch(1 if enabled else 0))
 
 
+def order_next_launch():
+    """The next kernel of the library starts only after everything earlier on its
+    stream has completed (needed after a foreign kernel rewrote step metadata)."""
+    check(library().qf_order_next_launch())
+
+
 def fused_kernel_plan(args):
     """(kernel name, resident CTAs per KV head) the fused attention call would use."""
     kernel, ctas = c_int32(0), c_int32(0)
@@ -216,7 +225,8 @@ def fused_kernel_plan(args):
 
 
 def device_status(reset=True):
-    """Status word of the kernels on the current device (0 = clean, 2 = bad page id)."""
+    """Status word of the kernels on the current device (0 = clean, 2 = bad page id,
+    3 = merge poll gave up, 4 = a position advanced past its block table)."""
     value = c_int32(0)
     check(library().qf_device_status(ctypes.byref(value), 1 if reset else 0))
     return value.value

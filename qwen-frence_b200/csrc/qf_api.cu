@@ -13,7 +13,15 @@ namespace {
 thread_local char g_error[512] = "";
 __device__ int g_status_word = 0;
 int g_dependent_launch = 1;
+int g_ordered_launch = 0;
 }  // namespace
+
+void request_ordered_launch() { g_ordered_launch = 1; }
+int take_ordered_launch() {
+  const int taken = g_ordered_launch;
+  g_ordered_launch = 0;
+  return taken;
+}
 
 int dependent_launch_enabled() { return g_dependent_launch; }
 void disable_dependent_launch() { g_dependent_launch = 0; }
@@ -48,6 +56,11 @@ const char* qf_last_error(void) { return qf::g_error; }
 
 int qf_set_dependent_launch(int32_t enabled) {
   qf::g_dependent_launch = enabled ? 1 : 0;
+  return QF_OK;
+}
+
+int qf_order_next_launch(void) {
+  qf::request_ordered_launch();
   return QF_OK;
 }
 

@@ -34,10 +34,14 @@ int* device_status_word();
 // launches the ordinary way (0); see qf_set_dependent_launch.
 int dependent_launch_enabled();
 void disable_dependent_launch();
+// qf_order_next_launch(): the next launch_chained() launches the ordinary way.
+void request_ordered_launch();
+int take_ordered_launch();  // 1 once after a request, else 0
 
 // Status codes kernels may record (1 is reserved).
-constexpr int kStatusBadPageId = 2;
-constexpr int kStatusMergeTimeout = 3;  // a warp gave up waiting for an earlier piece's merge
+constexpr int kStatusBadPageId = QF_STATUS_BAD_PAGE_ID;
+constexpr int kStatusMergeTimeout = QF_STATUS_MERGE_TIMEOUT;  // a warp gave up waiting for an earlier piece's merge
+constexpr int kStatusPositionPastTable = QF_STATUS_POSITION_PAST_TABLE;
 
 // ---- device side ---------------------------------------------------------
 #ifdef __CUDACC__
@@ -95,6 +99,14 @@ __device__ __forceinline__ int64_t load_index(const void* base, int dtype, int64
   return static_cast<const int32_t*>(base)[offset];
 }
 
+__device__ __forceinline__ void store_index(void* base, int dtype, int64_t offset, int64_t value) {
+  if (dtype == QF_INDEX_I64) {
+    static_cast<int64_t*>(base)[offset] = value;
+  } else {
+    static_cast<int32_t*>(base)[offset] = static_cast<int32_t>(value);
+  }
+}
+
 __device__ __forceinline__ float load_position(const void* base, int dtype, int64_t offset) {
   if (dtype == QF_INDEX_F32) return static_cast<const float*>(base)[offset];
   if (dtype == QF_INDEX_I64) return static_cast<float>(static_cast<const int64_t*>(base)[offset]);
@@ -135,7 +147,8 @@ inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 blo
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  const bool ordered = take_ordered_launch() != 0;
+  config.numAttrs = (dependent_launch_enabled() && !ordered) ? 1 : 0;
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
   if (err == cudaErrorNotSupported && config.numAttrs != 0) {
     (void)cudaGetLastError();

@@ -75,6 +75,7 @@ class DecodeStep:
                 torch.empty((b, k, kv_layout.Q_HEADS), dtype=torch.float32, device=self.device),
             )
         self.graph = None
+        self.steps_graph = None
         self.host_graph = None
         self._host = None
 
@@ -190,6 +191,48 @@ class DecodeStep:
         torch.cuda.current_stream(self.device).wait_stream(stream)
         self.graph = graph
         return graph
+
+    def advance(self):
+        """Move the step metadata on by one token on the device, in place (no host
+        rebuild, no copy): positions and lengths + 1, slots looked up in the block
+        table, which must already hold the pages of the coming tokens."""
+        if self.batch:
+            self.package.advance_decode_state(
+                self.positions, self.seq_lens, self.slot_mapping, self.block_table,
+                num_pages=self.workload.num_pages)
+
+    def capture_steps(self, count, warmup=1):
+        """Record `count` consecutive decode steps, each followed by the device-side
+        metadata advance, into one graph -- the shape of the reference's unrolled
+        decoder (engine/graph/unrolled_graph_decoder.py:92-130) with its per-step
+        metadata tensors replaced by one set advanced in place.  Warm-up runs advance
+        the metadata too; it is restored from the workload before recording."""
+        if self.batch == 0:
+            return None
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+
+        def run():
+            for _ in range(count):
+                self.step()
+                self.advance()
+
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                run()
+            self.reset_metadata()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.steps_graph = graph
+        return graph
+
+    def reset_metadata(self):
+        """Step metadata back to the workload's first step."""
+        for name in ("positions", "seq_lens", "slot_mapping", "block_table"):
+            getattr(self, name).copy_(getattr(self.workload, name))
 
     def replay(self):
         if self.batch == 0 or self.graph is None:

@@ -83,7 +83,7 @@ class Workload:
 
 
 def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers=None,
-                   batch=None, pool_pages=None, shard_policy="snake"):
+                   batch=None, pool_pages=None, shard_policy="snake", reserve_tokens=0):
     """Build rank `rank`'s share of workload `name`.
 
     scaling "weak": every rank gets its own full-size batch (different seed per
@@ -91,7 +91,10 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
     `sharding.partition_sequences`; each rank owns its sequences' pages.
     Page ids are local to the rank.  The pool is filled through a PagePool whose
     free list is randomly permuted first, so block tables are a seeded random
-    permutation of the pool.
+    permutation of the pool.  `reserve_tokens` > 0 reserves pages for that many
+    further tokens per sequence at admission (block tables then cover the tokens
+    that consecutive decode steps will append, as the reference's engine does for a
+    stable cohort, engine/cpp/src/iteration_loop.cpp:512-514).
     """
     spec = WORKLOADS[name]
     layers = spec["layers"] if layers is None else layers
@@ -108,7 +111,8 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
 
     local_batch = len(contexts)
     lengths = [c + 1 for c in contexts]
-    needed = sum(-(-n // kv_layout.PAGE_SIZE) for n in lengths)
+    reserved = [n + int(reserve_tokens) for n in lengths]
+    needed = sum(-(-n // kv_layout.PAGE_SIZE) for n in reserved)
     if pool_pages is None:
         if name == "cpu_single_layer_b8":
             pool_pages = 512
@@ -129,11 +133,11 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
         filler = max(0, int(0.9 * pool_pages) - needed)
         del pool.free_pages[:filler]
     if local_batch:
-        pool.allocate(lengths)
+        pool.allocate(reserved)
     max_blocks = max([len(t) for t in pool.block_tables] + [1])
     if local_batch:
         positions, seq_lens, table, slots = kv_layout.decode_step_inputs(
-            pool.cur_lens, pool.block_tables, max_blocks)
+            lengths, pool.block_tables, max_blocks)
     else:
         import numpy as np
 
@@ -149,6 +153,7 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
         positions=torch.from_numpy(positions), slot_mapping=torch.from_numpy(slots),
         live_pages=torch.tensor(live, dtype=torch.long), seed=seed,
         meta=dict(scaling=scaling, world_size=world_size, rank=rank, filler_pages=filler,
+                  reserve_tokens=int(reserve_tokens),
                   doc=spec["doc"]),
     )
 

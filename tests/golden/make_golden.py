@@ -18,7 +18,8 @@ Reference functions exercised (paths inside the reference tree):
   baseline/naive_forward.py                        apply_rotary_pos_emb
   engine/kvcache/paged_forward.py                  build_rope_from_positions
   engine/kvcache/paged_kv_cache.py                 PagedKVCache
-  engine/graph/paged_graph_decoder.py              build_decode_step_inputs
+  engine/graph/paged_graph_decoder.py              build_decode_step_inputs (one step, and
+                                                   the consecutive steps of a stable cohort)
   experiments/quant/attention.py                   quantize, dequantize
 """
 
@@ -166,6 +167,28 @@ def main():
         slot_mapping=slots.numpy(), max_blocks=np.int64(max_blocks),
     )
     del trace
+
+    # ------------------------- metadata of consecutive steps of a stable cohort
+    # Pages are reserved for the whole run at admission (what the device-side advance of
+    # engine/cpp/src/iteration_loop.cpp:500-528 relies on); build_decode_step_inputs is
+    # then evaluated at every step's lengths.  Step s + 1 must equal the advance of step s.
+    steps, start_lens = 40, [7, 16, 33, 1, 250]
+    cache = kv_cache.PagedKVCache(cfg, len(start_lens), 128, 16, "cpu", torch.float16)
+    generator = torch.Generator().manual_seed(5)
+    cache.free_blocks = [cache.free_blocks[i] for i in torch.randperm(128, generator=generator).tolist()]
+    cache.allocate_block([n + steps - 1 for n in start_lens])
+    max_blocks = max(len(t) for t in cache.block_tables) + 1
+    rows = {"positions": [], "seq_lens": [], "slot_mapping": []}
+    for step in range(steps):
+        cache.cur_lens = [n + step for n in start_lens]
+        _, positions, seq_lens, table, slots = graph.build_decode_step_inputs(
+            cache, [0] * len(start_lens), max_blocks, "cpu")
+        rows["positions"].append(positions.numpy())
+        rows["seq_lens"].append(seq_lens.numpy())
+        rows["slot_mapping"].append(slots.numpy())
+    np.savez_compressed(
+        GOLDEN_DIR / "metadata_steps.npz", block_table=table.numpy(),
+        **{key: np.stack(value) for key, value in rows.items()})
 
     # ------------------------------------------------------- split-K policy
     contexts = [1, 16, 1023, 1024, 1280, 1281, 2048, 4096, 32768]

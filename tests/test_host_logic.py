@@ -72,6 +72,12 @@ def test_c_side_validation_without_a_gpu(package):
         cabi.check(-1)
     assert lib.qf_set_tuning(99, 0) == -1
     assert lib.qf_set_tuning(0, 0) == 0
+    advance = lambda *dtypes, batch=1, page=16: lib.qf_advance_decode_metadata(
+        None, dtypes[0], None, dtypes[1], None, dtypes[2], None, dtypes[3], 1, 1, 1, 1, batch, page, None)
+    assert advance(1, 0, 1, 0, batch=0) == 0            # an empty cohort is a no-op, nothing launched
+    assert advance(2, 0, 1, 0) == -1 and b"integer dtype" in lib.qf_last_error()
+    assert advance(1, 0, 1, 0, page=0) == -1 and b"page size" in lib.qf_last_error()
+    assert advance(1, 0, 1, 0) == -1 and b"must not be null" in lib.qf_last_error()
 
 
 def test_missing_library_fails_loudly_with_one_build_command(package):
@@ -138,6 +144,10 @@ def test_cpu_tensors_are_rejected_not_computed(package):
         package.native_grouped_splitk_decode_attention(q, pool, pool, table, lens, split_k=2)
     with pytest.raises(ValueError, match="CUDA"):
         package.packed_qkv_rope_cache(torch.zeros(2, 2048, dtype=torch.float16), lens, lens, pool, pool)
+    with pytest.raises(ValueError, match="CUDA"):
+        package.advance_decode_state(lens.long(), lens, lens.long(), table)
+    with pytest.raises(ValueError, match="one entry per sequence"):
+        package.advance_decode_state(lens.long(), lens[:1], lens.long(), table)
     with pytest.raises(ValueError, match="CUDA"):
         package.rope_kv_write(q[None].transpose(1, 2)[:, :, :, :], pool[:1, :2].transpose(1, 2)[:, :, :2],
                               pool[:1, :2].transpose(1, 2)[:, :, :2], lens, lens, pool, pool)
@@ -232,6 +242,15 @@ def test_workloads_have_the_configured_shapes(package):
     w2 = build("decode_b64")
     assert w2.contexts == w.contexts and torch.equal(w2.block_table, w.block_table)  # seeded
     assert build("decode_b64", rank=1, world_size=2).contexts != w.contexts          # weak: own batch
+
+    # pages reserved at admission for the tokens of coming steps: same first step,
+    # wider tables that the device-side advance can walk
+    plain, reserved = build("decode_b64", batch=8, layers=1), build("decode_b64", batch=8, layers=1, reserve_tokens=40)
+    assert torch.equal(reserved.positions, plain.positions) and torch.equal(reserved.seq_lens, plain.seq_lens)
+    for b, context in enumerate(reserved.contexts):
+        pages = reserved.block_table[b, :-(-(context + 1 + 40) // 16)].tolist()
+        assert len(set(pages)) == len(pages) and all(0 <= page < reserved.num_pages for page in pages)
+    assert reserved.live_pages.numel() > plain.live_pages.numel()
 
     w = build("long_skew_b4")
     assert sorted(w.contexts) == [512, 4096, 16384, 32768] and w.block_table.shape[1] == 2049

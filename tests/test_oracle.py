@@ -191,6 +191,26 @@ def test_metadata_against_reference(oracle):
         assert actual.dtype == data[key].dtype and np.array_equal(actual, data[key]), key
 
 
+def test_advance_decode_state_against_reference_steps(oracle):
+    """Golden: build_decode_step_inputs evaluated at 40 consecutive steps of a cohort
+    whose pages were reserved up front; the advance of step s must be step s + 1
+    (engine/cpp/src/iteration_loop.cpp:500-528; the relation asserted by
+    engine/cpp/tests/test_iteration_loop.py:545-551)."""
+    data = np.load(GOLDEN_DIR / "metadata_steps.npz")
+    table = data["block_table"]
+    positions, seq_lens = data["positions"][0], data["seq_lens"][0]
+    for step in range(1, data["positions"].shape[0]):
+        positions, seq_lens, slots = oracle.advance_decode_state(positions, seq_lens, table)
+        assert np.array_equal(positions, data["positions"][step])
+        assert np.array_equal(seq_lens, data["seq_lens"][step])
+        assert np.array_equal(slots, data["slot_mapping"][step])
+    # page size 4, the block size of the reference's own test
+    positions, seq_lens, slots = oracle.advance_decode_state([2, 3, 10], [3, 4, 11], [[5, 9, 1], [7, 2, 8], [6, 0, 3]], 4)
+    assert slots.tolist() == [5 * 4 + 3, 2 * 4 + 0, 3 * 4 + 3]
+    with pytest.raises(IndexError):
+        oracle.advance_decode_state([15], [16], [[3]])
+
+
 # ---------------------------------------------------------------------- fp8
 
 def test_e4m3_decode_table_matches_reference_and_torch(oracle):
