@@ -3,6 +3,7 @@ GQA paged decode attention with split-K combine, over all 28 layers).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--split-k S]
     python bench.py --impl reference ...        # the CPU implementation, same metric
+    python bench.py --op layer_glue             # the small kernels either side of the path
 
 A step is one pass of the hot path over one batch of synthetic input: for every
 layer, the packed-QKV RoPE + KV write and the attention over the block tables.
@@ -69,6 +70,9 @@ def parse_args():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--workload", default="decode_b64")
+    parser.add_argument("--op", choices=("decode_step", "layer_glue"), default="decode_step",
+                        help="layer_glue: residual-add + RMSNorm and the device-side metadata advance\n"
+                             "(one GPU; prints its own JSON line)")
     parser.add_argument("--scaling", choices=("weak", "strong"), default="weak")
     parser.add_argument("--split-k", type=int, default=0, help="0: plan from host bounds")
     parser.add_argument("--layers", type=int, default=0, help="0: the workload's own (28)")
@@ -259,6 +263,114 @@ def run_reference(args, rank, world):
     }))
 
 
+def run_layer_glue(args):
+    """--op layer_glue: the kernels that sit either side of the hot path in a decode layer.
+
+    residual_add_rms_norm: (a) at decode sizes, 56 calls (two per layer) chained in one
+    graph -- launch latency, reported as microseconds per call; (b) 4096 x 8192 rows
+    (268 MB moved, larger than L2) -- HBM bound, reported against the measured copy peak.
+    unrolled steps: `--steps` consecutive decode steps of the workload recorded as ONE
+    graph with the metadata advanced on the device, against the same number of single-step
+    graph replays; no host-to-device copy in either."""
+    import torch
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    package = entry.load_package()
+    generator = torch.Generator(device=device).manual_seed(args.seed)
+
+    def time_graph(record, replays):
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            record()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            record()
+        torch.cuda.current_stream(device).wait_stream(side)
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / replays
+
+    def norm_inputs(rows, hidden):
+        make = lambda *shape: torch.randn(shape, device=device, dtype=torch.float16, generator=generator)
+        return make(rows, hidden), make(rows, hidden), make(hidden)
+
+    decode_sizes = {}
+    for rows in (64, 256):
+        residual, branch, weight = norm_inputs(rows, 1536)
+        calls = 2 * LAYERS
+        ms = time_graph(lambda: [package.residual_add_rms_norm(residual, branch, weight) for _ in range(calls)],
+                        args.steps)
+        decode_sizes[f"{rows}x1536"] = {"us_per_call": ms * 1e3 / calls, "calls_per_graph": calls}
+
+    rows, hidden = 4096, 8192
+    sets = [norm_inputs(rows, hidden) for _ in range(3)]  # 3 x 134 MB of inputs: beyond L2
+    ms = time_graph(lambda: [package.residual_add_rms_norm(*inputs) for inputs in sets], args.steps) / len(sets)
+    moved = 4 * rows * hidden * 2 + hidden * 2
+    peak, peak_kind = measured_peak_gbs()
+    achieved = moved / (ms * 1e-3) / 1e9
+    oracle = entry.load_oracle()
+    cpu_inputs = [t.cpu() for t in sets[0]]
+    cpu_start = time.perf_counter()
+    oracle.residual_add_rms_norm(*cpu_inputs)
+    cpu_seconds = time.perf_counter() - cpu_start
+
+    # ---- consecutive decode steps without the host ---------------------------------
+    steps = max(2, min(args.steps, 16))
+    workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=args.layers or None,
+                                                reserve_tokens=steps)
+    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
+    step.load_packed_rows()
+    step.capture(warmup=2)
+    step.capture_steps(steps)
+    torch.cuda.synchronize()
+
+    def replay_ms(run, count):
+        for _ in range(3):
+            run()
+            step.reset_metadata()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(count):
+            run()
+        end.record()
+        torch.cuda.synchronize()
+        step.reset_metadata()
+        return start.elapsed_time(end) / count
+
+    single_ms = replay_ms(step.replay, steps)
+    unrolled_ms = replay_ms(step.steps_graph.replay, 1) / steps
+    status = package.cabi.device_status()
+    print(json.dumps({
+        "op": "layer_glue", "n_gpus": 1, "data": "synthetic", "dtype": "f16 storage, f32 accumulate",
+        "residual_add_rms_norm": {
+            "decode": decode_sizes,
+            "large": {"rows": rows, "hidden": hidden, "ms_per_call": ms, "algorithmic_bytes": moved,
+                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                                   "frac": achieved / peak, "peak_kind": f"of {peak_kind}"},
+                      "cpu_baseline": {"value": moved / cpu_seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+                                       "kind": "port", "sample": "numpy oracle, one call on the same rows"}},
+        },
+        "unrolled_decode_steps": {
+            "workload": args.workload, "steps_per_graph": steps, "batch": workload.batch,
+            "ms_per_step_single_step_graph": single_ms, "ms_per_step_unrolled_graph": unrolled_ms,
+            "tokens_per_s_unrolled": workload.batch / (unrolled_ms * 1e-3),
+            "h2d_bytes_per_step": 0, "kernel_launches_per_graph": steps * (step.kernel_launches_per_step + 1),
+        },
+        "device_status": status,
+    }))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -275,6 +387,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     if args.warmup < 3:
         args.warmup = 3
+    if args.op == "layer_glue":
+        if rank == 0:
+            run_layer_glue(args)
+        return
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     distributed = world > 1

@@ -352,6 +352,27 @@ int qf_advance_decode_metadata(void* positions, int32_t positions_dtype,
                                int64_t table_width, int64_t num_pages,
                                int32_t batch, int32_t page_size, void* stream);
 
+/* ------------------------------------------------------------------------
+ * RMSNorm and residual-add + RMSNorm, the steps either side of attention in a
+ * decode layer.  Replace rms_norm (custom_kernels/fused_rms.py:52-75) and
+ * residual_add_rms_norm (custom_kernels/fused_rms.py:107-135; caller
+ * engine/graph/paged_graph_decoder.py:303-309, :325-331).  Per row of `hidden`
+ * fp16 / bf16 elements (row strides in elements, unit stride inside a row):
+ *   summed     = T(residual + branch)                      (stored; residual form only)
+ *   rms        = sqrtf(sum(float(summed)^2) / hidden + epsilon)
+ *   normalized = T(float(weight) * float(summed) / rms)
+ * `summed` is the exact fp16 / bf16 sum; the normalisation reads that rounded
+ * value, as the reference does.  Inputs and outputs may alias row for row
+ * (summed == residual, out == x).  rows == 0 is a no-op. */
+int qf_rms_norm(const void* x, int64_t x_row_stride, const void* weight, void* out,
+                int64_t out_row_stride, int64_t rows, int32_t hidden, int32_t dtype,
+                float epsilon, void* stream);
+int qf_residual_add_rms_norm(const void* residual, int64_t residual_row_stride,
+                             const void* branch, int64_t branch_row_stride,
+                             const void* weight, void* summed, int64_t summed_row_stride,
+                             void* normalized, int64_t normalized_row_stride, int64_t rows,
+                             int32_t hidden, int32_t dtype, float epsilon, void* stream);
+
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the
  * stride-generic kernel; 2 fast per-partition kernel only, no persistent kernel;

@@ -279,6 +279,37 @@ def advance_decode_state(positions, seq_lens, block_table, page_size=16):
     return positions, seq_lens, pages * page_size + positions % page_size
 
 
+# ---- RMSNorm -------------------------------------------------------------------
+
+def rms_norm(x, weight, epsilon=1e-6):
+    """RMSNorm of the last dimension in fp32, one rounding to x's dtype: restates
+    rms_norm_reference (custom_kernels/fused_rms.py:137-140), whose arithmetic is the
+    Triton kernel's (:38-42): weight * x / sqrt(mean(x^2) + epsilon).  The mean is
+    accumulated in float64 and rounded once to fp32."""
+    values = x.detach().cpu().float().numpy()
+    mean = np.mean(values.astype(np.float64) ** 2, axis=-1, keepdims=True).astype(np.float32)
+    rms = np.sqrt(mean + np.float32(epsilon), dtype=np.float32)
+    scaled = (weight.detach().cpu().float().numpy() * values) / rms
+    return torch.from_numpy(scaled.astype(np.float32)).to(x.dtype)
+
+
+def residual_add_rms_norm(residual, branch, weight, epsilon=1e-6):
+    """(residual + branch rounded to the model dtype, RMSNorm of that rounded sum):
+    restates _residual_add_rms_norm_kernel (custom_kernels/fused_rms.py:78-104)."""
+    summed = (residual.detach().cpu().float() + branch.detach().cpu().float()).to(residual.dtype)
+    return summed, rms_norm(summed, weight, epsilon)
+
+
+def ulp_distance(actual, expected):
+    """|actual - expected| in units of the spacing of expected's own 16-bit format."""
+    a, e = actual.detach().cpu(), expected.detach().cpu()
+    fraction_bits = 10 if e.dtype == torch.float16 else 7
+    smallest = -14 if e.dtype == torch.float16 else -126
+    magnitude = e.float().abs().clamp_min(2.0 ** smallest)
+    spacing = torch.exp2(torch.floor(torch.log2(magnitude)) - fraction_bits)
+    return (a.float() - e.float()).abs() / spacing
+
+
 def ulp_distance_fp16(actual, expected, reference_magnitude=None):
     """|actual - expected| in units of the fp16 spacing at max(|expected|,
     reference_magnitude): cancellation in x1*c - x2*s can leave a result far

@@ -21,6 +21,7 @@ current torch stream; none has a CPU fallback):
     native_decode_rope_kv_write_fp8, packed_qkv_rope_cache_fp8,
     grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
     advance_decode_state                                   custom_kernels/decode_state.py
+    rms_norm, residual_add_rms_norm                        custom_kernels/fused_rms.py
 """
 
 from __future__ import annotations
@@ -51,6 +52,8 @@ _EXPORTS = {
     "packed_qkv_rope_cache_fp8": "fp8_paged_kv",
     "grouped_splitk_decode_attention_fp8": "fp8_paged_kv",
     "advance_decode_state": "decode_state",
+    "rms_norm": "fused_rms",
+    "residual_add_rms_norm": "fused_rms",
 }
 _LOCAL = {"cabi": "_cabi", "build": "build", "kv_layout": "kv_layout", "workloads": "workloads",
           "decode_step": "decode_step", "sharding": "sharding"}

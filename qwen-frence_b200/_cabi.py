@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
     "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
+    "qf_rms_norm", "qf_residual_add_rms_norm",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -135,6 +136,11 @@ def library():
     lib.qf_order_next_launch.argtypes = []
     lib.qf_advance_decode_metadata.argtypes = (
         [c_void_p, c_int32] * 4 + [c_int64] * 4 + [c_int32, c_int32, c_void_p])
+    lib.qf_rms_norm.argtypes = [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_float, c_void_p]
+    lib.qf_residual_add_rms_norm.argtypes = [
+        c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+        c_int64, c_int32, c_int32, c_float, c_void_p]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32

@@ -21,6 +21,7 @@ Reference functions exercised (paths inside the reference tree):
   engine/graph/paged_graph_decoder.py              build_decode_step_inputs (one step, and
                                                    the consecutive steps of a stable cohort)
   experiments/quant/attention.py                   quantize, dequantize
+  custom_kernels/fused_rms.py                      rms_norm_reference
 """
 
 from __future__ import annotations
@@ -189,6 +190,42 @@ def main():
     np.savez_compressed(
         GOLDEN_DIR / "metadata_steps.npz", block_table=table.numpy(),
         **{key: np.stack(value) for key, value in rows.items()})
+
+    # --------------------------------------- RMSNorm, residual-add + RMSNorm
+    # rms_norm_reference is the CPU statement the reference checks its Triton kernel
+    # against (custom_kernels/fused_rms.py:137-140, :166-180); the residual form is the
+    # model-dtype add followed by it (experiments/decode/benchmark_fa3_fusion_kernels.py:71-78);
+    # nn.RMSNorm is what the model runs without custom kernels (baseline/naive_forward.py:59-64).
+    fused_rms = load(root / "custom_kernels/fused_rms.py", "ref_fused_rms")
+    generator = torch.Generator().manual_seed(21)
+    norm_cases = {}
+    for name, rows, hidden, dtype, epsilon in (
+            ("decode_b16_f16", 16, 1536, torch.float16, 1e-6),
+            ("decode_b8_bf16", 8, 1536, torch.bfloat16, 1e-6),
+            ("odd_width_f16", 5, 1000, torch.float16, 1e-5),
+            ("wide_rows_f16", 2, 8192 + 264, torch.float16, 1e-6),
+            ("tiny_values_bf16", 4, 96, torch.bfloat16, 1e-6)):
+        residual = torch.randn(rows, hidden, generator=generator).to(dtype)
+        branch = torch.randn(rows, hidden, generator=generator).to(dtype)
+        weight = torch.randn(hidden, generator=generator).to(dtype)
+        if name.startswith("tiny"):
+            residual, branch = residual * 1e-3, branch * 1e-3
+            residual[0], branch[0] = 0, 0  # a zero row: epsilon alone under the root
+        summed = residual + branch
+        module = torch.nn.RMSNorm(hidden, eps=epsilon, dtype=dtype)
+        with torch.no_grad():
+            module.weight.copy_(weight)
+            torch_norm = module(summed)
+        norm_cases[name] = dict(
+            residual=bits(residual), branch=bits(branch), weight=bits(weight), epsilon=np.float64(epsilon),
+            dtype="bfloat16" if dtype == torch.bfloat16 else "float16", summed=bits(summed),
+            normalized=bits(fused_rms.rms_norm_reference(summed, weight, epsilon)),
+            plain=bits(fused_rms.rms_norm_reference(residual, weight, epsilon)),
+            torch_rmsnorm=bits(torch_norm))
+    np.savez_compressed(GOLDEN_DIR / "rms_norm_cases.npz",
+                        **{f"{name}/{key}": value for name, case in norm_cases.items()
+                           for key, value in case.items()})
+    print("rms norm cases:", len(norm_cases))
 
     # ------------------------------------------------------- split-K policy
     contexts = [1, 16, 1023, 1024, 1280, 1281, 2048, 4096, 32768]

@@ -75,7 +75,7 @@ def test_advance_beyond_the_table_is_flagged_and_harmless(package, cuda_device):
     assert package.cabi.device_status() in (2, 4)  # both were recorded; the last write stays
     package.advance_decode_state(positions[2:3].clone(), seq_lens[2:3].clone(), slots[2:3].clone(), table[2:3])
     assert package.cabi.device_status() == 4       # position 33 of a two-page table
-    package.advance_decode_state(positions[3:].clone(), seq_lens[3:].clone(), slots[3:].clone(),
+    package.advance_decode_state(torch.full_like(positions[3:], 15), seq_lens[3:].clone(), slots[3:].clone(),
                                  torch.tensor([[0, -1]], dtype=torch.int32, device=cuda_device), num_pages=50)
     assert package.cabi.device_status() == 2
     # a row with slot -1 leaves the pools untouched

@@ -78,6 +78,11 @@ def test_c_side_validation_without_a_gpu(package):
     assert advance(2, 0, 1, 0) == -1 and b"integer dtype" in lib.qf_last_error()
     assert advance(1, 0, 1, 0, page=0) == -1 and b"page size" in lib.qf_last_error()
     assert advance(1, 0, 1, 0) == -1 and b"must not be null" in lib.qf_last_error()
+    assert lib.qf_rms_norm(None, 8, None, None, 8, 0, 8, 0, 1e-6, None) == 0   # no rows: nothing launched
+    assert lib.qf_rms_norm(None, 8, None, None, 8, 4, 8, 7, 1e-6, None) == -1 and b"fp16 or bf16" in lib.qf_last_error()
+    assert lib.qf_rms_norm(None, 8, None, None, 8, 4, 0, 0, 1e-6, None) == -1 and b"hidden" in lib.qf_last_error()
+    assert lib.qf_residual_add_rms_norm(None, 8, None, 8, None, None, 8, None, 8, 4, 8, 1, 1e-6, None) == -1
+    assert b"must not be null" in lib.qf_last_error()
 
 
 def test_missing_library_fails_loudly_with_one_build_command(package):
@@ -146,6 +151,11 @@ def test_cpu_tensors_are_rejected_not_computed(package):
         package.packed_qkv_rope_cache(torch.zeros(2, 2048, dtype=torch.float16), lens, lens, pool, pool)
     with pytest.raises(ValueError, match="CUDA"):
         package.advance_decode_state(lens.long(), lens, lens.long(), table)
+    hidden = torch.zeros(2, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="CUDA"):
+        package.rms_norm(hidden, hidden[0])
+    with pytest.raises(ValueError, match="CUDA"):
+        package.residual_add_rms_norm(hidden, hidden, hidden[0])
     with pytest.raises(ValueError, match="one entry per sequence"):
         package.advance_decode_state(lens.long(), lens[:1], lens.long(), table)
     with pytest.raises(ValueError, match="CUDA"):

@@ -211,6 +211,39 @@ def test_advance_decode_state_against_reference_steps(oracle):
         oracle.advance_decode_state([15], [16], [[3]])
 
 
+# ------------------------------------------------------------------ RMSNorm
+
+def _norm_cases():
+    data = np.load(GOLDEN_DIR / "rms_norm_cases.npz")
+    for name in sorted({key.split("/")[0] for key in data.files}):
+        dtype_name = str(data[f"{name}/dtype"])
+        yield name, {key.split("/")[1]: (tensor_from_bits(data[key], dtype_name) if data[key].dtype == np.int16
+                                         else data[key])
+                     for key in data.files if key.startswith(name + "/")}
+
+
+def test_rms_norm_against_reference(oracle):
+    """Golden: rms_norm_reference on the model-dtype residual sum
+    (custom_kernels/fused_rms.py:137-140; the sum is exact, the norm within one unit in
+    the last place of the 16-bit output -- the reference's own bounds are 0 and 2e-3,
+    experiments/decode/benchmark_fa3_fusion_kernels.py:77-78) and nn.RMSNorm, the model's
+    path without custom kernels (baseline/naive_forward.py:59-64)."""
+    seen = 0
+    for name, case in _norm_cases():
+        epsilon = float(case["epsilon"])
+        summed, normalized = oracle.residual_add_rms_norm(case["residual"], case["branch"], case["weight"], epsilon)
+        assert torch.equal(summed, case["summed"]), name
+        for actual, key in ((normalized, "normalized"), (oracle.rms_norm(case["residual"], case["weight"], epsilon), "plain")):
+            distance = oracle.ulp_distance(actual, case[key])
+            assert distance.max().item() <= 1.0, (name, key)
+            assert (distance > 0).float().mean().item() < 1e-3, (name, key)  # rounding ties only
+        torch.testing.assert_close(normalized.float(), case["torch_rmsnorm"].float(), atol=2e-3, rtol=1e-2)
+        seen += 1
+    assert seen == 5
+    zero_row = oracle.rms_norm(torch.zeros(1, 8, dtype=torch.float16), torch.ones(8, dtype=torch.float16))
+    assert torch.equal(zero_row, torch.zeros(1, 8, dtype=torch.float16))
+
+
 # ---------------------------------------------------------------------- fp8
 
 def test_e4m3_decode_table_matches_reference_and_torch(oracle):
