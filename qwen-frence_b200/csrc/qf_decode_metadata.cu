@@ -25,6 +25,9 @@ struct AdvanceParams {
 constexpr int kAdvanceThreads = 128;
 
 __global__ void __launch_bounds__(kAdvanceThreads) advance_metadata_kernel(AdvanceParams p) {
+  // Chained onto the previous kernel of the stream: resident early, but every kernel that
+  // read the old metadata has completed once this wait returns.
+  dependency_wait();
   const int b = blockIdx.x * kAdvanceThreads + threadIdx.x;
   if (b >= p.batch) return;
   const int64_t position = load_index(p.positions, p.pos_dtype, b) + 1;
@@ -78,11 +81,11 @@ extern "C" int qf_advance_decode_metadata(void* positions, int32_t positions_dty
   p.table_dtype = table_dtype;
   p.batch = batch, p.page_size = page_size;
   const unsigned blocks = static_cast<unsigned>((batch + kAdvanceThreads - 1) / kAdvanceThreads);
-  // An ordinary launch: it starts after every earlier kernel of the stream (which read
-  // the old metadata) has completed.  The kernel that follows must not start early
-  // either, because the partial pass reads lengths and table before its dependency wait.
-  advance_metadata_kernel<<<blocks, kAdvanceThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  QF_CUDA(cudaGetLastError());
+  QF_CUDA(launch_chained(advance_metadata_kernel, dim3(blocks), dim3(kAdvanceThreads), 0,
+                         static_cast<cudaStream_t>(stream), p));
+  // The kernel that follows must not start early: the partial pass reads lengths and
+  // table before its own dependency wait, and may become resident as soon as the kernel
+  // before it has started.
   request_ordered_launch();
   return QF_OK;
 }

@@ -108,7 +108,7 @@ struct Chunk<T, 1> {
 };
 
 template <typename T, int VEC, bool RESIDUAL>
-__global__ void __launch_bounds__(kMaxNormThreads) rms_norm_kernel(NormParams p) {
+__global__ void __launch_bounds__(kMaxNormThreads, 5) rms_norm_kernel(NormParams p) {
   release_dependents();
   using Piece = Chunk<T, VEC>;
   __shared__ float warp_sums[kMaxNormThreads / 32];
@@ -119,24 +119,27 @@ __global__ void __launch_bounds__(kMaxNormThreads) rms_norm_kernel(NormParams p)
 
   // Weights belong to the model: no kernel of the step writes them, so they may be
   // fetched while the previous kernel is still running.
-  Piece weight[kHeld];
-#pragma unroll
-  for (int i = 0; i < kHeld; ++i) {
-    const int c = threadIdx.x + i * threads;
-    if (c < chunks) weight[i].load(p.weight, static_cast<int64_t>(c) * VEC);
-  }
+  // (Only the thread's first chunk: at decode widths that is all it has, and for wide
+  // rows the registers are better spent on residency; the rest comes from L2 later.)
+  Piece first_weight;
+  if (threadIdx.x < chunks) first_weight.load(p.weight, static_cast<int64_t>(threadIdx.x) * VEC);
   dependency_wait();
+
+  const T* x_row = static_cast<const T*>(p.x) + row * p.x_stride;
+  const T* branch_row = RESIDUAL ? static_cast<const T*>(p.branch) + row * p.branch_stride : nullptr;
+  T* summed_row = RESIDUAL ? static_cast<T*>(p.summed) + row * p.summed_stride : nullptr;
+  T* norm_row = static_cast<T*>(p.normalized) + row * p.norm_stride;
 
   Piece held[kHeld];
   float squares = 0.f;
   auto fetch = [&](int c) {
     Piece value;
-    value.load(p.x, row * p.x_stride + static_cast<int64_t>(c) * VEC);
+    value.load(x_row, c * VEC);
     if (RESIDUAL) {
       Piece other;
-      other.load(p.branch, row * p.branch_stride + static_cast<int64_t>(c) * VEC);
+      other.load(branch_row, c * VEC);
       value.add(other);
-      value.store(p.summed, row * p.summed_stride + static_cast<int64_t>(c) * VEC);
+      value.store(summed_row, c * VEC);
     }
     return value;
   };
@@ -162,15 +165,18 @@ __global__ void __launch_bounds__(kMaxNormThreads) rms_norm_kernel(NormParams p)
 #pragma unroll
   for (int i = 0; i < kHeld; ++i) {
     const int c = threadIdx.x + i * threads;
-    if (c < chunks) held[i].scaled(weight[i], rms).store(p.normalized, row * p.norm_stride + static_cast<int64_t>(c) * VEC);
+    if (c < chunks) {
+      Piece w = first_weight;
+      if (i > 0) w.load(p.weight, c * VEC);
+      held[i].scaled(w, rms).store(norm_row, c * VEC);
+    }
   }
   for (int c = threadIdx.x + kHeld * threads; c < chunks; c += threads) {
     // the rounded sum this same thread stored above (or the input itself)
     Piece value, w;
-    value.load(RESIDUAL ? p.summed : p.x,
-               row * (RESIDUAL ? p.summed_stride : p.x_stride) + static_cast<int64_t>(c) * VEC);
-    w.load(p.weight, static_cast<int64_t>(c) * VEC);
-    value.scaled(w, rms).store(p.normalized, row * p.norm_stride + static_cast<int64_t>(c) * VEC);
+    value.load(RESIDUAL ? summed_row : x_row, c * VEC);
+    w.load(p.weight, c * VEC);
+    value.scaled(w, rms).store(norm_row, c * VEC);
   }
 }
 
