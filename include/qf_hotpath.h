@@ -344,6 +344,7 @@ int qf_order_next_launch(void);
 #define QF_STATUS_BAD_PAGE_ID 2
 #define QF_STATUS_MERGE_TIMEOUT 3
 #define QF_STATUS_POSITION_PAST_TABLE 4
+#define QF_STATUS_PIPELINE_TIMEOUT 5
 int qf_advance_decode_metadata(void* positions, int32_t positions_dtype,
                                void* seq_lens, int32_t lens_dtype,
                                void* slot_mapping, int32_t slot_dtype,
@@ -372,6 +373,46 @@ int qf_residual_add_rms_norm(const void* residual, int64_t residual_row_stride,
                              const void* weight, void* summed, int64_t summed_row_stride,
                              void* normalized, int64_t normalized_row_stride, int64_t rows,
                              int32_t hidden, int32_t dtype, float epsilon, void* stream);
+
+/* ------------------------------------------------------------------------
+ * QKV projection with RoPE + paged KV-cache write as its epilogue (decode).
+ * Replaces qkv_rope_cache of the reference's CUTLASS extension
+ * (custom_kernels/fused_gemm.py:271-278, custom_kernels/gemm_epilogue/
+ * fused_gemm.cu:223-310; caller engine/graph/paged_graph_decoder.py:218-224),
+ * without its norm-folding row scale:
+ *   packed[r, n] = T(sum_k hidden[r, k] * weight[n, k] + bias[n])   n < 2048, fp32 sum
+ *   then exactly qf_rope_kv_write on the packed row: Q heads 0-11 rotated into
+ *   q_out [rows, 12 * 128]; K heads rotated, V heads as they are, into row
+ *   slot_mapping[r] of the flat [slots, 2, 128] view of the pools.
+ * Rows >= *valid_tokens (device int32 scalar, may be NULL) get zero queries and no
+ * cache write.  A slot outside [0, num_slots) is skipped and recorded (status 2).
+ * hidden [rows, in_features] and weight [2048, in_features] (nn.Linear layout):
+ * unit stride inside a row, 16-byte aligned, row strides multiples of 8 elements;
+ * in_features a multiple of 64; pools contiguous.  An sm_100a tensor-core kernel
+ * (TMA operand loads, tcgen05.mma into TMEM); if one of its bounded barrier waits
+ * ever ran out the device status word would read 5 and the outputs be unreliable. */
+typedef struct qf_qkv_rope_cache_args {
+  const void* hidden;        /* device */
+  int64_t hidden_stride_row; /* elements */
+  const void* weight;        /* device */
+  int64_t weight_stride_row;
+  const void* bias;          /* device [2048], may be NULL */
+  void* q_out;               /* device [rows, >= 1536] */
+  int64_t q_stride_row;
+  const void* positions;     /* device [rows] */
+  int32_t positions_dtype;   /* QF_INDEX_* */
+  const void* slot_mapping;  /* device [rows] */
+  int32_t slot_dtype;
+  void* k_pool;              /* device, flat [num_slots, 2, 128] */
+  void* v_pool;
+  int64_t num_slots;
+  const void* valid_tokens;  /* device int32 scalar or NULL */
+  int32_t rows;
+  int32_t in_features;
+  int32_t dtype;             /* QF_DTYPE_* of hidden, weight, bias, q_out, pools */
+  double base;               /* RoPE theta */
+} qf_qkv_rope_cache_args;
+int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* args, void* stream);
 
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the

@@ -279,6 +279,27 @@ def advance_decode_state(positions, seq_lens, block_table, page_size=16):
     return positions, seq_lens, pages * page_size + positions % page_size
 
 
+# ---- QKV projection with the RoPE / cache epilogue ---------------------------------
+
+def qkv_projection(x, weight, bias=None):
+    """x @ weight.T + bias with a float64 sum, rounded once to x's dtype: the model-dtype
+    output of nn.Linear that the reference's epilogue rotates
+    (custom_kernels/gemm_epilogue/fused_gemm.cu:262-267: accumulator + bias, then
+    __float2half_rn)."""
+    packed = x.detach().cpu().double() @ weight.detach().cpu().double().T
+    if bias is not None:
+        packed = packed + bias.detach().cpu().double()
+    return packed.float().to(x.dtype)
+
+
+def qkv_rope_cache(x, weight, bias, positions, slot_mapping, k_pool, v_pool, *, base=1_000_000.0,
+                   valid_tokens=None):
+    """The fused projection restated as its two steps: qkv_projection, then the packed
+    epilogue (custom_kernels/fused_gemm.py:271-278).  Mutates the CPU pools, returns q."""
+    return packed_qkv_rope_cache(qkv_projection(x, weight, bias), positions, slot_mapping, k_pool, v_pool,
+                                 base=base, valid_tokens=valid_tokens)
+
+
 # ---- RMSNorm -------------------------------------------------------------------
 
 def rms_norm(x, weight, epsilon=1e-6):

@@ -22,6 +22,7 @@ current torch stream; none has a CPU fallback):
     grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
     advance_decode_state                                   custom_kernels/decode_state.py
     rms_norm, residual_add_rms_norm                        custom_kernels/fused_rms.py
+    qkv_rope_cache                                         custom_kernels/fused_gemm.py
 """
 
 from __future__ import annotations
@@ -54,6 +55,7 @@ _EXPORTS = {
     "advance_decode_state": "decode_state",
     "rms_norm": "fused_rms",
     "residual_add_rms_norm": "fused_rms",
+    "qkv_rope_cache": "fused_gemm",
 }
 _LOCAL = {"cabi": "_cabi", "build": "build", "kv_layout": "kv_layout", "workloads": "workloads",
           "decode_step": "decode_step", "sharding": "sharding"}

@@ -34,7 +34,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_splitk_decode_attention_static", "qf_grouped_splitk_decode_attention_stages",
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
     "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
-    "qf_rms_norm", "qf_residual_add_rms_norm",
+    "qf_rms_norm", "qf_residual_add_rms_norm", "qf_qkv_rope_cache",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -85,6 +85,24 @@ class DecodeAttentionArgs(Structure):
         ("batch", c_int32), ("q_heads", c_int32), ("kv_heads", c_int32), ("head_dim", c_int32),
         ("page_size", c_int32), ("split_k", c_int32), ("dtype", c_int32), ("kv_fp8", c_int32),
         ("scale", c_float),
+    ]
+
+
+class QkvRopeCacheArgs(Structure):
+    """Mirror of qf_qkv_rope_cache_args."""
+
+    _fields_ = [
+        ("hidden", c_void_p), ("hidden_stride_row", c_int64),
+        ("weight", c_void_p), ("weight_stride_row", c_int64),
+        ("bias", c_void_p),
+        ("q_out", c_void_p), ("q_stride_row", c_int64),
+        ("positions", c_void_p), ("positions_dtype", c_int32),
+        ("slot_mapping", c_void_p), ("slot_dtype", c_int32),
+        ("k_pool", c_void_p), ("v_pool", c_void_p),
+        ("num_slots", c_int64),
+        ("valid_tokens", c_void_p),
+        ("rows", c_int32), ("in_features", c_int32), ("dtype", c_int32),
+        ("base", c_double),
     ]
 
 
@@ -141,6 +159,7 @@ def library():
     lib.qf_residual_add_rms_norm.argtypes = [
         c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
         c_int64, c_int32, c_int32, c_float, c_void_p]
+    lib.qf_qkv_rope_cache.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32

@@ -25,7 +25,7 @@ INCLUDE = PACKAGE_DIR.parent / "include"
 BUILD_DIR = PACKAGE_DIR / "build"
 LIBRARY = PACKAGE_DIR / "libqf_hotpath.so"
 
-SOURCES = ("qf_api.cu", "qf_rope_kv_write.cu", "qf_decode_attention.cu", "qf_decode_metadata.cu", "qf_rms_norm.cu")
+SOURCES = ("qf_api.cu", "qf_rope_kv_write.cu", "qf_decode_attention.cu", "qf_decode_metadata.cu", "qf_rms_norm.cu", "qf_qkv_gemm_rope.cu")
 
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2")

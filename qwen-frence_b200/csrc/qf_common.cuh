@@ -42,6 +42,7 @@ int take_ordered_launch();  // 1 once after a request, else 0
 constexpr int kStatusBadPageId = QF_STATUS_BAD_PAGE_ID;
 constexpr int kStatusMergeTimeout = QF_STATUS_MERGE_TIMEOUT;  // a warp gave up waiting for an earlier piece's merge
 constexpr int kStatusPositionPastTable = QF_STATUS_POSITION_PAST_TABLE;
+constexpr int kStatusPipelineTimeout = QF_STATUS_PIPELINE_TIMEOUT;  // a bounded barrier wait of the GEMM ran out
 
 // ---- device side ---------------------------------------------------------
 #ifdef __CUDACC__

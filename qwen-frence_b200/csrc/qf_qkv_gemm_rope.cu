@@ -1,0 +1,406 @@
+// QKV projection with the RoPE + paged KV-cache write as its epilogue, for decode batches:
+//   packed = T(hidden @ weight^T + bias)            [rows, 2048], fp32 accumulate, one rounding
+//   q, k   = rope(packed)  (fp32, one rounding);  v = packed;  k, v -> cache slot of the row
+// i.e. exactly packed_qkv_rope_cache applied to the model-dtype output of the projection, as
+// the reference's CUTLASS epilogue does (custom_kernels/gemm_epilogue/fused_gemm.cu:223-310),
+// without the packed tensor ever reaching memory.
+//
+// Shape of the work: rows <= a few hundred, N = 2048, K = 1536 -- the 6.3 MB weight matrix is
+// streamed once; tensor-core time is negligible, so the kernel is built to keep many TMA
+// loads in flight per SM and to finish in about one weight-read time.
+//   * CTA tile: 128 rows x 64 columns = columns [32j, 32j+32) of one head and their rotation
+//     partners [64+32j, 64+32j+32), j = 0/1 -> 32 column tiles, so RoPE needs no exchange.
+//   * Operands travel by tiled TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast)
+//     into a 6-stage ring: A = 128 x 64 of hidden (rows beyond the batch are zero-filled or
+//     ignored), B = 2 x (32 x 64) of weight.  One thread issues the copies, one thread issues
+//     tcgen05.mma (M 128, N 64, K 16, fp32 accumulator in 64 TMEM columns); a stage is
+//     released by tcgen05.commit on its "empty" barrier.
+//   * Four epilogue warps compute their row's sin / cos while the ring runs, then read the
+//     accumulator with tcgen05.ld (32 lanes x 32 columns per warp and half), add the bias,
+//     round, rotate and store 64-byte runs to q / the cache.
+// Every barrier wait is bounded: when one runs out, the CTA records status 5, stops issuing,
+// waits (bounded) for copies and MMAs in flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <cmath>
+#include <type_traits>
+
+#include "qf_common.cuh"
+#include "qf_rope_math.cuh"
+
+namespace qf {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 64;   // 32 columns + their 32 rotation partners
+constexpr int kTileK = 64;   // 128 bytes per row: one swizzle atom wide
+constexpr int kStages = 6;
+constexpr int kBytesA = kTileM * kTileK * 2;  // 16 KB
+constexpr int kBytesB = kTileN * kTileK * 2;  // 8 KB
+constexpr int kStageBytes = kBytesA + kBytesB;
+constexpr int kGemmThreads = 192;             // warps 0-3 epilogue, 4 copies, 5 MMA + TMEM
+constexpr int kTmemColumns = 64;
+constexpr int kQkvWidth = 2048;
+constexpr int kSpinLimit = 1 << 21;
+constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 1024;  // + room to align to 1 KB
+
+struct GemmParams {
+  const void* bias;  // [2048] or null
+  void* q_out;
+  int64_t q_stride_row;
+  const void* positions;
+  const void* slots;
+  void* k_cache;     // flat [slots, 2, 128]
+  void* v_cache;
+  int64_t num_slots;
+  const int* valid_tokens;
+  int* status;
+  int rows, k_blocks, a_box_rows;
+  int pos_dtype, slot_dtype;
+};
+
+__device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait; gives up for the whole CTA (abort flag in shared memory) when it runs out.
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (int spin = 0; spin < kSpinLimit; ++spin) {
+    if (try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (spin > 128) __nanosleep(64);
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// K-major operand tile in 128-byte-swizzled shared memory: rows of 128 bytes, groups of
+// eight rows 1024 bytes apart (descriptor version 1, layout type 2 = SWIZZLE_128B).
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
+  uint64_t desc = (smem_address >> 4) & 0x3fffu;
+  desc |= uint64_t(1) << 16;            // leading byte offset (unused for swizzled K-major)
+  desc |= uint64_t(1024 >> 4) << 32;    // stride between 8-row groups
+  desc |= uint64_t(1) << 46;            // descriptor version
+  desc |= uint64_t(2) << 61;            // SWIZZLE_128B
+  return desc;
+}
+
+template <typename T>
+__device__ __forceinline__ float round_to_storage(float x) {
+  return to_float(from_float<T>(x));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    qkv_gemm_rope_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p, const __grid_constant__ InvFreqTable freq) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ float s_bias[kTileN];
+
+  release_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int head = n_tile >> 1, j = n_tile & 1;  // 16 heads: 12 Q, 2 K, 2 V
+  const int column0 = head * 128 + j * 32;       // partners at column0 + 64
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* aborted = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[s])));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&acc_bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    abort_flag = 0;
+  }
+  if (threadIdx.x < kTileN) {  // the model's bias: no kernel writes it
+    const int column = column0 + (threadIdx.x & 31) + (threadIdx.x >> 5) * 64;
+    s_bias[threadIdx.x] = p.bias ? to_float(static_cast<const T*>(p.bias)[column]) : 0.f;
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(kTmemColumns));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  // hidden comes from the kernel before this one
+  dependency_wait();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++issued) {
+        const int s = kb % kStages;
+        if (!wait_barrier(smem_u32(&empty_bar[s]), ((kb / kStages) & 1) ^ 1, aborted)) break;
+        const uint32_t full = smem_u32(&full_bar[s]);
+        const uint32_t bytes = static_cast<uint32_t>(p.a_box_rows) * kTileK * 2 + kBytesB;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(bytes) : "memory");
+        const uint32_t a = ring + s * kStageBytes, b = a + kBytesA;
+        tma_load_2d(a, &map_a, kb * kTileK, m_tile * kTileM, full);
+        tma_load_2d(b, &map_b, kb * kTileK, column0, full);
+        tma_load_2d(b + kBytesB / 2, &map_b, kb * kTileK, column0 + 64, full);
+      }
+      if (*aborted) {
+        // copies already issued still land in this CTA's shared memory: wait for them
+        for (int kb = issued > kStages ? issued - kStages : 0; kb < issued; ++kb) {
+          for (int spin = 0; spin < kSpinLimit; ++spin) {
+            if (try_wait(smem_u32(&full_bar[kb % kStages]), (kb / kStages) & 1)) break;
+            __nanosleep(64);
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A and B K-major, N = 64, M = 128
+      const uint32_t format = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;  // operand type code
+      const uint32_t idesc = (1u << 4) | (format << 7) | (format << 10) | (uint32_t(kTileN >> 3) << 17) |
+                             (uint32_t(kTileM >> 4) << 24);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int s = kb % kStages;
+        if (!wait_barrier(smem_u32(&full_bar[s]), (kb / kStages) & 1, aborted)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = ring + s * kStageBytes, b = a + kBytesA;
+        const uint64_t desc_a = operand_descriptor(a), desc_b = operand_descriptor(b);
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k) {
+          const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+          // 16 elements of K = 32 bytes further along the swizzled row
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+              :
+              : "r"(tmem_base), "l"(desc_a + uint64_t(k * 2)), "l"(desc_b + uint64_t(k * 2)), "r"(idesc),
+                "r"(accumulate)
+              : "memory");
+        }
+        // frees the stage once the MMAs that read it have completed
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_u32(&empty_bar[s]))
+                     : "memory");
+      }
+      // always: the epilogue and the TMEM release wait on this
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                       smem_u32(&acc_bar))
+                   : "memory");
+    }
+  } else {
+    // ---- epilogue warps: row m of the batch <-> TMEM lane 32 * warp + lane ----
+    const int m = m_tile * kTileM + warp * 32 + lane;
+    const int live_rows = p.valid_tokens ? min(*p.valid_tokens, p.rows) : p.rows;
+    const bool in_batch = m < p.rows, live = m < live_rows;
+    const bool is_q = head < 12, is_v = head >= 14;
+    int64_t slot = -1;
+    float cosine[32], sine[32];
+    if (live) {
+      if (!is_q) {
+        slot = load_index(p.slots, p.slot_dtype, m);
+        if (slot < 0 || slot >= p.num_slots) {
+          atomicExch(p.status, kStatusBadPageId);
+          slot = -1;
+        }
+      }
+      if (!is_v) {
+        const float position = load_position(p.positions, p.pos_dtype, m);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float angle = __fmul_rn(position, freq.v[j * 32 + c]);
+          cosine[c] = cosf(angle);
+          sine[c] = sinf(angle);
+        }
+      }
+    }
+    // warp-uniform: tcgen05.ld is a warp-wide instruction
+    const bool ready = __all_sync(0xffffffffu, wait_barrier(smem_u32(&acc_bar), 0, aborted) && !*aborted);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ready) {
+      uint32_t lo[32], hi[32];
+      const uint32_t address = tmem_base + (uint32_t(warp * 32) << 16);
+#define QF_TMEM_LOAD_32(dst, addr)                                                                        \
+  asm volatile(                                                                                           \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                            \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                            \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"            \
+      : "=r"(dst[0]), "=r"(dst[1]), "=r"(dst[2]), "=r"(dst[3]), "=r"(dst[4]), "=r"(dst[5]), "=r"(dst[6]),  \
+        "=r"(dst[7]), "=r"(dst[8]), "=r"(dst[9]), "=r"(dst[10]), "=r"(dst[11]), "=r"(dst[12]),             \
+        "=r"(dst[13]), "=r"(dst[14]), "=r"(dst[15]), "=r"(dst[16]), "=r"(dst[17]), "=r"(dst[18]),          \
+        "=r"(dst[19]), "=r"(dst[20]), "=r"(dst[21]), "=r"(dst[22]), "=r"(dst[23]), "=r"(dst[24]),          \
+        "=r"(dst[25]), "=r"(dst[26]), "=r"(dst[27]), "=r"(dst[28]), "=r"(dst[29]), "=r"(dst[30]),          \
+        "=r"(dst[31])                                                                                      \
+      : "r"(addr))
+      QF_TMEM_LOAD_32(lo, address);
+      QF_TMEM_LOAD_32(hi, address + 32);
+#undef QF_TMEM_LOAD_32
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+
+      T* first = nullptr;  // 32 elements here, their partners 64 elements further
+      if (is_q) {
+        if (in_batch) first = static_cast<T*>(p.q_out) + m * p.q_stride_row + column0;
+      } else if (live && slot >= 0) {
+        const int kv_head = (head - 12) & 1;
+        first = static_cast<T*>(is_v ? p.v_cache : p.k_cache) + (slot * 2 + kv_head) * 128 + j * 32;
+      }
+      if (first != nullptr) {
+        uint32_t out_lo[16], out_hi[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float a[2], b[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            // the projection's output in the model dtype, then the rotation in fp32
+            a[e] = round_to_storage<T>(__fadd_rn(__uint_as_float(lo[c + e]), s_bias[c + e]));
+            b[e] = round_to_storage<T>(__fadd_rn(__uint_as_float(hi[c + e]), s_bias[32 + c + e]));
+            if (!is_v) {
+              const float x = a[e], y = b[e];
+              a[e] = __fsub_rn(__fmul_rn(x, cosine[c + e]), __fmul_rn(y, sine[c + e]));
+              b[e] = __fadd_rn(__fmul_rn(y, cosine[c + e]), __fmul_rn(x, sine[c + e]));
+            }
+            if (is_q && !live) a[e] = 0.f, b[e] = 0.f;  // padded rows of a token bucket
+          }
+          out_lo[c >> 1] = pack2<T>(a[0], a[1]);
+          out_hi[c >> 1] = pack2<T>(b[0], b[1]);
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          reinterpret_cast<uint4*>(first)[v] =
+              make_uint4(out_lo[4 * v], out_lo[4 * v + 1], out_lo[4 * v + 2], out_lo[4 * v + 3]);
+          reinterpret_cast<uint4*>(first + 64)[v] =
+              make_uint4(out_hi[4 * v], out_hi[4 * v + 1], out_hi[4 * v + 2], out_hi[4 * v + 3]);
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  // ---- teardown: nobody touches TMEM after this barrier; MMAs have completed (or the
+  // bounded wait on the accumulator barrier has run out) before it is freed ----
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    if (*aborted) {
+      for (int spin = 0; spin < kSpinLimit; ++spin) {
+        if (try_wait(smem_u32(&acc_bar), 0)) break;
+        __nanosleep(64);
+      }
+      if (lane == 0) atomicExch(p.status, kStatusPipelineTimeout);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      entry = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(entry);
+  }();
+  return fn;
+}
+
+// [rows, columns] 16-bit matrix, unit stride inside a row; box = box_rows x 64 columns, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t columns, int64_t row_stride, int box_rows,
+              bool bf16) {
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(columns), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
+  const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                const_cast<void*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+template <typename T>
+cudaError_t launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p,
+                        const InvFreqTable& freq, cudaStream_t stream) {
+  auto kernel = qkv_gemm_rope_kernel<T>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemmSmemBytes));
+  if (err != cudaSuccess) return err;
+  const dim3 grid(kQkvWidth / kTileN, static_cast<unsigned>((p.rows + kTileM - 1) / kTileM));
+  return launch_chained(kernel, grid, dim3(kGemmThreads), kGemmSmemBytes, stream, map_a, map_b, p, freq);
+}
+
+}  // namespace
+}  // namespace qf
+
+extern "C" int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* a, void* stream) {
+  using namespace qf;
+  QF_REQUIRE(a != nullptr, "args must not be null");
+  QF_REQUIRE(a->dtype == QF_DTYPE_F16 || a->dtype == QF_DTYPE_BF16, "dtype must be fp16 or bf16");
+  QF_REQUIRE(a->rows >= 0, "row count must not be negative");
+  QF_REQUIRE(a->in_features > 0 && a->in_features % kTileK == 0,
+             "the input width must be a positive multiple of 64");
+  QF_REQUIRE(a->positions_dtype == QF_INDEX_I32 || a->positions_dtype == QF_INDEX_I64 ||
+                 a->positions_dtype == QF_INDEX_F32,
+             "positions must be int32, int64 or float32");
+  QF_REQUIRE(a->slot_dtype == QF_INDEX_I32 || a->slot_dtype == QF_INDEX_I64,
+             "slot mapping must use an integer dtype");
+  if (a->rows == 0) return QF_OK;
+  QF_REQUIRE(a->hidden && a->weight && a->q_out && a->positions && a->slot_mapping && a->k_pool && a->v_pool,
+             "hidden, weight, q_out, positions, slot mapping and pools must not be null");
+  QF_REQUIRE(aligned16(a->hidden) && aligned16(a->weight) && aligned16(a->q_out) && aligned16(a->k_pool) &&
+                 aligned16(a->v_pool) && a->hidden_stride_row % 8 == 0 && a->weight_stride_row % 8 == 0 &&
+                 a->q_stride_row % 8 == 0,
+             "tensors must be 16-byte aligned with row strides that are multiples of 8 elements");
+  QF_REQUIRE(a->hidden_stride_row >= a->in_features && a->weight_stride_row >= a->in_features &&
+                 a->q_stride_row >= 12 * 128,
+             "row strides are shorter than the rows");
+  QF_REQUIRE(a->num_slots > 0, "the pools must hold at least one slot");
+
+  const bool bf16 = a->dtype == QF_DTYPE_BF16;
+  const int box_rows = a->rows < kTileM ? a->rows : kTileM;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, a->hidden, a->rows, a->in_features, a->hidden_stride_row, box_rows, bf16) ||
+      !make_map(&map_b, a->weight, kQkvWidth, a->in_features, a->weight_stride_row, kTileN / 2, bf16)) {
+    return fail(QF_ECUDA, "cuTensorMapEncodeTiled failed or is unavailable");
+  }
+  GemmParams p;
+  p.bias = a->bias, p.q_out = a->q_out, p.q_stride_row = a->q_stride_row;
+  p.positions = a->positions, p.slots = a->slot_mapping;
+  p.k_cache = a->k_pool, p.v_cache = a->v_pool, p.num_slots = a->num_slots;
+  p.valid_tokens = static_cast<const int*>(a->valid_tokens);
+  p.status = device_status_word();
+  QF_REQUIRE(p.status != nullptr, "device status word is unavailable");
+  p.rows = a->rows, p.k_blocks = a->in_features / kTileK, p.a_box_rows = box_rows;
+  p.pos_dtype = a->positions_dtype, p.slot_dtype = a->slot_dtype;
+  const InvFreqTable freq = make_inv_freq(a->base, 64);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  QF_CUDA(bf16 ? launch_gemm<__nv_bfloat16>(map_a, map_b, p, freq, s) : launch_gemm<__half>(map_a, map_b, p, freq, s));
+  return QF_OK;
+}

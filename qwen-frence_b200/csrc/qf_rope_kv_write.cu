@@ -19,15 +19,10 @@
 #include <cmath>
 
 #include "qf_common.cuh"
+#include "qf_rope_math.cuh"
 
 namespace qf {
 namespace {
-
-constexpr int kMaxHalf = 128;  // head_dim <= 256
-
-struct InvFreqTable {
-  float v[kMaxHalf];
-};
 
 struct RopeParams {
   const void* q;
@@ -360,11 +355,8 @@ int launch_rope(const qf_rope_kv_write_args* a, const float* k_scale, const floa
   // inv_freq[i] = expf(i * (-(float)log(base) / half)): the kernels' formula
   // (custom_kernels/rope_kv_write.py:190-191), evaluated once on the host in
   // fp32 and handed to the kernel by value.
-  InvFreqTable freq{};
   const int half = a->head_dim / 2;
-  const float log_theta = static_cast<float>(std::log(a->base));
-  const float step = -log_theta / static_cast<float>(half);
-  for (int i = 0; i < half; ++i) freq.v[i] = expf(static_cast<float>(i) * step);
+  const InvFreqTable freq = make_inv_freq(a->base, half);
 
   // 16-byte vectors need unit d-strides and 8-element-aligned bases/strides.
   auto mult8 = [](int64_t s) { return (s & 7) == 0; };

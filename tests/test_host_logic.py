@@ -33,7 +33,8 @@ def test_library_exports_every_declared_symbol(package):
 @pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
 def test_ctypes_structs_match_c_layout(package, tmp_path):
     fields = {"qf_rope_kv_write_args": package.cabi.RopeKvWriteArgs,
-              "qf_decode_attention_args": package.cabi.DecodeAttentionArgs}
+              "qf_decode_attention_args": package.cabi.DecodeAttentionArgs,
+              "qf_qkv_rope_cache_args": package.cabi.QkvRopeCacheArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "qf_hotpath.h"', "int main(void) {"]
     for struct, cls in fields.items():
         lines.append(f'printf("{struct} %zu\\n", sizeof({struct}));')
@@ -83,6 +84,13 @@ def test_c_side_validation_without_a_gpu(package):
     assert lib.qf_rms_norm(None, 8, None, None, 8, 4, 0, 0, 1e-6, None) == -1 and b"hidden" in lib.qf_last_error()
     assert lib.qf_residual_add_rms_norm(None, 8, None, 8, None, None, 8, None, 8, 4, 8, 1, 1e-6, None) == -1
     assert b"must not be null" in lib.qf_last_error()
+    gemm = cabi.QkvRopeCacheArgs()
+    gemm.rows, gemm.in_features, gemm.dtype = 4, 1500, 0
+    assert lib.qf_qkv_rope_cache(ctypes.byref(gemm), None) == -1 and b"multiple of 64" in lib.qf_last_error()
+    gemm.in_features, gemm.rows = 1536, 0
+    assert lib.qf_qkv_rope_cache(ctypes.byref(gemm), None) == 0   # no rows: nothing launched
+    gemm.rows = 4
+    assert lib.qf_qkv_rope_cache(ctypes.byref(gemm), None) == -1 and b"must not be null" in lib.qf_last_error()
 
 
 def test_missing_library_fails_loudly_with_one_build_command(package):
@@ -156,6 +164,12 @@ def test_cpu_tensors_are_rejected_not_computed(package):
         package.rms_norm(hidden, hidden[0])
     with pytest.raises(ValueError, match="CUDA"):
         package.residual_add_rms_norm(hidden, hidden, hidden[0])
+    with pytest.raises(ValueError, match="CUDA"):
+        package.qkv_rope_cache(torch.zeros(2, 1536, dtype=torch.float16), torch.zeros(2048, 1536, dtype=torch.float16),
+                               None, None, positions=lens.long(), slots=lens.long(), k_pool=pool, v_pool=pool)
+    with pytest.raises(ValueError, match="norm folding"):
+        package.qkv_rope_cache(torch.zeros(2, 1536, dtype=torch.float16), torch.zeros(2048, 1536, dtype=torch.float16),
+                               None, torch.zeros(2), positions=lens.long(), slots=lens.long(), k_pool=pool, v_pool=pool)
     with pytest.raises(ValueError, match="one entry per sequence"):
         package.advance_decode_state(lens.long(), lens[:1], lens.long(), table)
     with pytest.raises(ValueError, match="CUDA"):
