@@ -266,6 +266,9 @@ def run_reference(args, rank, world):
 def run_layer_glue(args):
     """--op layer_glue: the kernels that sit either side of the hot path in a decode layer.
 
+    qkv_rope_cache: the QKV projection with the RoPE / cache epilogue (TMA + tcgen05), one
+    call per layer with that layer's own weights (176 MB in all: beyond L2), against the
+    library GEMM followed by the packed epilogue kernel.
     residual_add_rms_norm: (a) at decode sizes, 56 calls (two per layer) chained in one
     graph -- launch latency, reported as microseconds per call; (b) 4096 x 8192 rows
     (268 MB moved, larger than L2) -- HBM bound, reported against the measured copy peak.
@@ -324,10 +327,38 @@ def run_layer_glue(args):
     oracle.residual_add_rms_norm(*cpu_inputs)
     cpu_seconds = time.perf_counter() - cpu_start
 
+    # ---- QKV projection with the RoPE / cache epilogue: 28 layers' weights in turn ----
+    # (28 x 6.3 MB of weights: beyond L2, so every launch streams its matrix from HBM)
+    projection = {}
+    weights = [torch.randn((2048, 1536), device=device, dtype=torch.float16, generator=generator) * 0.05
+               for _ in range(LAYERS)]
+    bias = torch.randn((2048,), device=device, dtype=torch.float16, generator=generator) * 0.1
+    pool_k = torch.zeros((1024, 16, 2, 128), device=device, dtype=torch.float16)
+    pool_v = torch.zeros_like(pool_k)
+    for rows in (64, 256):
+        x = torch.randn((rows, 1536), device=device, dtype=torch.float16, generator=generator) * 0.5
+        positions = torch.randint(0, 4096, (rows,), device=device, generator=generator)
+        slots = torch.randperm(1024 * 16, device=device, generator=generator)[:rows]
+        fused_ms = time_graph(lambda: [package.qkv_rope_cache(x, w, bias, None, positions=positions, slots=slots,
+                                                              k_pool=pool_k, v_pool=pool_v) for w in weights],
+                              args.steps) / LAYERS
+        unfused_ms = time_graph(lambda: [package.packed_qkv_rope_cache(torch.nn.functional.linear(x, w, bias),
+                                                                        positions, slots, pool_k, pool_v)
+                                         for w in weights], args.steps) / LAYERS
+        moved_gemm = 2048 * 1536 * 2 + rows * 1536 * 2 + rows * 2048 * 2 + 2048 * 2 + rows * 16
+        projection[f"{rows}x1536"] = {
+            "us_per_call": fused_ms * 1e3, "us_per_call_cublas_plus_epilogue": unfused_ms * 1e3,
+            "algorithmic_bytes": moved_gemm,
+            "roofline": {"bound": "hbm", "achieved": moved_gemm / (fused_ms * 1e-3) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": moved_gemm / (fused_ms * 1e-3) / 1e9 / peak,
+                         "peak_kind": f"of {peak_kind}"}}
+    del weights
+
     # ---- consecutive decode steps without the host ---------------------------------
     steps = max(2, min(args.steps, 16))
+    chained_replays = 3
     workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=args.layers or None,
-                                                reserve_tokens=steps)
+                                                reserve_tokens=steps * (chained_replays + 1))
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
     step.load_packed_rows()
     step.capture(warmup=2)
@@ -349,7 +380,18 @@ def run_layer_glue(args):
         return start.elapsed_time(end) / count
 
     single_ms = replay_ms(step.replay, steps)
-    unrolled_ms = replay_ms(step.steps_graph.replay, 1) / steps
+    # the reserved pages cover one warm-up replay and the timed ones back to back
+    step.steps_graph.replay()
+    step.reset_metadata()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(chained_replays):
+        step.steps_graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    step.reset_metadata()
+    unrolled_ms = start.elapsed_time(end) / (chained_replays * steps)
     status = package.cabi.device_status()
     print(json.dumps({
         "op": "layer_glue", "n_gpus": 1, "data": "synthetic", "dtype": "f16 storage, f32 accumulate",
@@ -361,6 +403,7 @@ def run_layer_glue(args):
                       "cpu_baseline": {"value": moved / cpu_seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
                                        "kind": "port", "sample": "numpy oracle, one call on the same rows"}},
         },
+        "qkv_rope_cache": projection,
         "unrolled_decode_steps": {
             "workload": args.workload, "steps_per_graph": steps, "batch": workload.batch,
             "ms_per_step_single_step_graph": single_ms, "ms_per_step_unrolled_graph": unrolled_ms,

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&acc_bar)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions use the async proxy
     abort_flag = 0;
   }
   if (threadIdx.x < kTileN) {  // the model's bias: no kernel writes it
