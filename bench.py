@@ -335,19 +335,29 @@ def run_layer_glue(args):
     bias = torch.randn((2048,), device=device, dtype=torch.float16, generator=generator) * 0.1
     pool_k = torch.zeros((1024, 16, 2, 128), device=device, dtype=torch.float16)
     pool_v = torch.zeros_like(pool_k)
+    gamma = torch.randn((1536,), device=device, dtype=torch.float16, generator=generator)
     for rows in (64, 256):
         x = torch.randn((rows, 1536), device=device, dtype=torch.float16, generator=generator) * 0.5
+        branch = torch.randn((rows, 1536), device=device, dtype=torch.float16, generator=generator) * 0.5
         positions = torch.randint(0, 4096, (rows,), device=device, generator=generator)
         slots = torch.randperm(1024 * 16, device=device, generator=generator)[:rows]
-        fused_ms = time_graph(lambda: [package.qkv_rope_cache(x, w, bias, None, positions=positions, slots=slots,
-                                                              k_pool=pool_k, v_pool=pool_v) for w in weights],
-                              args.steps) / LAYERS
-        unfused_ms = time_graph(lambda: [package.packed_qkv_rope_cache(torch.nn.functional.linear(x, w, bias),
-                                                                        positions, slots, pool_k, pool_v)
-                                         for w in weights], args.steps) / LAYERS
+        fused = lambda h, w: package.qkv_rope_cache(h, w, bias, None, positions=positions, slots=slots,
+                                                    k_pool=pool_k, v_pool=pool_v)
+        unfused = lambda h, w: package.packed_qkv_rope_cache(torch.nn.functional.linear(h, w, bias),
+                                                             positions, slots, pool_k, pool_v)
+        norm = lambda: package.residual_add_rms_norm(x, branch, gamma)[1]
+        fused_ms = time_graph(lambda: [fused(x, w) for w in weights], args.steps) / LAYERS
+        unfused_ms = time_graph(lambda: [unfused(x, w) for w in weights], args.steps) / LAYERS
+        # as a layer runs it: the norm before the projection, whose tail the projection's
+        # set-up and first weight tiles overlap
+        norm_ms = time_graph(lambda: [norm() for _ in weights], args.steps) / LAYERS
+        fused_pair_ms = time_graph(lambda: [fused(norm(), w) for w in weights], args.steps) / LAYERS
+        unfused_pair_ms = time_graph(lambda: [unfused(norm(), w) for w in weights], args.steps) / LAYERS
         moved_gemm = 2048 * 1536 * 2 + rows * 1536 * 2 + rows * 2048 * 2 + 2048 * 2 + rows * 16
         projection[f"{rows}x1536"] = {
             "us_per_call": fused_ms * 1e3, "us_per_call_cublas_plus_epilogue": unfused_ms * 1e3,
+            "us_after_norm": (fused_pair_ms - norm_ms) * 1e3,
+            "us_after_norm_cublas_plus_epilogue": (unfused_pair_ms - norm_ms) * 1e3,
             "algorithmic_bytes": moved_gemm,
             "roofline": {"bound": "hbm", "achieved": moved_gemm / (fused_ms * 1e-3) / 1e9, "peak": peak,
                          "unit": "GB/s", "frac": moved_gemm / (fused_ms * 1e-3) / 1e9 / peak,
@@ -397,7 +407,7 @@ def run_layer_glue(args):
         "op": "layer_glue", "n_gpus": 1, "data": "synthetic", "dtype": "f16 storage, f32 accumulate",
         "residual_add_rms_norm": {
             "decode": decode_sizes,
-            "large": {"rows": rows, "hidden": hidden, "ms_per_call": ms, "algorithmic_bytes": moved,
+            "large": {"rows": 4096, "hidden": 8192, "ms_per_call": ms, "algorithmic_bytes": moved,
                       "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}"},
                       "cpu_baseline": {"value": moved / cpu_seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(),

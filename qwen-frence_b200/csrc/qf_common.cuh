@@ -137,27 +137,55 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Launch `kernel` so that it may overlap the tail of the previous kernel of `stream`
 // (the kernel itself orders its memory accesses with dependency_wait()).  Falls back
-// to an ordinary launch, for good, if the driver refuses the attribute.
+// to an ordinary launch, for good, if the driver refuses the attribute.  With a
+// ClusterShape as the first kernel argument slot the grid is launched as thread-block
+// clusters of that shape.
+struct ClusterShape {
+  unsigned x, y, z;
+};
+
 template <typename... Params, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
-                                  cudaStream_t stream, Args... args) {
+inline cudaError_t launch_chained_impl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, const ClusterShape* cluster, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid, config.blockDim = block;
   config.dynamicSmemBytes = smem, config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = attribute;
+  cudaLaunchAttribute attribute[2];
+  unsigned count = 0;
+  if (cluster != nullptr) {
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = cluster->x;
+    attribute[count].val.clusterDim.y = cluster->y;
+    attribute[count].val.clusterDim.z = cluster->z;
+    ++count;
+  }
   const bool ordered = take_ordered_launch() != 0;
-  config.numAttrs = (dependent_launch_enabled() && !ordered) ? 1 : 0;
+  const bool chained = dependent_launch_enabled() && !ordered;
+  attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[count].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = count + (chained ? 1 : 0);
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
-  if (err == cudaErrorNotSupported && config.numAttrs != 0) {
+  if (err == cudaErrorNotSupported && chained) {
     (void)cudaGetLastError();
     disable_dependent_launch();
-    config.numAttrs = 0;
+    config.numAttrs = count;
     err = cudaLaunchKernelEx(&config, kernel, args...);
   }
   return err;
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, ClusterShape cluster, Args... args) {
+  return launch_chained_impl(kernel, grid, block, smem, stream, &cluster, args...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+  return launch_chained_impl(kernel, grid, block, smem, stream, static_cast<const ClusterShape*>(nullptr),
+                             args...);
 }
 
 #endif  // __CUDACC__

@@ -17,7 +17,12 @@
 //     released by tcgen05.commit on its "empty" barrier.
 //   * Four epilogue warps compute their row's sin / cos while the ring runs, then read the
 //     accumulator with tcgen05.ld (32 lanes x 32 columns per warp and half), add the bias,
-//     round, rotate and store 64-byte runs to q / the cache.
+//     round, rotate and store to q / the cache.
+//   * 32 tiles would leave most of the 148 SMs idle and each CTA waiting on its own ring, so
+//     for up to 256 rows K is split four ways over a thread-block cluster (128 - 256 CTAs, a
+//     whole K slice in flight per CTA): the four partial accumulators are exchanged through
+//     distributed shared memory as a reduce-scatter, after which each CTA owns 8 columns and
+//     their 8 partners of the tile and finishes those (sums taken in rank order).
 // Every barrier wait is bounded: when one runs out, the CTA records status 5, stops issuing,
 // waits (bounded) for copies and MMAs in flight, frees its TMEM and returns.
 #include <cuda.h>
@@ -104,10 +109,35 @@ __device__ __forceinline__ float round_to_storage(float x) {
   return to_float(from_float<T>(x));
 }
 
-template <typename T>
+// Cluster helpers (SPLIT > 1: the CTAs of a cluster share one output tile and split K).
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_shared_address(uint32_t local_address, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void store_peer_f32(uint32_t address, uint32_t bits) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(address), "r"(bits) : "memory");
+}
+
+// SPLIT = 1: one CTA per tile walks all of K.  SPLIT = 4: a cluster of four CTAs per tile,
+// each accumulates a quarter of K, then the four exchange partial sums through distributed
+// shared memory so that each ends up with (and finishes) a quarter of the tile's columns.
+template <typename T, int SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     qkv_gemm_rope_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const GemmParams p, const __grid_constant__ InvFreqTable freq) {
+  constexpr int kOwn = 32 / SPLIT;  // columns (and as many partners) this CTA finishes
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_bar;
   __shared__ uint32_t tmem_base_slot;
@@ -117,9 +147,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   release_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int rank = SPLIT > 1 ? static_cast<int>(cluster_rank()) : 0;
   const int head = n_tile >> 1, j = n_tile & 1;  // 16 heads: 12 Q, 2 K, 2 V
   const int column0 = head * 128 + j * 32;       // partners at column0 + 64
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t exchange = ring + kStages * kStageBytes;  // [source rank][2 * kOwn values][128 rows] fp32
+  const int my_blocks = p.k_blocks / SPLIT, first_block = rank * my_blocks;
   volatile int* aborted = &abort_flag;
 
   if (threadIdx.x == 0) {
@@ -145,29 +178,49 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // Phase 1 of the cluster barrier: its wait (before the first remote store) proves that
+  // every CTA of the cluster is resident.
+  if (SPLIT > 1) cluster_arrive();
 
-  // hidden comes from the kernel before this one
-  dependency_wait();
-
+  uint32_t lo[32], hi[32];  // this row's accumulators (epilogue warps)
+  bool ready = false;
   if (warp == 4) {
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++issued) {
-        const int s = kb % kStages;
-        if (!wait_barrier(smem_u32(&empty_bar[s]), ((kb / kStages) & 1) ^ 1, aborted)) break;
-        const uint32_t full = smem_u32(&full_bar[s]);
-        const uint32_t bytes = static_cast<uint32_t>(p.a_box_rows) * kTileK * 2 + kBytesB;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(bytes) : "memory");
-        const uint32_t a = ring + s * kStageBytes, b = a + kBytesA;
-        tma_load_2d(a, &map_a, kb * kTileK, m_tile * kTileM, full);
-        tma_load_2d(b, &map_b, kb * kTileK, column0, full);
-        tma_load_2d(b + kBytesB / 2, &map_b, kb * kTileK, column0 + 64, full);
+      const uint32_t bytes = static_cast<uint32_t>(p.a_box_rows) * kTileK * 2 + kBytesB;
+      auto load_weights = [&](int i) {
+        const uint32_t b = ring + (i % kStages) * kStageBytes + kBytesA, full = smem_u32(&full_bar[i % kStages]);
+        tma_load_2d(b, &map_b, (first_block + i) * kTileK, column0, full);
+        tma_load_2d(b + kBytesB / 2, &map_b, (first_block + i) * kTileK, column0 + 64, full);
+      };
+      auto load_rows = [&](int i) {
+        tma_load_2d(ring + (i % kStages) * kStageBytes, &map_a, (first_block + i) * kTileK, m_tile * kTileM,
+                    smem_u32(&full_bar[i % kStages]));
+      };
+      // The weights belong to the model (no kernel writes them): the first ring-full of
+      // weight tiles is requested while the previous kernel is still running; the rows of
+      // `hidden` follow once that kernel has completed.
+      const int early = my_blocks < kStages ? my_blocks : kStages;
+      for (int i = 0; i < early; ++i) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full_bar[i])), "r"(bytes)
+                     : "memory");
+        load_weights(i);
+      }
+      dependency_wait();
+      for (int i = 0; i < early; ++i) load_rows(i);
+      int issued = early;
+      for (int i = early; i < my_blocks; ++i, ++issued) {
+        const int s = i % kStages;
+        if (!wait_barrier(smem_u32(&empty_bar[s]), ((i / kStages) & 1) ^ 1, aborted)) break;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full_bar[s])), "r"(bytes)
+                     : "memory");
+        load_rows(i);
+        load_weights(i);
       }
       if (*aborted) {
         // copies already issued still land in this CTA's shared memory: wait for them
-        for (int kb = issued > kStages ? issued - kStages : 0; kb < issued; ++kb) {
+        for (int i = issued > kStages ? issued - kStages : 0; i < issued; ++i) {
           for (int spin = 0; spin < kSpinLimit; ++spin) {
-            if (try_wait(smem_u32(&full_bar[kb % kStages]), (kb / kStages) & 1)) break;
+            if (try_wait(smem_u32(&full_bar[i % kStages]), (i / kStages) & 1)) break;
             __nanosleep(64);
           }
         }
@@ -175,19 +228,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else if (warp == 5) {
     if (lane == 0) {
+      dependency_wait();
       // instruction descriptor: fp32 accumulate, A and B K-major, N = 64, M = 128
       const uint32_t format = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;  // operand type code
       const uint32_t idesc = (1u << 4) | (format << 7) | (format << 10) | (uint32_t(kTileN >> 3) << 17) |
                              (uint32_t(kTileM >> 4) << 24);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        const int s = kb % kStages;
-        if (!wait_barrier(smem_u32(&full_bar[s]), (kb / kStages) & 1, aborted)) break;
+      for (int i = 0; i < my_blocks; ++i) {
+        const int s = i % kStages;
+        if (!wait_barrier(smem_u32(&full_bar[s]), (i / kStages) & 1, aborted)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = ring + s * kStageBytes, b = a + kBytesA;
         const uint64_t desc_a = operand_descriptor(a), desc_b = operand_descriptor(b);
 #pragma unroll
         for (int k = 0; k < kTileK / 16; ++k) {
-          const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+          const uint32_t accumulate = (i | k) != 0 ? 1u : 0u;
           // 16 elements of K = 32 bytes further along the swizzled row
           asm volatile(
               "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -207,37 +261,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                        smem_u32(&acc_bar))
                    : "memory");
     }
-  } else {
-    // ---- epilogue warps: row m of the batch <-> TMEM lane 32 * warp + lane ----
-    const int m = m_tile * kTileM + warp * 32 + lane;
+  }
+
+  // ---- epilogue warps: row m of the batch <-> TMEM lane 32 * warp + lane ----
+  const int row = warp * 32 + lane;  // meaningful for warps 0-3
+  const int m = m_tile * kTileM + row;
+  const bool is_q = head < 12, is_v = head >= 14;
+  bool in_batch = false, live = false;
+  int64_t slot = -1;
+  float cosine[kOwn], sine[kOwn];
+  if (warp < 4) {
+    dependency_wait();  // positions, slots and valid_tokens may come from the kernel before
     const int live_rows = p.valid_tokens ? min(*p.valid_tokens, p.rows) : p.rows;
-    const bool in_batch = m < p.rows, live = m < live_rows;
-    const bool is_q = head < 12, is_v = head >= 14;
-    int64_t slot = -1;
-    float cosine[32], sine[32];
+    in_batch = m < p.rows, live = m < live_rows;
     if (live) {
       if (!is_q) {
         slot = load_index(p.slots, p.slot_dtype, m);
         if (slot < 0 || slot >= p.num_slots) {
-          atomicExch(p.status, kStatusBadPageId);
+          if (rank == 0) atomicExch(p.status, kStatusBadPageId);
           slot = -1;
         }
       }
       if (!is_v) {
         const float position = load_position(p.positions, p.pos_dtype, m);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float angle = __fmul_rn(position, freq.v[j * 32 + c]);
+        for (int c = 0; c < kOwn; ++c) {
+          const float angle = __fmul_rn(position, freq.v[j * 32 + rank * kOwn + c]);
           cosine[c] = cosf(angle);
           sine[c] = sinf(angle);
         }
       }
     }
     // warp-uniform: tcgen05.ld is a warp-wide instruction
-    const bool ready = __all_sync(0xffffffffu, wait_barrier(smem_u32(&acc_bar), 0, aborted) && !*aborted);
+    ready = __all_sync(0xffffffffu, wait_barrier(smem_u32(&acc_bar), 0, aborted) && !*aborted);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ready) {
-      uint32_t lo[32], hi[32];
       const uint32_t address = tmem_base + (uint32_t(warp * 32) << 16);
 #define QF_TMEM_LOAD_32(dst, addr)                                                                        \
   asm volatile(                                                                                           \
@@ -255,41 +313,85 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       QF_TMEM_LOAD_32(hi, address + 32);
 #undef QF_TMEM_LOAD_32
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-
-      T* first = nullptr;  // 32 elements here, their partners 64 elements further
-      if (is_q) {
-        if (in_batch) first = static_cast<T*>(p.q_out) + m * p.q_stride_row + column0;
-      } else if (live && slot >= 0) {
-        const int kv_head = (head - 12) & 1;
-        first = static_cast<T*>(is_v ? p.v_cache : p.k_cache) + (slot * 2 + kv_head) * 128 + j * 32;
-      }
-      if (first != nullptr) {
-        uint32_t out_lo[16], out_hi[16];
+      if (SPLIT > 1) {
+        cluster_wait();  // phase 1: the peers are resident
+        // reduce-scatter: the partial sums of columns [kOwn * d, kOwn * (d + 1)) and of their
+        // partners go to CTA d, into the slot of this CTA's rank (its own share included)
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float a[2], b[2];
+        for (int d = 0; d < SPLIT; ++d) {
+          const uint32_t slot_base =
+              peer_shared_address(exchange + uint32_t(rank * 2 * kOwn * kTileM + row) * 4, uint32_t(d));
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            // the projection's output in the model dtype, then the rotation in fp32
-            a[e] = round_to_storage<T>(__fadd_rn(__uint_as_float(lo[c + e]), s_bias[c + e]));
-            b[e] = round_to_storage<T>(__fadd_rn(__uint_as_float(hi[c + e]), s_bias[32 + c + e]));
-            if (!is_v) {
-              const float x = a[e], y = b[e];
-              a[e] = __fsub_rn(__fmul_rn(x, cosine[c + e]), __fmul_rn(y, sine[c + e]));
-              b[e] = __fadd_rn(__fmul_rn(y, cosine[c + e]), __fmul_rn(x, sine[c + e]));
-            }
-            if (is_q && !live) a[e] = 0.f, b[e] = 0.f;  // padded rows of a token bucket
+          for (int c = 0; c < kOwn; ++c) {
+            store_peer_f32(slot_base + uint32_t(c * kTileM) * 4, lo[d * kOwn + c]);
+            store_peer_f32(slot_base + uint32_t((kOwn + c) * kTileM) * 4, hi[d * kOwn + c]);
           }
-          out_lo[c >> 1] = pack2<T>(a[0], a[1]);
-          out_hi[c >> 1] = pack2<T>(b[0], b[1]);
         }
+      }
+    }
+  }
+  __syncwarp();
+  if (SPLIT > 1) {
+    // every thread passes phase 1 exactly once, then phase 2: the partial sums have
+    // arrived (release / acquire at cluster scope)
+    if (!(warp < 4 && ready)) cluster_wait();
+    cluster_arrive();
+    cluster_wait();
+  }
+
+  if (warp < 4 && ready) {
+    float sum_lo[kOwn], sum_hi[kOwn];
+    if (SPLIT > 1) {
+      const float* parts = reinterpret_cast<const float*>(smem_raw + (exchange - smem_u32(smem_raw)));
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          reinterpret_cast<uint4*>(first)[v] =
-              make_uint4(out_lo[4 * v], out_lo[4 * v + 1], out_lo[4 * v + 2], out_lo[4 * v + 3]);
-          reinterpret_cast<uint4*>(first + 64)[v] =
-              make_uint4(out_hi[4 * v], out_hi[4 * v + 1], out_hi[4 * v + 2], out_hi[4 * v + 3]);
+      for (int c = 0; c < kOwn; ++c) {
+        float a = 0.f, b = 0.f;
+#pragma unroll
+        for (int source = 0; source < SPLIT; ++source) {  // always in rank order: deterministic
+          a = __fadd_rn(a, parts[(source * 2 * kOwn + c) * kTileM + row]);
+          b = __fadd_rn(b, parts[(source * 2 * kOwn + kOwn + c) * kTileM + row]);
         }
+        sum_lo[c] = a, sum_hi[c] = b;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kOwn; ++c) sum_lo[c] = __uint_as_float(lo[c]), sum_hi[c] = __uint_as_float(hi[c]);
+    }
+
+    const int own0 = rank * kOwn;  // first own column inside the 32-column run
+    T* first = nullptr;            // kOwn elements here, their partners 64 elements further
+    if (is_q) {
+      if (in_batch) first = static_cast<T*>(p.q_out) + m * p.q_stride_row + column0 + own0;
+    } else if (live && slot >= 0) {
+      const int kv_head = (head - 12) & 1;
+      first = static_cast<T*>(is_v ? p.v_cache : p.k_cache) + (slot * 2 + kv_head) * 128 + j * 32 + own0;
+    }
+    if (first != nullptr) {
+      uint32_t out_lo[kOwn / 2], out_hi[kOwn / 2];
+#pragma unroll
+      for (int c = 0; c < kOwn; c += 2) {
+        float a[2], b[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          // the projection's output in the model dtype, then the rotation in fp32
+          a[e] = round_to_storage<T>(__fadd_rn(sum_lo[c + e], s_bias[own0 + c + e]));
+          b[e] = round_to_storage<T>(__fadd_rn(sum_hi[c + e], s_bias[32 + own0 + c + e]));
+          if (!is_v) {
+            const float x = a[e], y = b[e];
+            a[e] = __fsub_rn(__fmul_rn(x, cosine[c + e]), __fmul_rn(y, sine[c + e]));
+            b[e] = __fadd_rn(__fmul_rn(y, cosine[c + e]), __fmul_rn(x, sine[c + e]));
+          }
+          if (is_q && !live) a[e] = 0.f, b[e] = 0.f;  // padded rows of a token bucket
+        }
+        out_lo[c >> 1] = pack2<T>(a[0], a[1]);
+        out_hi[c >> 1] = pack2<T>(b[0], b[1]);
+      }
+#pragma unroll
+      for (int v = 0; v < kOwn / 8; ++v) {
+        reinterpret_cast<uint4*>(first)[v] =
+            make_uint4(out_lo[4 * v], out_lo[4 * v + 1], out_lo[4 * v + 2], out_lo[4 * v + 3]);
+        reinterpret_cast<uint4*>(first + 64)[v] =
+            make_uint4(out_hi[4 * v], out_hi[4 * v + 1], out_hi[4 * v + 2], out_hi[4 * v + 3]);
       }
     }
   }
@@ -346,15 +448,31 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t columns,
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
+constexpr size_t kExchangeBytes = 2 * 32 * kTileM * 4;  // [SPLIT][2 * 32 / SPLIT][128] fp32 = 32 KB
+
+template <typename T, int SPLIT>
+cudaError_t launch_split(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p,
+                         const InvFreqTable& freq, unsigned m_tiles, cudaStream_t stream) {
+  auto kernel = qkv_gemm_rope_kernel<T, SPLIT>;
+  const size_t smem = kGemmSmemBytes + (SPLIT > 1 ? kExchangeBytes : 0);
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (err != cudaSuccess) return err;
+  const dim3 grid(kQkvWidth / kTileN, m_tiles, SPLIT);
+  if (SPLIT == 1) return launch_chained(kernel, grid, dim3(kGemmThreads), smem, stream, map_a, map_b, p, freq);
+  return launch_chained(kernel, grid, dim3(kGemmThreads), smem, stream, ClusterShape{1, 1, SPLIT}, map_a, map_b, p,
+                        freq);
+}
+
 template <typename T>
 cudaError_t launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p,
                         const InvFreqTable& freq, cudaStream_t stream) {
-  auto kernel = qkv_gemm_rope_kernel<T>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kGemmSmemBytes));
-  if (err != cudaSuccess) return err;
-  const dim3 grid(kQkvWidth / kTileN, static_cast<unsigned>((p.rows + kTileM - 1) / kTileM));
-  return launch_chained(kernel, grid, dim3(kGemmThreads), kGemmSmemBytes, stream, map_a, map_b, p, freq);
+  const unsigned m_tiles = static_cast<unsigned>((p.rows + kTileM - 1) / kTileM);
+  // 32 column tiles per 128 rows: split K over a cluster while the grid still fits the
+  // SMs in one wave (one CTA per SM), and K divides into slices of at least two blocks.
+  auto fits = [&](int split) { return p.k_blocks % split == 0 && p.k_blocks >= 2 * split && m_tiles * split <= 4; };
+  if (fits(4)) return launch_split<T, 4>(map_a, map_b, p, freq, m_tiles, stream);
+  if (fits(2)) return launch_split<T, 2>(map_a, map_b, p, freq, m_tiles, stream);
+  return launch_split<T, 1>(map_a, map_b, p, freq, m_tiles, stream);
 }
 
 }  // namespace
