@@ -414,6 +414,14 @@ typedef struct qf_qkv_rope_cache_args {
 } qf_qkv_rope_cache_args;
 int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* args, void* stream);
 
+/* The same call with a per-CTA timeline: timeline [CTAs][QF_GEMM_TIMELINE_COLUMNS] (device
+ * int64, CTAs = 32 column tiles x ceil(rows / 128) x K split, at most 32 * ceil(rows/128) * 4)
+ * receives %globaltimer nanoseconds at {entry, barriers and TMEM ready, previous kernel
+ * complete, first operand tiles landed, last MMA issued, accumulator complete, partial sums
+ * sent, peers' sums arrived, outputs stored, TMEM released}.  For profiling. */
+#define QF_GEMM_TIMELINE_COLUMNS 10
+int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* timeline, void* stream);
+
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the
  * stride-generic kernel; 2 fast per-partition kernel only, no persistent kernel;

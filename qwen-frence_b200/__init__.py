@@ -22,7 +22,7 @@ current torch stream; none has a CPU fallback):
     grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
     advance_decode_state                                   custom_kernels/decode_state.py
     rms_norm, residual_add_rms_norm                        custom_kernels/fused_rms.py
-    qkv_rope_cache                                         custom_kernels/fused_gemm.py
+    qkv_rope_cache, qkv_rope_cache_timeline                custom_kernels/fused_gemm.py
 """
 
 from __future__ import annotations
@@ -56,6 +56,7 @@ _EXPORTS = {
     "rms_norm": "fused_rms",
     "residual_add_rms_norm": "fused_rms",
     "qkv_rope_cache": "fused_gemm",
+    "qkv_rope_cache_timeline": "fused_gemm",
 }
 _LOCAL = {"cabi": "_cabi", "build": "build", "kv_layout": "kv_layout", "workloads": "workloads",
           "decode_step": "decode_step", "sharding": "sharding"}

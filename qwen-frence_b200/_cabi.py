@@ -35,9 +35,11 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
     "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
     "qf_rms_norm", "qf_residual_add_rms_norm", "qf_qkv_rope_cache",
+    "qf_qkv_rope_cache_timeline",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
+GEMM_TIMELINE_COLUMNS = 10
 STATIC_SCRATCH_BYTES = 16 << 20
 
 
@@ -160,6 +162,7 @@ def library():
         c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
         c_int64, c_int32, c_int32, c_float, c_void_p]
     lib.qf_qkv_rope_cache.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p]
+    lib.qf_qkv_rope_cache_timeline.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p, c_void_p]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32

@@ -47,6 +47,7 @@ constexpr int kGemmThreads = 192;             // warps 0-3 epilogue, 4 copies, 5
 constexpr int kTmemColumns = 64;
 constexpr int kQkvWidth = 2048;
 constexpr int kSpinLimit = 1 << 21;
+constexpr int kGemmTimelineColumns = QF_GEMM_TIMELINE_COLUMNS;
 constexpr size_t kGemmSmemBytes = kStages * kStageBytes + 1024;  // + room to align to 1 KB
 
 struct GemmParams {
@@ -60,9 +61,16 @@ struct GemmParams {
   int64_t num_slots;
   const int* valid_tokens;
   int* status;
+  long long* timeline;  // [CTAs][kGemmTimelineColumns] %globaltimer stamps, or null
   int rows, k_blocks, a_box_rows;
   int pos_dtype, slot_dtype;
 };
+
+__device__ __forceinline__ long long nanoseconds_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -126,8 +134,9 @@ __device__ __forceinline__ uint32_t peer_shared_address(uint32_t local_address, 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
   return remote;
 }
-__device__ __forceinline__ void store_peer_f32(uint32_t address, uint32_t bits) {
-  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(address), "r"(bits) : "memory");
+__device__ __forceinline__ void store_peer_v4(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
 }
 
 // SPLIT = 1: one CTA per tile walks all of K.  SPLIT = 4: a cluster of four CTAs per tile,
@@ -147,11 +156,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   release_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  long long* stamps = p.timeline == nullptr ? nullptr
+                                            : p.timeline + ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x +
+                                                            blockIdx.x) * kGemmTimelineColumns;
+  auto stamp = [&](int column) {
+    if (stamps != nullptr) stamps[column] = nanoseconds_now();
+  };
+  if (threadIdx.x == 0) stamp(0);  // entry
   const int rank = SPLIT > 1 ? static_cast<int>(cluster_rank()) : 0;
   const int head = n_tile >> 1, j = n_tile & 1;  // 16 heads: 12 Q, 2 K, 2 V
   const int column0 = head * 128 + j * 32;       // partners at column0 + 64
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t exchange = ring + kStages * kStageBytes;  // [source rank][2 * kOwn values][128 rows] fp32
+  const uint32_t exchange = ring + kStages * kStageBytes;  // [source rank][2 * kOwn / 4 groups][128 rows][4] fp32
   const int my_blocks = p.k_blocks / SPLIT, first_block = rank * my_blocks;
   volatile int* aborted = &abort_flag;
 
@@ -164,6 +180,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions use the async proxy
     abort_flag = 0;
+  }
+  if (threadIdx.x == 4 * 32) {  // the copy thread fetches its two descriptors while the others set up
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
   }
   if (threadIdx.x < kTileN) {  // the model's bias: no kernel writes it
     const int column = column0 + (threadIdx.x & 31) + (threadIdx.x >> 5) * 64;
@@ -178,6 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) stamp(1);  // barriers and TMEM ready
   // Phase 1 of the cluster barrier: its wait (before the first remote store) proves that
   // every CTA of the cluster is resident.
   if (SPLIT > 1) cluster_arrive();
@@ -185,28 +206,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint32_t lo[32], hi[32];  // this row's accumulators (epilogue warps)
   bool ready = false;
   if (warp == 4) {
+    const uint32_t bytes = static_cast<uint32_t>(p.a_box_rows) * kTileK * 2 + kBytesB;
+    auto load_weights = [&](int i) {
+      const uint32_t b = ring + (i % kStages) * kStageBytes + kBytesA, full = smem_u32(&full_bar[i % kStages]);
+      tma_load_2d(b, &map_b, (first_block + i) * kTileK, column0, full);
+      tma_load_2d(b + kBytesB / 2, &map_b, (first_block + i) * kTileK, column0 + 64, full);
+    };
+    auto load_rows = [&](int i) {
+      tma_load_2d(ring + (i % kStages) * kStageBytes, &map_a, (first_block + i) * kTileK, m_tile * kTileM,
+                  smem_u32(&full_bar[i % kStages]));
+    };
+    // The weights belong to the model (no kernel writes them): the first ring-full of weight
+    // tiles is requested while the previous kernel is still running; the rows of `hidden`
+    // follow once that kernel has completed.  One lane per stage: a thread issues a tensor
+    // copy every 70 ns or so, which in one thread would stagger the ring by a microsecond.
+    const int early = my_blocks < kStages ? my_blocks : kStages;
+    if (lane < early) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full_bar[lane])), "r"(bytes)
+                   : "memory");
+      load_weights(lane);
+    }
+    dependency_wait();
+    if (lane == 0) stamp(2);  // previous kernel complete
+    if (lane < early) load_rows(lane);
     if (lane == 0) {
-      const uint32_t bytes = static_cast<uint32_t>(p.a_box_rows) * kTileK * 2 + kBytesB;
-      auto load_weights = [&](int i) {
-        const uint32_t b = ring + (i % kStages) * kStageBytes + kBytesA, full = smem_u32(&full_bar[i % kStages]);
-        tma_load_2d(b, &map_b, (first_block + i) * kTileK, column0, full);
-        tma_load_2d(b + kBytesB / 2, &map_b, (first_block + i) * kTileK, column0 + 64, full);
-      };
-      auto load_rows = [&](int i) {
-        tma_load_2d(ring + (i % kStages) * kStageBytes, &map_a, (first_block + i) * kTileK, m_tile * kTileM,
-                    smem_u32(&full_bar[i % kStages]));
-      };
-      // The weights belong to the model (no kernel writes them): the first ring-full of
-      // weight tiles is requested while the previous kernel is still running; the rows of
-      // `hidden` follow once that kernel has completed.
-      const int early = my_blocks < kStages ? my_blocks : kStages;
-      for (int i = 0; i < early; ++i) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full_bar[i])), "r"(bytes)
-                     : "memory");
-        load_weights(i);
-      }
-      dependency_wait();
-      for (int i = 0; i < early; ++i) load_rows(i);
       int issued = early;
       for (int i = early; i < my_blocks; ++i, ++issued) {
         const int s = i % kStages;
@@ -236,6 +259,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int i = 0; i < my_blocks; ++i) {
         const int s = i % kStages;
         if (!wait_barrier(smem_u32(&full_bar[s]), (i / kStages) & 1, aborted)) break;
+        if (i == 0) stamp(3);  // first operand tiles landed
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = ring + s * kStageBytes, b = a + kBytesA;
         const uint64_t desc_a = operand_descriptor(a), desc_b = operand_descriptor(b);
@@ -256,6 +280,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                          smem_u32(&empty_bar[s]))
                      : "memory");
       }
+      stamp(4);  // last MMA issued
       // always: the epilogue and the TMEM release wait on this
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                        smem_u32(&acc_bar))
@@ -295,6 +320,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // warp-uniform: tcgen05.ld is a warp-wide instruction
     ready = __all_sync(0xffffffffu, wait_barrier(smem_u32(&acc_bar), 0, aborted) && !*aborted);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (threadIdx.x == 0) stamp(5);  // accumulator complete
     if (ready) {
       const uint32_t address = tmem_base + (uint32_t(warp * 32) << 16);
 #define QF_TMEM_LOAD_32(dst, addr)                                                                        \
@@ -319,12 +345,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // partners go to CTA d, into the slot of this CTA's rank (its own share included)
 #pragma unroll
         for (int d = 0; d < SPLIT; ++d) {
-          const uint32_t slot_base =
-              peer_shared_address(exchange + uint32_t(rank * 2 * kOwn * kTileM + row) * 4, uint32_t(d));
+          // [source rank][group of four values][row][4]: 16-byte stores, the lanes of a warp
+          // (consecutive rows) side by side, so a store covers 512 contiguous bytes
+          const uint32_t group0 =
+              peer_shared_address(exchange + uint32_t((rank * (2 * kOwn / 4)) * kTileM + row) * 16, uint32_t(d));
 #pragma unroll
-          for (int c = 0; c < kOwn; ++c) {
-            store_peer_f32(slot_base + uint32_t(c * kTileM) * 4, lo[d * kOwn + c]);
-            store_peer_f32(slot_base + uint32_t((kOwn + c) * kTileM) * 4, hi[d * kOwn + c]);
+          for (int c = 0; c < kOwn; c += 4) {
+            store_peer_v4(group0 + uint32_t((c / 4) * kTileM) * 16, lo[d * kOwn + c], lo[d * kOwn + c + 1],
+                          lo[d * kOwn + c + 2], lo[d * kOwn + c + 3]);
+            store_peer_v4(group0 + uint32_t(((kOwn + c) / 4) * kTileM) * 16, hi[d * kOwn + c], hi[d * kOwn + c + 1],
+                          hi[d * kOwn + c + 2], hi[d * kOwn + c + 3]);
           }
         }
       }
@@ -335,23 +365,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // every thread passes phase 1 exactly once, then phase 2: the partial sums have
     // arrived (release / acquire at cluster scope)
     if (!(warp < 4 && ready)) cluster_wait();
+    if (threadIdx.x == 0) stamp(6);  // partial sums sent
     cluster_arrive();
     cluster_wait();
   }
+  if (threadIdx.x == 0) stamp(7);  // partial sums of the peers arrived
 
   if (warp < 4 && ready) {
     float sum_lo[kOwn], sum_hi[kOwn];
     if (SPLIT > 1) {
-      const float* parts = reinterpret_cast<const float*>(smem_raw + (exchange - smem_u32(smem_raw)));
+      const float4* parts = reinterpret_cast<const float4*>(smem_raw + (exchange - smem_u32(smem_raw)));
 #pragma unroll
-      for (int c = 0; c < kOwn; ++c) {
-        float a = 0.f, b = 0.f;
+      for (int c = 0; c < kOwn; ++c) sum_lo[c] = 0.f, sum_hi[c] = 0.f;
 #pragma unroll
-        for (int source = 0; source < SPLIT; ++source) {  // always in rank order: deterministic
-          a = __fadd_rn(a, parts[(source * 2 * kOwn + c) * kTileM + row]);
-          b = __fadd_rn(b, parts[(source * 2 * kOwn + kOwn + c) * kTileM + row]);
+      for (int source = 0; source < SPLIT; ++source) {  // always in rank order: deterministic
+        const float4* group0 = parts + (source * (2 * kOwn / 4)) * kTileM + row;
+#pragma unroll
+        for (int c = 0; c < kOwn; c += 4) {
+          const float4 a = group0[(c / 4) * kTileM], b = group0[((kOwn + c) / 4) * kTileM];
+          sum_lo[c] = __fadd_rn(sum_lo[c], a.x), sum_lo[c + 1] = __fadd_rn(sum_lo[c + 1], a.y);
+          sum_lo[c + 2] = __fadd_rn(sum_lo[c + 2], a.z), sum_lo[c + 3] = __fadd_rn(sum_lo[c + 3], a.w);
+          sum_hi[c] = __fadd_rn(sum_hi[c], b.x), sum_hi[c + 1] = __fadd_rn(sum_hi[c + 1], b.y);
+          sum_hi[c + 2] = __fadd_rn(sum_hi[c + 2], b.z), sum_hi[c + 3] = __fadd_rn(sum_hi[c + 3], b.w);
         }
-        sum_lo[c] = a, sum_hi[c] = b;
       }
     } else {
 #pragma unroll
@@ -396,6 +432,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  if (threadIdx.x == 0) stamp(8);  // outputs stored
   __syncwarp();
   // ---- teardown: nobody touches TMEM after this barrier; MMAs have completed (or the
   // bounded wait on the accumulator barrier has run out) before it is freed ----
@@ -411,6 +448,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+    if (lane == 0) stamp(9);  // TMEM released
   }
 }
 
@@ -478,8 +516,24 @@ cudaError_t launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, cons
 }  // namespace
 }  // namespace qf
 
+namespace qf {
+namespace {
+int run_qkv_rope_cache(const qf_qkv_rope_cache_args* a, long long* timeline, void* stream);
+}
+}  // namespace qf
+
 extern "C" int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* a, void* stream) {
-  using namespace qf;
+  return qf::run_qkv_rope_cache(a, nullptr, stream);
+}
+
+extern "C" int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* a, int64_t* timeline, void* stream) {
+  QF_REQUIRE(timeline != nullptr, "timeline must not be null");
+  return qf::run_qkv_rope_cache(a, reinterpret_cast<long long*>(timeline), stream);
+}
+
+namespace qf {
+namespace {
+int run_qkv_rope_cache(const qf_qkv_rope_cache_args* a, long long* timeline, void* stream) {
   QF_REQUIRE(a != nullptr, "args must not be null");
   QF_REQUIRE(a->dtype == QF_DTYPE_F16 || a->dtype == QF_DTYPE_BF16, "dtype must be fp16 or bf16");
   QF_REQUIRE(a->rows >= 0, "row count must not be negative");
@@ -515,6 +569,7 @@ extern "C" int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* a, void* stream) 
   p.k_cache = a->k_pool, p.v_cache = a->v_pool, p.num_slots = a->num_slots;
   p.valid_tokens = static_cast<const int*>(a->valid_tokens);
   p.status = device_status_word();
+  p.timeline = timeline;
   QF_REQUIRE(p.status != nullptr, "device status word is unavailable");
   p.rows = a->rows, p.k_blocks = a->in_features / kTileK, p.a_box_rows = box_rows;
   p.pos_dtype = a->positions_dtype, p.slot_dtype = a->slot_dtype;
@@ -523,3 +578,5 @@ extern "C" int qf_qkv_rope_cache(const qf_qkv_rope_cache_args* a, void* stream) 
   QF_CUDA(bf16 ? launch_gemm<__nv_bfloat16>(map_a, map_b, p, freq, s) : launch_gemm<__half>(map_a, map_b, p, freq, s));
   return QF_OK;
 }
+}  // namespace
+}  // namespace qf

@@ -42,8 +42,19 @@ def _require(condition, message):
         raise ValueError(message)
 
 
+def qkv_rope_cache_timeline(x, weight, bias, partials, *, positions, slots, k_pool, v_pool,
+                            valid_tokens=None, theta=1_000_000.0):
+    """The same call, also returning per-CTA %globaltimer stamps [CTAs, 10] (int64,
+    nanoseconds): entry, barriers and TMEM ready, previous kernel complete, first operand
+    tiles landed, last MMA issued, accumulator complete, partial sums sent, peers' sums
+    arrived, outputs stored, TMEM released.  CTAs that do not exist for this shape stay 0."""
+    return qkv_rope_cache(x, weight, bias, partials, positions=positions, slots=slots, k_pool=k_pool,
+                          v_pool=v_pool, valid_tokens=valid_tokens, theta=theta, _timeline=True)
+
+
 def qkv_rope_cache(x, weight, bias, partials, *, positions, slots, k_pool, v_pool,
-                   valid_tokens=None, hidden=None, eps=1e-6, theta=1_000_000.0, config=-1):
+                   valid_tokens=None, hidden=None, eps=1e-6, theta=1_000_000.0, config=-1,
+                   _timeline=False):
     """QKV + bias, rotate-half RoPE, K/V into the paged cache; returns Q [M, 12, 128].
 
     x: (M, K) fp16 / bf16 with unit stride inside a row; weight: (2048, K), the
@@ -97,5 +108,11 @@ def qkv_rope_cache(x, weight, bias, partials, *, positions, slots, k_pool, v_poo
     import ctypes
 
     with cabi.device_of(x):
+        if _timeline:
+            ctas = 32 * (-(-rows // 128)) * 4
+            timeline = torch.zeros((ctas, cabi.GEMM_TIMELINE_COLUMNS), dtype=torch.int64, device=x.device)
+            cabi.check(cabi.library().qf_qkv_rope_cache_timeline(
+                ctypes.byref(args), timeline.data_ptr(), cabi.stream_pointer(x.device)))
+            return q, timeline
         cabi.check(cabi.library().qf_qkv_rope_cache(ctypes.byref(args), cabi.stream_pointer(x.device)))
     return q

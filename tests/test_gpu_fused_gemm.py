@@ -191,3 +191,23 @@ def test_layer_front_in_a_graph(package, oracle, cuda_device):
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, expected)
+
+
+def test_timeline_is_ordered_and_leaves_results_alone(package, cuda_device):
+    """The profiling entry returns the same outputs plus per-CTA timestamps in program
+    order: entry <= ready <= ... <= TMEM released, for every CTA that exists."""
+    for rows, ctas in ((64, 128), (200, 128), (300, 96)):
+        x, weight, bias, positions, slots = _case(cuda_device, rows, exact=True, seed=rows)
+        k_a, v_a = _pools(cuda_device, x.dtype)
+        k_b, v_b = _pools(cuda_device, x.dtype)
+        q_a = package.qkv_rope_cache(x, weight, bias, None, positions=positions, slots=slots, k_pool=k_a, v_pool=v_a)
+        q_b, timeline = package.qkv_rope_cache_timeline(x, weight, bias, None, positions=positions, slots=slots,
+                                                        k_pool=k_b, v_pool=v_b)
+        assert torch.equal(q_a, q_b) and torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+        stamps = timeline.cpu()
+        live = stamps[stamps[:, 0] > 0]
+        assert live.shape[0] == ctas
+        order = [0, 1, 3, 4, 5, 7, 8, 9]  # columns every CTA writes, in program order
+        for earlier, later in zip(order, order[1:]):
+            assert bool((live[:, earlier] <= live[:, later]).all()), (rows, earlier, later)
+        assert int((live[:, 9] - live[:, 0]).max()) < 1_000_000  # a kernel of microseconds
