@@ -298,8 +298,9 @@ int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
  * reads as zeros); 3 when a warp of the tensor-core persistent kernel gave up its
  * bounded poll for an earlier sequence's merge (the one wait in the library that
  * is not a hardware wait_group or barrier; the result of that call is then
- * unreliable).  Synchronises the device; for tests and debugging only.
- * `reset` != 0 clears it after reading. */
+ * unreliable); 4 when qf_advance_decode_metadata moved a position beyond its block
+ * table; 5 when a bounded barrier wait of qf_qkv_rope_cache ran out.  Synchronises
+ * the device; for tests and debugging only.  `reset` != 0 clears it after reading. */
 int qf_device_status(int32_t* status, int32_t reset);
 
 /* Programmatic dependent launch (on by default).  The RoPE / KV-write kernel, the
