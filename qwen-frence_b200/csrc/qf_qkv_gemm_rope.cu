@@ -126,6 +126,9 @@ __device__ __forceinline__ uint32_t cluster_rank() {
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() {  // nothing to publish: presence only
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0) stamp(1);  // barriers and TMEM ready
   // Phase 1 of the cluster barrier: its wait (before the first remote store) proves that
   // every CTA of the cluster is resident.
-  if (SPLIT > 1) cluster_arrive();
+  if (SPLIT > 1) cluster_arrive_relaxed();
 
   uint32_t lo[32], hi[32];  // this row's accumulators (epilogue warps)
   bool ready = false;
