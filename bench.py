@@ -402,6 +402,33 @@ def run_layer_glue(args):
     torch.cuda.synchronize()
     step.reset_metadata()
     unrolled_ms = start.elapsed_time(end) / (chained_replays * steps)
+    # ---- the front of every layer as the engine would run it: norm, projection, attention ----
+    front = None
+    if not step.fp8 and workload.batch:
+        b = workload.batch
+        hidden_in = torch.randn((b, 1536), device=device, dtype=torch.float16, generator=generator) * 0.5
+        branch_in = torch.randn((b, 1536), device=device, dtype=torch.float16, generator=generator) * 0.5
+        layer_weights = [torch.randn((2048, 1536), device=device, dtype=torch.float16, generator=generator) * 0.03
+                         for _ in range(step.layers)]
+
+        def layer_front(fused):
+            for index, w in enumerate(layer_weights):
+                h = package.residual_add_rms_norm(hidden_in, branch_in, gamma)[1]
+                if fused:
+                    q = package.qkv_rope_cache(h, w, bias, None, positions=step.positions, slots=step.slot_mapping,
+                                               k_pool=step.k_pools[index], v_pool=step.v_pools[index])
+                else:
+                    q = package.packed_qkv_rope_cache(torch.nn.functional.linear(h, w, bias), step.positions,
+                                                      step.slot_mapping, step.k_pools[index], step.v_pools[index])
+                package.grouped_splitk_decode_attention(q, step.k_pools[index], step.v_pools[index], step.block_table,
+                                                        step.seq_lens, split_k=step.split_k, partials=step.partials)
+
+        fused_front_ms = time_graph(lambda: layer_front(True), args.steps)
+        library_front_ms = time_graph(lambda: layer_front(False), args.steps)
+        front = {"layers": step.layers, "batch": b,
+                 "ms_per_step_fused_projection": fused_front_ms,
+                 "ms_per_step_library_gemm_plus_epilogue": library_front_ms,
+                 "tokens_per_s_fused_projection": b / (fused_front_ms * 1e-3)}
     status = package.cabi.device_status()
     print(json.dumps({
         "op": "layer_glue", "n_gpus": 1, "data": "synthetic", "dtype": "f16 storage, f32 accumulate",
@@ -414,6 +441,7 @@ def run_layer_glue(args):
                                        "kind": "port", "sample": "numpy oracle, one call on the same rows"}},
         },
         "qkv_rope_cache": projection,
+        "layer_front_norm_projection_attention": front,
         "unrolled_decode_steps": {
             "workload": args.workload, "steps_per_graph": steps, "batch": workload.batch,
             "ms_per_step_single_step_graph": single_ms, "ms_per_step_unrolled_graph": unrolled_ms,
