@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by RUNNING the reference's own Python functions.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path of the qwen-frence tree>
 
 Needs the benjaminW2025/qwen-frence tree on disk (it is imported, unmodified, on
 CPU); the GPU test box has no such tree, which is why the vectors are committed.
@@ -55,7 +55,7 @@ def load(path, name):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of the benjaminW2025/qwen-frence tree")
     root = Path(parser.parse_args().reference)
     sys.dont_write_bytecode = True
     for sub in ("baseline", "engine/kvcache", "engine/graph", "custom_kernels",
