@@ -79,6 +79,9 @@ def parse_args():
     parser.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--fused-write", action="store_true",
+                        help="RoPE + KV write folded into the attention partial pass (two launches per layer\n"
+                             "instead of three; measured slower, see the design notes)")
     parser.add_argument("--kernel", choices=tuple(KERNEL_MODES), default="auto",
                         help="partial-pass kernel of the fused attention call (auto: the library's choice)")
     return parser.parse_args()
@@ -484,7 +487,8 @@ def main():
         args.workload, rank=rank, world_size=world, scaling=args.scaling, seed=args.seed,
         layers=args.layers or None)
     package.cabi.set_tuning(force_generic=KERNEL_MODES[args.kernel])  # read at launch (and capture) time
-    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
+    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package,
+                                          fused_write=args.fused_write)
     step.load_packed_rows()
     step.capture(warmup=2)
     host = step.host_buffers()
@@ -548,8 +552,11 @@ def main():
         for layer in range(step.layers):
             k_pool, v_pool = step.k_pools[layer], step.v_pools[layer]
             scales = (step.k_scales[layer], step.v_scales[layer]) if step.fp8 else None
+            source = q
+            if step.fused_write:  # the partial pass reads the layer's packed rows and writes the new K/V rows
+                source = step.packed[layer].as_strided((workload.batch, 12, 128), (step.packed.stride(1), 128, 1))
             arg_sets.append(splitk.fill_attention_args(
-                cabi, q, k_pool, v_pool, step.block_table, step.seq_lens, split_k=step.split_k,
+                cabi, source, k_pool, v_pool, step.block_table, step.seq_lens, split_k=step.split_k,
                 scale=128 ** -0.5, partials=partials, out=out, kv_scales=scales))
         del fp8
         lib = cabi.library()
@@ -560,8 +567,13 @@ def main():
             # the partial pass of the fused attention call, without its combine
             stream = cabi.stream_pointer(device)
             for arg in arg_sets:
-                cabi.check(lib.qf_grouped_splitk_decode_attention_stages(
-                    ctypes.byref(arg), cabi.STAGE_PARTIAL, stream))
+                if step.fused_write:
+                    cabi.check(lib.qf_packed_rope_decode_attention(
+                        ctypes.byref(arg), step.positions.data_ptr(), cabi.torch_index_code(step.positions.dtype),
+                        1, 1_000_000.0, cabi.STAGE_PARTIAL, stream))
+                else:
+                    cabi.check(lib.qf_grouped_splitk_decode_attention_stages(
+                        ctypes.byref(arg), cabi.STAGE_PARTIAL, stream))
 
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
@@ -578,6 +590,10 @@ def main():
         peak, peak_kind = measured_peak_gbs()
         launch_bytes = partial_kernel_bytes(package, workload, step.split_k, step.fp8, kernel_name,
                                             ctas_per_head)
+        if step.fused_write:
+            # instead of rotated Q (12 x 128 x 2 B, already counted): the packed row (2048 x 2 B) and a
+            # position are read, and the new K and V rows (2 x 2 x 128 x 2 B) written
+            launch_bytes += workload.batch * ((2048 - 1536) * 2 + 4 + 2 * 2 * 128 * 2)
         achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
@@ -585,6 +601,7 @@ def main():
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed, kernel_name))
             if world == 1 and step.split_k == 10 else None,  # the captured launch used split_k 10
+            "fused_write": step.fused_write,
             "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,
             "kv_bytes_per_launch": package.kv_layout.kv_bytes_per_layer(
                 workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2),
@@ -616,7 +633,7 @@ def main():
                 "workload": args.workload, "doc": workload.meta["doc"], "global_batch": global_batch,
                 "batch_per_gpu": workload.batch, "layers": step.layers, "page_size": 16,
                 "heads": "12q/2kv x 128", "split_k": step.split_k, "parallelism": f"by-sequence x{world}",
-                "kernel": args.kernel,
+                "kernel": args.kernel, "fused_write": step.fused_write,
                 "l2": "inputs exceed L2: each step reads %.2f GB of K/V from %d per-layer pools (L2 is 126 MB)"
                       % (step.layers * package.kv_layout.kv_bytes_per_layer(
                           workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2) / 1e9, 2 * step.layers),

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "qf_grouped_splitk_decode_attention_plan", "qf_grouped_splitk_persistent_timeline",
     "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
     "qf_rms_norm", "qf_residual_add_rms_norm", "qf_qkv_rope_cache",
-    "qf_qkv_rope_cache_timeline",
+    "qf_qkv_rope_cache_timeline", "qf_packed_rope_decode_attention",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -163,6 +163,8 @@ def library():
         c_int64, c_int32, c_int32, c_float, c_void_p]
     lib.qf_qkv_rope_cache.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p]
     lib.qf_qkv_rope_cache_timeline.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p, c_void_p]
+    lib.qf_packed_rope_decode_attention.argtypes = [
+        POINTER(DecodeAttentionArgs), c_void_p, c_int32, c_int64, c_double, c_int32, c_void_p]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32

@@ -18,6 +18,7 @@
 #include "qf_decode_partial.cuh"
 #include "qf_decode_stream.cuh"
 #include "qf_decode_mma.cuh"
+#include "qf_rope_math.cuh"
 
 namespace qf {
 namespace {
@@ -414,9 +415,9 @@ size_t mma_smem_bytes(bool fp8) {
 }
 
 // One CTA per SM for 16-bit pools (its rings take most of the shared memory), two for FP8.
-template <typename T, bool FP8, bool PROFILE>
-int launch_mma(const FastParams& p, cudaStream_t stream) {
-  auto kernel = decode_mma_kernel<T, FP8, PROFILE>;
+template <typename T, bool FP8, bool PROFILE, bool ROPE = false>
+int launch_mma(const FastParams& p, cudaStream_t stream, const RopeInputs& rope = RopeInputs{}) {
+  auto kernel = decode_mma_kernel<T, FP8, PROFILE, ROPE>;
   const size_t smem = mma_smem_bytes(FP8);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
@@ -424,7 +425,7 @@ int launch_mma(const FastParams& p, cudaStream_t stream) {
   QF_REQUIRE(resident >= p.kv_heads, "could not size the tensor-core kernel for this device");
   StreamParams sp{p, resident / p.kv_heads};
   QF_CUDA(launch_chained(kernel, dim3(static_cast<unsigned>(sp.ctas_per_head * p.kv_heads)),
-                         dim3(kFastThreads), smem, stream, sp));
+                         dim3(kFastThreads), smem, stream, sp, rope));
   QF_CUDA(cudaGetLastError());
   return QF_OK;
 }
@@ -743,6 +744,44 @@ int qf_grouped_splitk_persistent_timeline(const qf_decode_attention_args* args, 
              "these arguments do not select the tensor-core persistent kernel");
   return qf::launch_persistent_partial(args, kind, static_cast<cudaStream_t>(stream),
                                        reinterpret_cast<long long*>(timeline));
+}
+
+int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const void* positions,
+                                    int32_t positions_dtype, int64_t positions_stride, double base,
+                                    int32_t stages, void* stream) {
+  int rc = qf::validate(args, true);
+  QF_REQUIRE(stages >= 1 && stages <= (QF_STAGE_PARTIAL | QF_STAGE_COMBINE),
+             "stages must be QF_STAGE_PARTIAL, QF_STAGE_COMBINE or both");
+  if (rc != QF_OK) return rc;
+  QF_REQUIRE(positions != nullptr || args->batch == 0, "positions must not be null");
+  QF_REQUIRE(positions_dtype == QF_INDEX_I32 || positions_dtype == QF_INDEX_I64 || positions_dtype == QF_INDEX_F32,
+             "positions must be int32, int64 or float32");
+  if (args->batch == 0) return QF_OK;
+  // q points at the packed rows: 16 segments of 128, the query heads first
+  if (args->kv_fp8 || args->q_heads != 12 || args->kv_heads != 2 || args->q_stride_h != QF_HEAD_DIM ||
+      args->q_stride_b < 16 * QF_HEAD_DIM || args->split_k < 2 ||
+      qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCore) {
+    return qf::fail(QF_EUNSUPPORTED,
+                    "the fused step needs 16-bit pools, the packed 12 + 2 + 2 head layout, split_k >= 2 and a "
+                    "layout the tensor-core kernel takes; run the RoPE / KV write and the attention separately");
+  }
+  int* status = qf::status_word_for_current_device();
+  QF_REQUIRE(status != nullptr, "could not resolve the device status word");
+  const qf::FastParams p = qf::fast_params(args, nullptr, nullptr, status);
+  qf::RopeInputs rope{};
+  rope.packed = static_cast<const unsigned char*>(args->q);
+  rope.row_bytes = args->q_stride_b * 2;
+  rope.positions = positions, rope.pos_stride = positions_stride, rope.pos_dtype = positions_dtype;
+  const qf::InvFreqTable freq = qf::make_inv_freq(base, QF_HEAD_DIM / 2);
+  for (int i = 0; i < QF_HEAD_DIM / 2; ++i) rope.inv_freq[i] = freq.v[i];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (stages & QF_STAGE_PARTIAL) {
+    rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true>(p, s, rope)
+                                     : qf::launch_mma<__nv_bfloat16, false, false, true>(p, s, rope);
+    if (rc != QF_OK) return rc;
+  }
+  if (!(stages & QF_STAGE_COMBINE)) return QF_OK;
+  return qf_grouped_splitk_decode_attention_stages(args, QF_STAGE_COMBINE, stream);
 }
 
 int qf_grouped_splitk_decode_attention(const qf_decode_attention_args* args, void* stream) {

@@ -94,6 +94,7 @@ constexpr int kPaddedHeads = 8;
 #define QF_PIECE_OVERHEAD 6
 #endif
 constexpr int kPieceOverhead = QF_PIECE_OVERHEAD;
+constexpr int kQTileBytes = QF_GQA_GROUP * (QF_HEAD_DIM * 2 + 16);  // six padded rows; cos / sin may follow
 constexpr int kQRowBytes = QF_HEAD_DIM * 2 + 16;                        // Q tile: head stride, padded against bank conflicts
 constexpr int kDepositHeadStride = QF_HEAD_DIM + 8;                      // floats; the pad spreads the heads over banks
 constexpr int kDepositFloats = QF_GQA_GROUP * kDepositHeadStride;        // one warp's O^T of a piece: 3.2 KB
@@ -198,8 +199,64 @@ constexpr int kTimelineColumns = 10;
 // probabilities (relative to the scale of the warp's first page of the piece, which
 // multiplies the accumulator once at the end, so that probabilities keep their
 // magnitude in f16; the reference moves up when a page's scale exceeds it 16 times).
-template <typename T, bool FP8, bool PROFILE>
-__global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) decode_mma_kernel(const StreamParams sp) {
+// What the ROPE variant needs on top: the packed QKV rows of the step ([Q0..Q11 | K0 K1 |
+// V0 V1] x 128 per sequence), their positions and the rotation frequencies.  With ROPE the
+// kernel is the whole layer step: `f.q` points at the packed rows (so the Q tile of a piece
+// arrives unrotated and every warp rotates its copy in shared memory), and the warp that
+// owns a sequence's last page rotates the new K row, copies the new V row, stores both into
+// the pools and only then issues the copy of that page -- so no separate RoPE / KV-write
+// kernel runs.  Same arithmetic as that kernel (fp32 products, one rounding), same bits.
+struct RopeInputs {
+  const unsigned char* packed;  // row b at packed + b * row_bytes
+  int64_t row_bytes;
+  const void* positions;
+  int64_t pos_stride;
+  int pos_dtype;
+  float inv_freq[QF_HEAD_DIM / 2];
+};
+
+// The rare pieces of the ROPE variant are kept out of line: inlined into the three copies
+// of the tile-issue code they put thousands of instructions of sin / cos into the page loop,
+// which then missed the instruction cache on every iteration (a third slower).
+__device__ __noinline__ void rope_store_cos_sin(float2* behind_tile, float position, const RopeInputs& rope, int lane) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int f = lane + 32 * half;
+    const float angle = __fmul_rn(position, rope.inv_freq[f]);
+    behind_tile[f] = make_float2(cosf(angle), sinf(angle));
+  }
+}
+
+// The step's new token: K head rotated and V head copied from the packed row into their pool
+// rows (both at once, so that the loads overlap).
+template <typename T>
+__device__ __noinline__ void rope_store_new_row(unsigned char* k_row_out, unsigned char* v_row_out,
+                                                const unsigned char* row_in, int kv_head, float position,
+                                                const RopeInputs& rope, int lane) {
+  const T* from = reinterpret_cast<const T*>(row_in + (12 + kv_head) * QF_HEAD_DIM * 2);
+  const uint4* v_from = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2);
+  const float x[4] = {to_float(from[lane]), to_float(from[lane + 64]), to_float(from[lane + 32]),
+                      to_float(from[lane + 96])};
+  uint4 v_bits = make_uint4(0u, 0u, 0u, 0u);
+  if (lane < 16) v_bits = v_from[lane];
+  T* to = reinterpret_cast<T*>(k_row_out);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int f = lane + 32 * half;
+    const float angle = __fmul_rn(position, rope.inv_freq[f]);
+    const float c = cosf(angle), sn = sinf(angle);
+    const float x1 = x[2 * half], x2 = x[2 * half + 1];
+    to[f] = from_float<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+    to[f + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+  }
+  if (lane < 16) reinterpret_cast<uint4*>(v_row_out)[lane] = v_bits;
+  __syncwarp();  // the lanes' stores are ordered before the lanes' copies of the rows
+}
+
+template <typename T, bool FP8, bool PROFILE, bool ROPE = false>
+__global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
+    decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
+  static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
   using Ring = RingShape<FP8>;
   constexpr int kAhead = Ring::kAhead;
@@ -284,9 +341,9 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
   // Page ids and row counts of 32 of this warp's units at a time, one per lane (id -3:
   // an empty unit, nothing to load), and the sequence whose Q rows must precede the
   // page (-1 unless it is the warp's first page of the sequence in this share).
-  auto describe = [&](int chunk, int& id, int& rows, int& q_of) {
+  auto describe = [&](int chunk, int& id, int& rows, int& q_of, int& last_of, float& pos) {
     const int k = chunk * 32 + lane;
-    id = -1, rows = 0, q_of = -1;
+    id = -1, rows = 0, q_of = -1, last_of = -1, pos = 0.f;
     if (k < my_pages) {
       const int unit = begin + warp + kMmaWarps * k;
       const int sequence = sequence_of_unit(work, p.batch, unit);
@@ -303,12 +360,17 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
                                           : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
+      // ROPE: the page that takes the step's new token (the last token of the sequence)
+      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
+      // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
+      if (ROPE) pos = load_position(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
       if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous unit is no page of this sequence
     }
   };
-  int id_now, rows_now, q_now, id_next, rows_next, q_next;
-  describe(0, id_now, rows_now, q_now);
-  describe(1, id_next, rows_next, q_next);
+  int id_now, rows_now, q_now, last_now, id_next, rows_next, q_next, last_next;
+  float pos_now, pos_next;
+  describe(0, id_now, rows_now, q_now, last_now, pos_now);
+  describe(1, id_next, rows_next, q_next, last_next, pos_next);
   if (PROFILE) t_ids = id_now + id_next > -100 ? global_nanoseconds() : 0;  // after the ids have arrived
 
   // The warp's tiles, in ring order: for each of its pages [Q rows, if the page is its
@@ -316,12 +378,38 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
   const unsigned char* q_base = static_cast<const unsigned char*>(p.q) +
                                 (static_cast<int64_t>(kv_head) * QF_GQA_GROUP * p.q_sh) * 2;
   int fill_page = 0, fill_stage = 0, fill_slot = 0;  // stage 0: Q, 1: K, 2: V
+  // ROPE: the step's new token of `sequence` is row rows - 1 of page `id`: store it (K
+  // rotated, V as it is) so that the copy of the page brings it along.
+  auto store_new_row = [&](int sequence, int id, int rows, float position) {
+    const int64_t row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
+                        kv_head * p.k_head_bytes;
+    rope_store_new_row<T>(const_cast<unsigned char*>(p.k_pool) + row, const_cast<unsigned char*>(p.v_pool) + row,
+                          rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes, kv_head, position, rope,
+                          lane);
+  };
+  // New rows are stored when their units are described, 32 units at a time: those among the
+  // warp's first 64 units up front (past its first four units in the shadow of the first
+  // tiles' latency: the first four tiles touch at most the first four units), later ones
+  // when the descriptors are refreshed.  Stored from inside the page loop, next to the copy
+  // of its page, a row cost its warp the contents of its ring (a third of the kernel's time).
+  auto store_new_rows_of = [&](int& id_of, int& rows_of, int& last_of, float& pos_of, unsigned lanes) {
+    unsigned pending = __ballot_sync(kFull, last_of >= 0 && id_of >= 0) & lanes;
+    while (pending != 0) {
+      const int source = __ffs(pending) - 1;
+      pending &= pending - 1;
+      store_new_row(__shfl_sync(kFull, last_of, source), __shfl_sync(kFull, id_of, source),
+                    __shfl_sync(kFull, rows_of, source), __shfl_sync(kFull, pos_of, source));
+      if (lane == source) last_of = -1;
+    }
+  };
   auto issue_tile = [&]() {
     int id = -3;
     while (fill_page < my_pages) {
       if (fill_stage == 0 && (fill_page & 31) == 0 && fill_page > 0) {
-        id_now = id_next, rows_now = rows_next, q_now = q_next;
-        describe((fill_page >> 5) + 1, id_next, rows_next, q_next);
+        id_now = id_next, rows_now = rows_next, q_now = q_next, last_now = last_next, pos_now = pos_next;
+        describe((fill_page >> 5) + 1, id_next, rows_next, q_next, last_next, pos_next);
+        // ROPE: the new rows of the 32 units just described, well before their pages are copied
+        if constexpr (ROPE) store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
       }
       id = __shfl_sync(kFull, id_now, fill_page & 31);
       if (id != -3) break;
@@ -339,6 +427,12 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
         for (int j = 0; j < 3; ++j) {
           const int chunk = lane + 32 * j, head = chunk >> 4, c = chunk & 15;
           copy_chunk_async<false>(dst + head * kQRowBytes + c * 16, src + head * p.q_sh * 2 + c * 16);
+        }
+        if constexpr (ROPE) {
+          // cos / sin of this lane's two frequencies ride behind the tile; the same lane
+          // reads them back when it rotates the heads
+          rope_store_cos_sin(reinterpret_cast<float2*>(dst + kQTileBytes),
+                             __shfl_sync(kFull, pos_now, fill_page & 31), rope, lane);
         }
       } else {
         if (id < 0) {
@@ -390,8 +484,13 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
   // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
   // newest K/V rows) and writes the partial buffers the previous combine read.
   dependency_wait();
+  if constexpr (ROPE) store_new_rows_of(id_now, rows_now, last_now, pos_now, 0xfu);
 #pragma unroll
   for (int i = 0; i < kAhead; ++i) issue_tile();
+  if constexpr (ROPE) {
+    store_new_rows_of(id_now, rows_now, last_now, pos_now, ~0xfu);
+    store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
+  }
 
   // ---- fragments ----
   // ldmatrix row addresses inside a tile; matrix i = lane / 8.
@@ -453,6 +552,24 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm) deco
       __syncwarp();
       if (PROFILE && t_first == 0) t_first = global_nanoseconds();
       issue_tile();
+      if constexpr (ROPE) {
+        // the tile holds the six unrotated query heads of the group: rotate them in place,
+        // each lane its two frequencies of every head
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int f = lane + 32 * half;
+          const float2 cs = reinterpret_cast<const float2*>(ring + read_slot * Ring::kSlotBytes + kQTileBytes)[f];
+          const float c = cs.x, sn = cs.y;
+#pragma unroll
+          for (int head = 0; head < QF_GQA_GROUP; ++head) {
+            T* row = reinterpret_cast<T*>(ring + read_slot * Ring::kSlotBytes + head * kQRowBytes);
+            const float x1 = to_float(row[f]), x2 = to_float(row[f + 64]);
+            row[f] = from_float<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+            row[f + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+          }
+        }
+        __syncwarp();
+      }
       const unsigned char* q_tile = ring + read_slot * Ring::kSlotBytes + q_lane_offset;
       read_slot = read_slot == Ring::kSlots - 1 ? 0 : read_slot + 1;
 #pragma unroll

@@ -1,0 +1,97 @@
+"""One layer's decode step in two launches: RoPE + paged KV write folded into the
+attention partial pass, then the split-K combine.
+
+The reference runs this as two operators on one stream -- packed_qkv_rope_cache
+(custom_kernels/packed_qkv_rope_cache.py:91-133) and then
+grouped_splitk_decode_attention (custom_kernels/paged_decode_grouped_splitk.py:228-334),
+engine/graph/paged_graph_decoder.py:234-289 -- and `packed_qkv_rope_attention` returns
+exactly what that pair returns and leaves the pools exactly as it leaves them.  When
+the tensor-core persistent kernel does not apply to the arguments (FP8 pools, split_k
+1, an unusual layout) it runs the pair itself.
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import sys
+from pathlib import Path
+
+Q_HEADS, KV_HEADS, HEAD_DIM = 12, 2, 128
+PACKED_WIDTH = (Q_HEADS + 2 * KV_HEADS) * HEAD_DIM
+
+
+def _sibling(name, directory=None):
+    key = f"qf_hotpath_{name.lstrip('_')}"
+    module = sys.modules.get(key)
+    if module is None:
+        base = Path(__file__).resolve().parent if directory is None else directory
+        spec = importlib.util.spec_from_file_location(key, base / f"{name}.py")
+        module = importlib.util.module_from_spec(spec)
+        sys.modules[key] = module
+        spec.loader.exec_module(module)
+    return module
+
+
+def _require(condition, message):
+    if not condition:
+        raise ValueError(message)
+
+
+def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, block_table, seq_lens, *,
+                              split_k, scale=None, base=1_000_000.0, partials=None, require_fused=False):
+    """RoPE Q/K of the packed rows, write K/V at `slot_mapping`, attend over `block_table`.
+
+    packed: (B, 2048) or (B, 1, 2048) fp16 / bf16, rows of [Q0..Q11 | K0 K1 | V0 V1];
+    positions, slot_mapping, seq_lens: (B,); pools (pages, 16, 2, 128); block_table
+    (B, max_blocks).  `slot_mapping[b]` must name token seq_lens[b] - 1 of sequence b in
+    `block_table` (what the engine builds, engine/graph/paged_graph_decoder.py:392-417):
+    the fused kernel derives the slot from the table.  Returns the attention output
+    (B, 12, 128); the rotated queries are not materialised.  `require_fused=True` raises
+    instead of running the two operators when the fused kernel does not apply.
+    """
+    import ctypes
+
+    import torch
+
+    cabi = _sibling("_cabi", Path(__file__).resolve().parents[1])
+    attention = _sibling("paged_decode_grouped_splitk")
+    if packed.ndim == 3:
+        _require(packed.shape[1] == 1, "packed QKV must have one decode token per row")
+        packed = packed[:, 0, :]
+    _require(packed.ndim == 2 and packed.shape[1] == PACKED_WIDTH, "expected packed QKV shape (batch, 2048)")
+    batch = packed.shape[0]
+    _require(tuple(positions.shape) == (batch,) and tuple(slot_mapping.shape) == (batch,) and
+             tuple(seq_lens.shape) == (batch,), "positions, slot_mapping and seq_lens must hold one entry per row")
+    _require(packed.is_cuda, "packed QKV must live on a CUDA device")
+
+    def pair():
+        if require_fused:
+            raise RuntimeError("the fused step does not apply to these arguments")
+        q = _sibling("packed_qkv_rope_cache").packed_qkv_rope_cache(
+            packed, positions, slot_mapping, k_pool, v_pool, base=base)
+        return attention.grouped_splitk_decode_attention(
+            q, k_pool, v_pool, block_table, seq_lens, split_k=split_k, scale=scale, partials=partials)
+
+    fused_ok = (batch > 0 and int(split_k) >= 2 and k_pool.dtype == packed.dtype and packed.stride(1) == 1
+                and tuple(k_pool.shape[1:]) == (16, KV_HEADS, HEAD_DIM)
+                and k_pool.shape == v_pool.shape and block_table.ndim == 2 and block_table.shape[1] > 0)
+    if not fused_ok:
+        return pair()
+    q_view = packed.as_strided((batch, Q_HEADS, HEAD_DIM), (packed.stride(0), HEAD_DIM, 1))
+    out = torch.empty((batch, Q_HEADS, HEAD_DIM), dtype=packed.dtype, device=packed.device)
+    if partials is None:
+        shape = (batch, int(split_k), Q_HEADS, HEAD_DIM)
+        partials = (torch.empty(shape, dtype=torch.float32, device=packed.device),
+                    torch.empty(shape[:3], dtype=torch.float32, device=packed.device),
+                    torch.empty(shape[:3], dtype=torch.float32, device=packed.device))
+    args = attention.fill_attention_args(
+        cabi, q_view, k_pool, v_pool, block_table, seq_lens, split_k=int(split_k),
+        scale=HEAD_DIM ** -0.5 if scale is None else scale, partials=partials, out=out)
+    if cabi.fused_kernel_plan(args)[0] != "decode_mma_kernel":
+        return pair()
+    positions = positions.contiguous()
+    with cabi.device_of(packed):
+        cabi.check(cabi.library().qf_packed_rope_decode_attention(
+            ctypes.byref(args), positions.data_ptr(), cabi.torch_index_code(positions.dtype, allow_float=True),
+            1, float(base), cabi.STAGE_PARTIAL | cabi.STAGE_COMBINE, cabi.stream_pointer(packed.device)))
+    return out

@@ -26,7 +26,7 @@ from . import kv_layout
 
 class DecodeStep:
     def __init__(self, workload, device, *, split_k=None, dtype=torch.float16,
-                 fill_pools=True, package=None):
+                 fill_pools=True, package=None, fused_write=False):
         import sys
 
         self.package = package if package is not None else sys.modules[__package__]
@@ -39,7 +39,10 @@ class DecodeStep:
         self.split_k = int(split_k) if split_k else kv_layout.plan_split_k(
             max(self.batch, 1), workload.max_context,
             sm_count=torch.cuda.get_device_properties(self.device).multi_processor_count)
-        self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 else 3)
+        # fused_write: RoPE + KV write inside the attention partial pass (two launches per
+        # layer instead of three) where the tensor-core kernel applies
+        self.fused_write = bool(fused_write) and not self.fp8 and self.split_k > 1
+        self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 or self.fused_write else 3)
 
         shape = (workload.num_pages, kv_layout.PAGE_SIZE, kv_layout.KV_HEADS, kv_layout.HEAD_DIM)
         pool_dtype = torch.uint8 if self.fp8 else dtype
@@ -147,6 +150,10 @@ class DecodeStep:
                 q, self.k_pools[index], self.v_pools[index], self.k_scales[index], self.v_scales[index],
                 self.block_table, self.seq_lens, split_k=self.split_k,
                 partials=self._fp8_partials())
+        elif self.fused_write:
+            out = pkg.packed_qkv_rope_attention(
+                self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index],
+                self.block_table, self.seq_lens, split_k=self.split_k, partials=self.partials)
         else:
             q = pkg.packed_qkv_rope_cache(
                 self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index])
