@@ -54,7 +54,8 @@ FALLBACK_HBM_GBS = 6650.0
 # ncu capture summarised in profiles/ (same per-launch workload as a full-size launch: one
 # layer of the named workload at seed 0).  Workloads without a capture report null.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.00e6,
+    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.00e6,          # RoPE / KV write as its own kernel
+    ("decode_b64", 0, "decode_mma_kernel+rope"): 137.60e6 + 3.85e6,     # the default: write folded in
     ("decode_b64", 0, "decode_partial_kernel"): 137.92e6 + 5.0e6,
 }
 
@@ -79,9 +80,8 @@ def parse_args():
     parser.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--seed", type=int, default=0)
-    parser.add_argument("--fused-write", action="store_true",
-                        help="RoPE + KV write folded into the attention partial pass (two launches per layer\n"
-                             "instead of three; measured slower, see the design notes)")
+    parser.add_argument("--unfused-write", action="store_true",
+                        help="RoPE + KV write as its own kernel: three launches per layer instead of two")
     parser.add_argument("--kernel", choices=tuple(KERNEL_MODES), default="auto",
                         help="partial-pass kernel of the fused attention call (auto: the library's choice)")
     return parser.parse_args()
@@ -488,7 +488,7 @@ def main():
         layers=args.layers or None)
     package.cabi.set_tuning(force_generic=KERNEL_MODES[args.kernel])  # read at launch (and capture) time
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package,
-                                          fused_write=args.fused_write)
+                                          fused_write=not args.unfused_write and args.kernel in ("auto", "persistent_mma"))
     step.load_packed_rows()
     step.capture(warmup=2)
     host = step.host_buffers()
@@ -570,7 +570,7 @@ def main():
                 if step.fused_write:
                     cabi.check(lib.qf_packed_rope_decode_attention(
                         ctypes.byref(arg), step.positions.data_ptr(), cabi.torch_index_code(step.positions.dtype),
-                        1, 1_000_000.0, cabi.STAGE_PARTIAL, stream))
+                        1, step.rope_table.data_ptr(), step.rope_table.shape[0], cabi.STAGE_PARTIAL, stream))
                 else:
                     cabi.check(lib.qf_grouped_splitk_decode_attention_stages(
                         ctypes.byref(arg), cabi.STAGE_PARTIAL, stream))
@@ -591,15 +591,16 @@ def main():
         launch_bytes = partial_kernel_bytes(package, workload, step.split_k, step.fp8, kernel_name,
                                             ctas_per_head)
         if step.fused_write:
-            # instead of rotated Q (12 x 128 x 2 B, already counted): the packed row (2048 x 2 B) and a
-            # position are read, and the new K and V rows (2 x 2 x 128 x 2 B) written
-            launch_bytes += workload.batch * ((2048 - 1536) * 2 + 4 + 2 * 2 * 128 * 2)
+            # instead of rotated Q (12 x 128 x 2 B, already counted): the packed row (2048 x 2 B), a position
+            # and its 512 B of the rotation table are read, the new K and V rows (2 x 2 x 128 x 2 B) written
+            launch_bytes += workload.batch * ((2048 - 1536) * 2 + 4 + 512 + 2 * 2 * 128 * 2)
         achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.seed, kernel_name))
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(
+                (args.workload, args.seed, kernel_name + ("+rope" if step.fused_write else "")))
             if world == 1 and step.split_k == 10 else None,  # the captured launch used split_k 10
             "fused_write": step.fused_write,
             "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,

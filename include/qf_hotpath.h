@@ -431,20 +431,31 @@ int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* time
  * the results are those of that pair, bit for bit in the pools.
  *   args->q            the packed rows [batch, 2048] = [Q0..Q11 | K0 K1 | V0 V1] x 128
  *                      (q_stride_b = row stride, q_stride_h = 128, q_stride_d = 1)
- *   positions          [batch]: rotation position of the row (the engine's seq_len - 1)
+ *   positions          [batch] int32 / int64: rotation position of the row (the engine's
+ *                      seq_len - 1), an index into rope_table
+ *   rope_table         [table_positions][64] (cos, sin) fp32 pairs from qf_build_rope_table;
+ *                      a position outside it is clamped and recorded (status 4)
  * Every warp that works on a sequence rotates its own copy of the six query heads in
- * shared memory; the warp that owns the sequence's last page stores the rotated K row
- * and the V row at token seq_len - 1 of that page -- the slot the engine's slot mapping
- * names (engine/graph/paged_graph_decoder.py:392-417) -- before it copies the page.
- * Sequences of length 0 write nothing.  No rotated Q is returned.
+ * shared memory (the position's row of the table travels with the Q tile); the warp that
+ * owns the sequence's last page stores the rotated K row and the V row at token
+ * seq_len - 1 of that page -- the slot the engine's slot mapping names
+ * (engine/graph/paged_graph_decoder.py:392-417) -- before it copies the page.  Sequences of
+ * length 0 write nothing.  No rotated Q is returned.
  * QF_EUNSUPPORTED unless: 16-bit pools, 12 + 2 heads, split_k >= 2, and arguments for
  * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA;
  * callers then run qf_rope_kv_write and qf_grouped_splitk_decode_attention.
  * `stages`: QF_STAGE_PARTIAL | QF_STAGE_COMBINE for the whole step; one of them alone
  * launches only that kernel (timing). */
 int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const void* positions,
-                                    int32_t positions_dtype, int64_t positions_stride, double base,
-                                    int32_t stages, void* stream);
+                                    int32_t positions_dtype, int64_t positions_stride,
+                                    const float* rope_table, int32_t table_positions, int32_t stages,
+                                    void* stream);
+
+/* table[position][f] = (cosf(a), sinf(a)), a = (float)position * inv_freq[f], f < 64,
+ * inv_freq as in qf_rope_kv_write: the cos / sin cache the model's own RoPE keeps
+ * (engine/kvcache/paged_forward.py build_rope_from_positions), in fp32 and with the fused
+ * kernels' formula.  `table` holds positions * 64 * 2 floats. */
+int qf_build_rope_table(float* table, int32_t positions, double base, void* stream);
 
 /* Switches for tests and experiments (process-wide, read at launch time).
  * force_generic: 0 automatic choice; 1 every attention call goes through the

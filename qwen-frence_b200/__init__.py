@@ -23,7 +23,7 @@ current torch stream; none has a CPU fallback):
     advance_decode_state                                   custom_kernels/decode_state.py
     rms_norm, residual_add_rms_norm                        custom_kernels/fused_rms.py
     qkv_rope_cache, qkv_rope_cache_timeline                custom_kernels/fused_gemm.py
-    packed_qkv_rope_attention                              custom_kernels/fused_decode_step.py
+    packed_qkv_rope_attention, build_rope_table            custom_kernels/fused_decode_step.py
 """
 
 from __future__ import annotations
@@ -59,6 +59,7 @@ _EXPORTS = {
     "qkv_rope_cache": "fused_gemm",
     "qkv_rope_cache_timeline": "fused_gemm",
     "packed_qkv_rope_attention": "fused_decode_step",
+    "build_rope_table": "fused_decode_step",
 }
 _LOCAL = {"cabi": "_cabi", "build": "build", "kv_layout": "kv_layout", "workloads": "workloads",
           "decode_step": "decode_step", "sharding": "sharding"}

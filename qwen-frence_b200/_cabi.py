@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "qf_set_dependent_launch", "qf_order_next_launch", "qf_advance_decode_metadata",
     "qf_rms_norm", "qf_residual_add_rms_norm", "qf_qkv_rope_cache",
     "qf_qkv_rope_cache_timeline", "qf_packed_rope_decode_attention",
+    "qf_build_rope_table",
 )
 KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
@@ -164,7 +165,8 @@ def library():
     lib.qf_qkv_rope_cache.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p]
     lib.qf_qkv_rope_cache_timeline.argtypes = [POINTER(QkvRopeCacheArgs), c_void_p, c_void_p]
     lib.qf_packed_rope_decode_attention.argtypes = [
-        POINTER(DecodeAttentionArgs), c_void_p, c_int32, c_int64, c_double, c_int32, c_void_p]
+        POINTER(DecodeAttentionArgs), c_void_p, c_int32, c_int64, c_void_p, c_int32, c_int32, c_void_p]
+    lib.qf_build_rope_table.argtypes = [c_void_p, c_int32, c_double, c_void_p]
     for name in EXPORTED_SYMBOLS:
         if name not in ("qf_last_error",):
             getattr(lib, name).restype = c_int32

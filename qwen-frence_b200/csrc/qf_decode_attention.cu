@@ -437,6 +437,17 @@ int launch_mma_for_pools(const FastParams& p, bool fp8, cudaStream_t stream) {
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
+// (cos, sin) of position * inv_freq[f] for every position and rotary frequency: the very
+// expressions of the RoPE / KV-write kernel, so a kernel that reads the table rotates to the
+// same bits as that kernel.
+__global__ void rope_table_kernel(float2* table, int positions, const __grid_constant__ InvFreqTable freq) {
+  const int64_t entry = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (entry >= static_cast<int64_t>(positions) * (QF_HEAD_DIM / 2)) return;
+  const int position = static_cast<int>(entry / (QF_HEAD_DIM / 2)), f = static_cast<int>(entry % (QF_HEAD_DIM / 2));
+  const float angle = __fmul_rn(static_cast<float>(position), freq.v[f]);
+  table[entry] = make_float2(cosf(angle), sinf(angle));
+}
+
 int validate(const qf_decode_attention_args* a, bool need_out) {
   QF_REQUIRE(a != nullptr, "args must not be null");
   QF_REQUIRE(a->batch >= 0 && a->q_heads >= 1 && a->kv_heads >= 1, "invalid batch or head counts");
@@ -746,16 +757,31 @@ int qf_grouped_splitk_persistent_timeline(const qf_decode_attention_args* args, 
                                        reinterpret_cast<long long*>(timeline));
 }
 
+int qf_build_rope_table(float* table, int32_t positions, double base, void* stream) {
+  QF_REQUIRE(positions >= 0, "the number of positions must not be negative");
+  if (positions == 0) return QF_OK;
+  QF_REQUIRE(table != nullptr && qf::aligned16(table), "the table must be a 16-byte aligned device buffer");
+  const qf::InvFreqTable freq = qf::make_inv_freq(base, QF_HEAD_DIM / 2);
+  const int64_t entries = static_cast<int64_t>(positions) * (QF_HEAD_DIM / 2);
+  const unsigned blocks = static_cast<unsigned>((entries + 255) / 256);
+  qf::rope_table_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<float2*>(table),
+                                                                             positions, freq);
+  QF_CUDA(cudaGetLastError());
+  return QF_OK;
+}
+
 int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const void* positions,
-                                    int32_t positions_dtype, int64_t positions_stride, double base,
-                                    int32_t stages, void* stream) {
+                                    int32_t positions_dtype, int64_t positions_stride, const float* rope_table,
+                                    int32_t table_positions, int32_t stages, void* stream) {
   int rc = qf::validate(args, true);
   QF_REQUIRE(stages >= 1 && stages <= (QF_STAGE_PARTIAL | QF_STAGE_COMBINE),
              "stages must be QF_STAGE_PARTIAL, QF_STAGE_COMBINE or both");
   if (rc != QF_OK) return rc;
   QF_REQUIRE(positions != nullptr || args->batch == 0, "positions must not be null");
-  QF_REQUIRE(positions_dtype == QF_INDEX_I32 || positions_dtype == QF_INDEX_I64 || positions_dtype == QF_INDEX_F32,
-             "positions must be int32, int64 or float32");
+  QF_REQUIRE(positions_dtype == QF_INDEX_I32 || positions_dtype == QF_INDEX_I64,
+             "positions must be int32 or int64");
+  QF_REQUIRE(rope_table != nullptr && table_positions >= 1 && qf::aligned16(rope_table),
+             "the rotation table must be a 16-byte aligned device buffer of at least one position");
   if (args->batch == 0) return QF_OK;
   // q points at the packed rows: 16 segments of 128, the query heads first
   if (args->kv_fp8 || args->q_heads != 12 || args->kv_heads != 2 || args->q_stride_h != QF_HEAD_DIM ||
@@ -772,8 +798,7 @@ int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const 
   rope.packed = static_cast<const unsigned char*>(args->q);
   rope.row_bytes = args->q_stride_b * 2;
   rope.positions = positions, rope.pos_stride = positions_stride, rope.pos_dtype = positions_dtype;
-  const qf::InvFreqTable freq = qf::make_inv_freq(base, QF_HEAD_DIM / 2);
-  for (int i = 0; i < QF_HEAD_DIM / 2; ++i) rope.inv_freq[i] = freq.v[i];
+  rope.table = reinterpret_cast<const float2*>(rope_table), rope.table_positions = table_positions;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (stages & QF_STAGE_PARTIAL) {
     rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true>(p, s, rope)

@@ -200,58 +200,24 @@ constexpr int kTimelineColumns = 10;
 // multiplies the accumulator once at the end, so that probabilities keep their
 // magnitude in f16; the reference moves up when a page's scale exceeds it 16 times).
 // What the ROPE variant needs on top: the packed QKV rows of the step ([Q0..Q11 | K0 K1 |
-// V0 V1] x 128 per sequence), their positions and the rotation frequencies.  With ROPE the
-// kernel is the whole layer step: `f.q` points at the packed rows (so the Q tile of a piece
-// arrives unrotated and every warp rotates its copy in shared memory), and the warp that
-// owns a sequence's last page rotates the new K row, copies the new V row, stores both into
-// the pools and only then issues the copy of that page -- so no separate RoPE / KV-write
-// kernel runs.  Same arithmetic as that kernel (fp32 products, one rounding), same bits.
+// V0 V1] x 128 per sequence), their positions and a table of (cos, sin) per position and
+// rotary frequency (qf_build_rope_table: the same fp32 expressions as the RoPE / KV-write
+// kernel, so the same bits).  With ROPE the kernel is the whole layer step: `f.q` points at
+// the packed rows, so the Q tile of a piece arrives unrotated, its position's 512 bytes of
+// the table ride behind it as one more 16-byte copy per lane, and every warp rotates its
+// copy of the six heads in shared memory; the warp that owns a sequence's last page rotates
+// the new K row, copies the new V row and stores both into the pools before it copies that
+// page -- so no separate RoPE / KV-write kernel runs.  No sin / cos and no call in this
+// kernel: with them (inlined or out of line) the page loop ran 4 to 10 us slower.
 struct RopeInputs {
   const unsigned char* packed;  // row b at packed + b * row_bytes
   int64_t row_bytes;
-  const void* positions;
+  const void* positions;        // integer positions
   int64_t pos_stride;
+  const float2* table;          // [table_positions][64] (cos, sin)
   int pos_dtype;
-  float inv_freq[QF_HEAD_DIM / 2];
+  int table_positions;
 };
-
-// The rare pieces of the ROPE variant are kept out of line: inlined into the three copies
-// of the tile-issue code they put thousands of instructions of sin / cos into the page loop,
-// which then missed the instruction cache on every iteration (a third slower).
-__device__ __noinline__ void rope_store_cos_sin(float2* behind_tile, float position, const RopeInputs& rope, int lane) {
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int f = lane + 32 * half;
-    const float angle = __fmul_rn(position, rope.inv_freq[f]);
-    behind_tile[f] = make_float2(cosf(angle), sinf(angle));
-  }
-}
-
-// The step's new token: K head rotated and V head copied from the packed row into their pool
-// rows (both at once, so that the loads overlap).
-template <typename T>
-__device__ __noinline__ void rope_store_new_row(unsigned char* k_row_out, unsigned char* v_row_out,
-                                                const unsigned char* row_in, int kv_head, float position,
-                                                const RopeInputs& rope, int lane) {
-  const T* from = reinterpret_cast<const T*>(row_in + (12 + kv_head) * QF_HEAD_DIM * 2);
-  const uint4* v_from = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2);
-  const float x[4] = {to_float(from[lane]), to_float(from[lane + 64]), to_float(from[lane + 32]),
-                      to_float(from[lane + 96])};
-  uint4 v_bits = make_uint4(0u, 0u, 0u, 0u);
-  if (lane < 16) v_bits = v_from[lane];
-  T* to = reinterpret_cast<T*>(k_row_out);
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int f = lane + 32 * half;
-    const float angle = __fmul_rn(position, rope.inv_freq[f]);
-    const float c = cosf(angle), sn = sinf(angle);
-    const float x1 = x[2 * half], x2 = x[2 * half + 1];
-    to[f] = from_float<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
-    to[f + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
-  }
-  if (lane < 16) reinterpret_cast<uint4*>(v_row_out)[lane] = v_bits;
-  __syncwarp();  // the lanes' stores are ordered before the lanes' copies of the rows
-}
 
 template <typename T, bool FP8, bool PROFILE, bool ROPE = false>
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
@@ -341,9 +307,9 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   // Page ids and row counts of 32 of this warp's units at a time, one per lane (id -3:
   // an empty unit, nothing to load), and the sequence whose Q rows must precede the
   // page (-1 unless it is the warp's first page of the sequence in this share).
-  auto describe = [&](int chunk, int& id, int& rows, int& q_of, int& last_of, float& pos) {
+  auto describe = [&](int chunk, int& id, int& rows, int& q_of, int& last_of, int& pos) {
     const int k = chunk * 32 + lane;
-    id = -1, rows = 0, q_of = -1, last_of = -1, pos = 0.f;
+    id = -1, rows = 0, q_of = -1, last_of = -1, pos = 0;
     if (k < my_pages) {
       const int unit = begin + warp + kMmaWarps * k;
       const int sequence = sequence_of_unit(work, p.batch, unit);
@@ -363,12 +329,16 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       // ROPE: the page that takes the step's new token (the last token of the sequence)
       if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
       // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
-      if (ROPE) pos = load_position(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
+      if (ROPE) {
+        const int64_t at = load_index(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
+        if (at < 0 || at >= rope.table_positions) atomicExch(p.status, kStatusPositionPastTable);
+        pos = static_cast<int>(at < 0 ? 0 : (at >= rope.table_positions ? rope.table_positions - 1 : at));
+      }
       if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous unit is no page of this sequence
     }
   };
   int id_now, rows_now, q_now, last_now, id_next, rows_next, q_next, last_next;
-  float pos_now, pos_next;
+  int pos_now, pos_next;  // ROPE: row of the (cos, sin) table
   describe(0, id_now, rows_now, q_now, last_now, pos_now);
   describe(1, id_next, rows_next, q_next, last_next, pos_next);
   if (PROFILE) t_ids = id_now + id_next > -100 ? global_nanoseconds() : 0;  // after the ids have arrived
@@ -380,19 +350,32 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   int fill_page = 0, fill_stage = 0, fill_slot = 0;  // stage 0: Q, 1: K, 2: V
   // ROPE: the step's new token of `sequence` is row rows - 1 of page `id`: store it (K
   // rotated, V as it is) so that the copy of the page brings it along.
-  auto store_new_row = [&](int sequence, int id, int rows, float position) {
+  auto store_new_row = [&](int sequence, int id, int rows, int position) {
     const int64_t row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
                         kv_head * p.k_head_bytes;
-    rope_store_new_row<T>(const_cast<unsigned char*>(p.k_pool) + row, const_cast<unsigned char*>(p.v_pool) + row,
-                          rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes, kv_head, position, rope,
-                          lane);
+    const unsigned char* row_in = rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes;
+    const T* from = reinterpret_cast<const T*>(row_in + (12 + kv_head) * QF_HEAD_DIM * 2);
+    const float2* cs = rope.table + static_cast<int64_t>(position) * (QF_HEAD_DIM / 2);
+    // every load first: one trip to memory for the whole row
+    const float2 cs_lo = cs[lane], cs_hi = cs[lane + 32];
+    const float x1 = to_float(from[lane]), x2 = to_float(from[lane + 64]);
+    const float y1 = to_float(from[lane + 32]), y2 = to_float(from[lane + 96]);
+    uint4 v_bits = make_uint4(0u, 0u, 0u, 0u);
+    if (lane < 16) v_bits = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2)[lane];
+    T* to = reinterpret_cast<T*>(const_cast<unsigned char*>(p.k_pool) + row);
+    to[lane] = from_float<T>(__fsub_rn(__fmul_rn(x1, cs_lo.x), __fmul_rn(x2, cs_lo.y)));
+    to[lane + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, cs_lo.x), __fmul_rn(x1, cs_lo.y)));
+    to[lane + 32] = from_float<T>(__fsub_rn(__fmul_rn(y1, cs_hi.x), __fmul_rn(y2, cs_hi.y)));
+    to[lane + 96] = from_float<T>(__fadd_rn(__fmul_rn(y2, cs_hi.x), __fmul_rn(y1, cs_hi.y)));
+    if (lane < 16) reinterpret_cast<uint4*>(const_cast<unsigned char*>(p.v_pool) + row)[lane] = v_bits;
+    __syncwarp();  // the lanes' stores are ordered before the lanes' copies of the rows
   };
   // New rows are stored when their units are described, 32 units at a time: those among the
   // warp's first 64 units up front (past its first four units in the shadow of the first
   // tiles' latency: the first four tiles touch at most the first four units), later ones
   // when the descriptors are refreshed.  Stored from inside the page loop, next to the copy
   // of its page, a row cost its warp the contents of its ring (a third of the kernel's time).
-  auto store_new_rows_of = [&](int& id_of, int& rows_of, int& last_of, float& pos_of, unsigned lanes) {
+  auto store_new_rows_of = [&](int& id_of, int& rows_of, int& last_of, int& pos_of, unsigned lanes) {
     unsigned pending = __ballot_sync(kFull, last_of >= 0 && id_of >= 0) & lanes;
     while (pending != 0) {
       const int source = __ffs(pending) - 1;
@@ -429,10 +412,11 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
           copy_chunk_async<false>(dst + head * kQRowBytes + c * 16, src + head * p.q_sh * 2 + c * 16);
         }
         if constexpr (ROPE) {
-          // cos / sin of this lane's two frequencies ride behind the tile; the same lane
-          // reads them back when it rotates the heads
-          rope_store_cos_sin(reinterpret_cast<float2*>(dst + kQTileBytes),
-                             __shfl_sync(kFull, pos_now, fill_page & 31), rope, lane);
+          // the position's (cos, sin) of all 64 frequencies ride behind the tile: 32 chunks
+          const int position = __shfl_sync(kFull, pos_now, fill_page & 31);
+          copy_chunk_async<false>(dst + kQTileBytes + lane * 16,
+                                  reinterpret_cast<const unsigned char*>(
+                                      rope.table + static_cast<int64_t>(position) * (QF_HEAD_DIM / 2)) + lane * 16);
         }
       } else {
         if (id < 0) {

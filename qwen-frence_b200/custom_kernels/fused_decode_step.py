@@ -37,8 +37,31 @@ def _require(condition, message):
         raise ValueError(message)
 
 
+_tables = {}
+
+
+def build_rope_table(positions, *, base=1_000_000.0, device=None):
+    """(cos, sin) fp32 pairs [positions, 64, 2] of every position and rotary frequency, with
+    the expressions of the RoPE / KV-write kernel (so the fused step rotates to the same
+    bits).  Cached per (device, base, positions); 512 bytes per position."""
+    import torch
+
+    cabi = _sibling("_cabi", Path(__file__).resolve().parents[1])
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index, float(base), int(positions))
+    table = _tables.get(key)
+    if table is None:
+        table = torch.empty((int(positions), HEAD_DIM // 2, 2), dtype=torch.float32, device=device)
+        with cabi.device_of(table):
+            cabi.check(cabi.library().qf_build_rope_table(
+                table.data_ptr(), int(positions), float(base), cabi.stream_pointer(device)))
+        _tables[key] = table
+    return table
+
+
 def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, block_table, seq_lens, *,
-                              split_k, scale=None, base=1_000_000.0, partials=None, require_fused=False):
+                              split_k, scale=None, base=1_000_000.0, partials=None, rope_table=None,
+                              require_fused=False):
     """RoPE Q/K of the packed rows, write K/V at `slot_mapping`, attend over `block_table`.
 
     packed: (B, 2048) or (B, 1, 2048) fp16 / bf16, rows of [Q0..Q11 | K0 K1 | V0 V1];
@@ -46,7 +69,10 @@ def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, b
     (B, max_blocks).  `slot_mapping[b]` must name token seq_lens[b] - 1 of sequence b in
     `block_table` (what the engine builds, engine/graph/paged_graph_decoder.py:392-417):
     the fused kernel derives the slot from the table.  Returns the attention output
-    (B, 12, 128); the rotated queries are not materialised.  `require_fused=True` raises
+    (B, 12, 128); the rotated queries are not materialised.  `rope_table`: the result of
+    `build_rope_table` covering every position (default: a cached table of as many
+    positions as the block table can hold -- build it before capturing a graph; positions
+    must then be int32 / int64).  `require_fused=True` raises
     instead of running the two operators when the fused kernel does not apply.
     """
     import ctypes
@@ -74,7 +100,8 @@ def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, b
 
     fused_ok = (batch > 0 and int(split_k) >= 2 and k_pool.dtype == packed.dtype and packed.stride(1) == 1
                 and tuple(k_pool.shape[1:]) == (16, KV_HEADS, HEAD_DIM)
-                and k_pool.shape == v_pool.shape and block_table.ndim == 2 and block_table.shape[1] > 0)
+                and k_pool.shape == v_pool.shape and block_table.ndim == 2 and block_table.shape[1] > 0
+                and positions.dtype in (torch.int32, torch.int64))
     if not fused_ok:
         return pair()
     q_view = packed.as_strided((batch, Q_HEADS, HEAD_DIM), (packed.stride(0), HEAD_DIM, 1))
@@ -90,8 +117,13 @@ def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, b
     if cabi.fused_kernel_plan(args)[0] != "decode_mma_kernel":
         return pair()
     positions = positions.contiguous()
+    if rope_table is None:
+        rope_table = build_rope_table(block_table.shape[1] * 16, base=base, device=packed.device)
+    _require(rope_table.is_cuda and rope_table.dtype == torch.float32 and rope_table.is_contiguous()
+             and tuple(rope_table.shape[1:]) == (HEAD_DIM // 2, 2), "rope_table must come from build_rope_table")
     with cabi.device_of(packed):
         cabi.check(cabi.library().qf_packed_rope_decode_attention(
-            ctypes.byref(args), positions.data_ptr(), cabi.torch_index_code(positions.dtype, allow_float=True),
-            1, float(base), cabi.STAGE_PARTIAL | cabi.STAGE_COMBINE, cabi.stream_pointer(packed.device)))
+            ctypes.byref(args), positions.data_ptr(), cabi.torch_index_code(positions.dtype),
+            1, rope_table.data_ptr(), rope_table.shape[0], cabi.STAGE_PARTIAL | cabi.STAGE_COMBINE,
+            cabi.stream_pointer(packed.device)))
     return out

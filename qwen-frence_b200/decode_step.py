@@ -43,6 +43,11 @@ class DecodeStep:
         # layer instead of three) where the tensor-core kernel applies
         self.fused_write = bool(fused_write) and not self.fp8 and self.split_k > 1
         self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 or self.fused_write else 3)
+        self.rope_table = None
+        if self.fused_write:  # (cos, sin) of every position the block tables can hold
+            with torch.cuda.device(self.device):
+                self.rope_table = self.package.build_rope_table(
+                    workload.block_table.shape[1] * kv_layout.PAGE_SIZE, device=self.device)
 
         shape = (workload.num_pages, kv_layout.PAGE_SIZE, kv_layout.KV_HEADS, kv_layout.HEAD_DIM)
         pool_dtype = torch.uint8 if self.fp8 else dtype
@@ -153,7 +158,8 @@ class DecodeStep:
         elif self.fused_write:
             out = pkg.packed_qkv_rope_attention(
                 self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index],
-                self.block_table, self.seq_lens, split_k=self.split_k, partials=self.partials)
+                self.block_table, self.seq_lens, split_k=self.split_k, partials=self.partials,
+                rope_table=self.rope_table, require_fused=True)  # a silent fallback would miscount launches
         else:
             q = pkg.packed_qkv_rope_cache(
                 self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index])

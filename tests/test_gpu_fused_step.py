@@ -115,6 +115,19 @@ def test_metadata_types_graph_replay_and_fallbacks(package, cuda_device):
     torch.cuda.synchronize()
     assert torch.equal(out, want_out2) and torch.equal(k_pool, want_k2) and torch.equal(v_pool, want_v2)
 
+    # a position outside the table is clamped and recorded, never read out of bounds
+    small = package.build_rope_table(64, device=cuda_device)
+    package.packed_qkv_rope_attention(case["packed"], case["positions"], case["slots"], case["k_pool"].clone(),
+                                      case["v_pool"].clone(), case["table"], case["lens"], split_k=5,
+                                      rope_table=small, require_fused=True)
+    assert package.cabi.device_status() == 4
+    table = package.build_rope_table(4096, base=10_000.0, device=cuda_device)
+    positions = torch.arange(4096, dtype=torch.float32)
+    inv_freq = torch.tensor([float(f) for f in range(64)], dtype=torch.float32)
+    assert table.shape == (4096, 64, 2) and float(table[0, :, 0].min()) == 1.0 and float(table[0, :, 1].abs().max()) == 0.0
+    angle = positions[:, None].double() * torch.exp(inv_freq.double() * (-torch.log(torch.tensor(10_000.0)).double() / 64))
+    torch.testing.assert_close(table[..., 0].cpu().double(), torch.cos(angle), atol=2e-3, rtol=0)
+    del positions, inv_freq, angle
     single_out, single_k, _ = _fused(package, case, 1)
     want_single, want_single_k, _ = _pair(package, case, 1)
     assert torch.equal(single_out, want_single) and torch.equal(single_k, want_single_k)
