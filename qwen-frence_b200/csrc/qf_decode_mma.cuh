@@ -350,25 +350,38 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   int fill_page = 0, fill_stage = 0, fill_slot = 0;  // stage 0: Q, 1: K, 2: V
   // ROPE: the step's new token of `sequence` is row rows - 1 of page `id`: store it (K
   // rotated, V as it is) so that the copy of the page brings it along.
-  auto store_new_row = [&](int sequence, int id, int rows, int position) {
-    const int64_t row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
-                        kv_head * p.k_head_bytes;
+  struct NewRow {  // what one lane holds of a new token between its loads and its stores
+    float2 cs_lo, cs_hi;
+    float x1, x2, y1, y2;
+    uint4 v_bits;
+    int64_t row;  // byte offset of the pool row (the same in both pools)
+  };
+  auto load_new_row = [&](int sequence, int id, int rows, int position) {
+    NewRow r;
+    r.row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
+            kv_head * p.k_head_bytes;
     const unsigned char* row_in = rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes;
     const T* from = reinterpret_cast<const T*>(row_in + (12 + kv_head) * QF_HEAD_DIM * 2);
     const float2* cs = rope.table + static_cast<int64_t>(position) * (QF_HEAD_DIM / 2);
-    // every load first: one trip to memory for the whole row
-    const float2 cs_lo = cs[lane], cs_hi = cs[lane + 32];
-    const float x1 = to_float(from[lane]), x2 = to_float(from[lane + 64]);
-    const float y1 = to_float(from[lane + 32]), y2 = to_float(from[lane + 96]);
-    uint4 v_bits = make_uint4(0u, 0u, 0u, 0u);
-    if (lane < 16) v_bits = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2)[lane];
-    T* to = reinterpret_cast<T*>(const_cast<unsigned char*>(p.k_pool) + row);
-    to[lane] = from_float<T>(__fsub_rn(__fmul_rn(x1, cs_lo.x), __fmul_rn(x2, cs_lo.y)));
-    to[lane + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, cs_lo.x), __fmul_rn(x1, cs_lo.y)));
-    to[lane + 32] = from_float<T>(__fsub_rn(__fmul_rn(y1, cs_hi.x), __fmul_rn(y2, cs_hi.y)));
-    to[lane + 96] = from_float<T>(__fadd_rn(__fmul_rn(y2, cs_hi.x), __fmul_rn(y1, cs_hi.y)));
-    if (lane < 16) reinterpret_cast<uint4*>(const_cast<unsigned char*>(p.v_pool) + row)[lane] = v_bits;
+    // every load at once: one trip to memory for the whole row
+    r.cs_lo = cs[lane], r.cs_hi = cs[lane + 32];
+    r.x1 = to_float(from[lane]), r.x2 = to_float(from[lane + 64]);
+    r.y1 = to_float(from[lane + 32]), r.y2 = to_float(from[lane + 96]);
+    r.v_bits = make_uint4(0u, 0u, 0u, 0u);
+    if (lane < 16) r.v_bits = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2)[lane];
+    return r;
+  };
+  auto finish_new_row = [&](const NewRow& r) {
+    T* to = reinterpret_cast<T*>(const_cast<unsigned char*>(p.k_pool) + r.row);
+    to[lane] = from_float<T>(__fsub_rn(__fmul_rn(r.x1, r.cs_lo.x), __fmul_rn(r.x2, r.cs_lo.y)));
+    to[lane + 64] = from_float<T>(__fadd_rn(__fmul_rn(r.x2, r.cs_lo.x), __fmul_rn(r.x1, r.cs_lo.y)));
+    to[lane + 32] = from_float<T>(__fsub_rn(__fmul_rn(r.y1, r.cs_hi.x), __fmul_rn(r.y2, r.cs_hi.y)));
+    to[lane + 96] = from_float<T>(__fadd_rn(__fmul_rn(r.y2, r.cs_hi.x), __fmul_rn(r.y1, r.cs_hi.y)));
+    if (lane < 16) reinterpret_cast<uint4*>(const_cast<unsigned char*>(p.v_pool) + r.row)[lane] = r.v_bits;
     __syncwarp();  // the lanes' stores are ordered before the lanes' copies of the rows
+  };
+  auto store_new_row = [&](int sequence, int id, int rows, int position) {
+    finish_new_row(load_new_row(sequence, id, rows, position));
   };
   // New rows are stored when their units are described, 32 units at a time: those among the
   // warp's first 64 units up front (past its first four units in the shadow of the first
@@ -468,12 +481,27 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
   // newest K/V rows) and writes the partial buffers the previous combine read.
   dependency_wait();
-  if constexpr (ROPE) store_new_rows_of(id_now, rows_now, last_now, pos_now, 0xfu);
-#pragma unroll
-  for (int i = 0; i < kAhead; ++i) issue_tile();
   if constexpr (ROPE) {
-    store_new_rows_of(id_now, rows_now, last_now, pos_now, ~0xfu);
+    store_new_rows_of(id_now, rows_now, last_now, pos_now, 0xfu);
+    // The warp's next new row (usually its only one): its loads go out ahead of the first
+    // tiles' copies -- behind them they would queue after the whole GPU's opening burst --
+    // and it is stored once those copies are on their way.
+    const unsigned pending = __ballot_sync(kFull, last_now >= 0 && id_now >= 0);
+    NewRow early;
+    const int source = pending != 0 ? __ffs(pending) - 1 : -1;
+    if (source >= 0) {
+      early = load_new_row(__shfl_sync(kFull, last_now, source), __shfl_sync(kFull, id_now, source),
+                           __shfl_sync(kFull, rows_now, source), __shfl_sync(kFull, pos_now, source));
+      if (lane == source) last_now = -1;
+    }
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) issue_tile();
+    if (source >= 0) finish_new_row(early);
+    store_new_rows_of(id_now, rows_now, last_now, pos_now, kFull);
     store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) issue_tile();
   }
 
   // ---- fragments ----
