@@ -25,6 +25,8 @@ from . import kv_layout
 
 
 class DecodeStep:
+    FUSED_WRITE_MAX_BATCH = 128
+
     def __init__(self, workload, device, *, split_k=None, dtype=torch.float16,
                  fill_pools=True, package=None, fused_write=False):
         import sys
@@ -41,7 +43,10 @@ class DecodeStep:
             sm_count=torch.cuda.get_device_properties(self.device).multi_processor_count)
         # fused_write: RoPE + KV write inside the attention partial pass (two launches per
         # layer instead of three) where the tensor-core kernel applies
-        self.fused_write = bool(fused_write) and not self.fp8 and self.split_k > 1
+        # (up to FUSED_WRITE_MAX_BATCH sequences: every sequence costs one warp per KV head a
+        # round trip to memory for the new row, and beyond that the launch saved no longer pays)
+        self.fused_write = (bool(fused_write) and not self.fp8 and self.split_k > 1
+                            and (fused_write == "always" or self.batch <= self.FUSED_WRITE_MAX_BATCH))
         self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 or self.fused_write else 3)
         self.rope_table = None
         if self.fused_write:  # (cos, sin) of every position the block tables can hold

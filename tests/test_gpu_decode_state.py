@@ -87,17 +87,19 @@ def test_advance_beyond_the_table_is_flagged_and_harmless(package, cuda_device):
     package.cabi.device_status()  # the skipped row is recorded too; leave the word clean
 
 
-@pytest.mark.parametrize("fp8", [False, True])
-def test_unrolled_steps_equal_host_driven_steps(package, cuda_device, fp8):
+@pytest.mark.parametrize("fp8,fused", [(False, False), (True, False), (False, True)])
+def test_unrolled_steps_equal_host_driven_steps(package, cuda_device, fp8, fused):
     """Twenty decode steps (every sequence crosses a page boundary) as ONE graph with the
     metadata advanced on the device, against twenty eager steps whose metadata the host
     builds and copies in, fully ordered launches: same pools, same outputs, same final
-    metadata, bit for bit; a replay from restored state repeats it."""
+    metadata, bit for bit; a replay from restored state repeats it.  Also with the two-launch
+    layer step, whose partial pass reads the advanced positions."""
     steps = 20
     name = "fp8_b128" if fp8 else "decode_b64"
     workload = package.workloads.build_workload(name, batch=12, layers=2, reserve_tokens=steps)
     layout = package.kv_layout
-    make = lambda: package.decode_step.DecodeStep(workload, cuda_device, split_k=4, package=package)
+    make = lambda fused_write=False: package.decode_step.DecodeStep(
+        workload, cuda_device, split_k=4, package=package, fused_write=fused_write)
 
     host_driven = make()
     host_driven.load_packed_rows()
@@ -116,7 +118,7 @@ def test_unrolled_steps_equal_host_driven_steps(package, cuda_device, fp8):
     finally:
         package.cabi.set_dependent_launch(True)
 
-    unrolled = make()
+    unrolled = make(fused)  # fused: the RoPE + KV write inside the partial pass, positions advanced on the device
     unrolled.load_packed_rows()
     pristine = [pool.clone() for pool in unrolled.k_pools + unrolled.v_pools]
     unrolled.capture_steps(steps)
