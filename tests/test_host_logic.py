@@ -84,6 +84,14 @@ def test_c_side_validation_without_a_gpu(package):
     assert lib.qf_rms_norm(None, 8, None, None, 8, 4, 0, 0, 1e-6, None) == -1 and b"hidden" in lib.qf_last_error()
     assert lib.qf_residual_add_rms_norm(None, 8, None, 8, None, None, 8, None, 8, 4, 8, 1, 1e-6, None) == -1
     assert b"must not be null" in lib.qf_last_error()
+    assert lib.qf_build_rope_table(None, 0, 1e6, None) == 0          # no positions: nothing launched
+    assert lib.qf_build_rope_table(None, 8, 1e6, None) == -1 and b"aligned" in lib.qf_last_error()
+    step_args = cabi.DecodeAttentionArgs()
+    step_args.batch, step_args.q_heads, step_args.kv_heads, step_args.head_dim, step_args.page_size = 2, 12, 2, 128, 16
+    step_args.split_k = 4
+    assert lib.qf_packed_rope_decode_attention(ctypes.byref(step_args), None, 0, 1, None, 0, 3, None) == -1
+    assert lib.qf_packed_rope_decode_attention(ctypes.byref(step_args), None, 0, 1, None, 0, 9, None) == -1
+    assert b"stages" in lib.qf_last_error()
     gemm = cabi.QkvRopeCacheArgs()
     gemm.rows, gemm.in_features, gemm.dtype = 4, 1500, 0
     assert lib.qf_qkv_rope_cache(ctypes.byref(gemm), None) == -1 and b"multiple of 64" in lib.qf_last_error()
