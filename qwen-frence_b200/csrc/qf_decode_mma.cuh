@@ -384,8 +384,8 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     finish_new_row(load_new_row(sequence, id, rows, position));
   };
   // New rows are stored when their units are described, 32 units at a time: those among the
-  // warp's first 64 units up front (past its first four units in the shadow of the first
-  // tiles' latency: the first four tiles touch at most the first four units), later ones
+  // warp's first 64 units up front (past its first two pages in the shadow of the first
+  // tiles' latency), later ones
   // when the descriptors are refreshed.  Stored from inside the page loop, next to the copy
   // of its page, a row cost its warp the contents of its ring (a third of the kernel's time).
   auto store_new_rows_of = [&](int& id_of, int& rows_of, int& last_of, int& pos_of, unsigned lanes) {
@@ -482,7 +482,11 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   // newest K/V rows) and writes the partial buffers the previous combine read.
   dependency_wait();
   if constexpr (ROPE) {
-    store_new_rows_of(id_now, rows_now, last_now, pos_now, 0xfu);
+    // the first four tiles (Q K V of a page, then Q or K of the next) touch the warp's first
+    // two units that are pages: only their new rows have to be in place before any copy
+    unsigned first_two = __ballot_sync(kFull, id_now != -3);
+    first_two &= ~((first_two & (first_two - 1)) & ((first_two & (first_two - 1)) - 1));
+    store_new_rows_of(id_now, rows_now, last_now, pos_now, first_two);
     // The warp's next new row (usually its only one): its loads go out ahead of the first
     // tiles' copies -- behind them they would queue after the whole GPU's opening burst --
     // and it is stored once those copies are on their way.
