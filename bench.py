@@ -372,7 +372,8 @@ def run_layer_glue(args):
     chained_replays = 3
     workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=args.layers or None,
                                                 reserve_tokens=steps * (chained_replays + 1))
-    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
+    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package,
+                                          fused_write=not args.unfused_write)
     step.load_packed_rows()
     step.capture(warmup=2)
     step.capture_steps(steps)
@@ -447,6 +448,7 @@ def run_layer_glue(args):
         "layer_front_norm_projection_attention": front,
         "unrolled_decode_steps": {
             "workload": args.workload, "steps_per_graph": steps, "batch": workload.batch,
+            "fused_write": step.fused_write,
             "ms_per_step_single_step_graph": single_ms, "ms_per_step_unrolled_graph": unrolled_ms,
             "tokens_per_s_unrolled": workload.batch / (unrolled_ms * 1e-3),
             "h2d_bytes_per_step": 0, "kernel_launches_per_graph": steps * (step.kernel_launches_per_step + 1),
