@@ -295,12 +295,12 @@ class DecodeStep:
         main = torch.cuda.Stream(self.device)
         copier = torch.cuda.Stream(self.device)
 
-        # Rows travel in a few copies of growing size (1, 2, 4, ... layers): the first one
+        # Rows travel in a few copies of growing size (1, 3, 9, ... layers): the first one
         # is short, so the first layer starts early, and there are few cross-stream
         # dependencies, each of which costs the waiting kernel its early start.
         chunks, first = [], 0
         while first < self.layers:
-            size = min(max(1, len(chunks) and 2 * chunks[-1][1]), self.layers - first)
+            size = min(max(1, len(chunks) and 3 * chunks[-1][1]), self.layers - first)
             chunks.append((first, size))
             first += size
 
