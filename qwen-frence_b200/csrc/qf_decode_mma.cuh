@@ -327,7 +327,15 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
       // ROPE: the page that takes the step's new token (the last token of the sequence)
-      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
+      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) {
+        // (not when the length was cut to the table's capacity: the token's slot is then
+        // outside the table, and nothing is written for it)
+        if (load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) == work.length[sequence]) {
+          last_of = sequence;
+        } else {
+          atomicExch(p.status, kStatusPositionPastTable);
+        }
+      }
       // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
       if (ROPE) {
         const int64_t at = load_index(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);

@@ -128,6 +128,21 @@ def test_metadata_types_graph_replay_and_fallbacks(package, cuda_device):
     angle = positions[:, None].double() * torch.exp(inv_freq.double() * (-torch.log(torch.tensor(10_000.0)).double() / 64))
     torch.testing.assert_close(table[..., 0].cpu().double(), torch.cos(angle), atol=2e-3, rtol=0)
     del positions, inv_freq, angle
+    # a sequence length beyond what its table row can hold: attended up to the table's end as
+    # in the plain kernels, its new token (whose slot lies outside the table) is not written
+    narrow = dict(case, table=case["table"][:, :3].contiguous())  # 48 tokens per row
+    k_cut, v_cut = case["k_pool"].clone(), case["v_pool"].clone()
+    package.packed_qkv_rope_attention(narrow["packed"], narrow["positions"], narrow["slots"], k_cut, v_cut,
+                                      narrow["table"], narrow["lens"], split_k=5, require_fused=True)
+    assert package.cabi.device_status() == 4
+    fits = [b for b, n in enumerate(lengths) if n <= 48]
+    cut = [b for b, n in enumerate(lengths) if n > 48]
+    flat_k, want_flat_k = k_cut.view(-1, 2, 128), want_k.view(-1, 2, 128)
+    assert torch.equal(flat_k[case["slots"][fits]], want_flat_k[case["slots"][fits]])
+    untouched = torch.ones(flat_k.shape[0], dtype=torch.bool, device=cuda_device)
+    untouched[case["slots"][fits]] = False
+    assert torch.equal(flat_k[untouched].view(torch.int16), case["k_pool"].view(-1, 2, 128)[untouched].view(torch.int16))
+    assert len(cut) == 3
     single_out, single_k, _ = _fused(package, case, 1)
     want_single, want_single_k, _ = _pair(package, case, 1)
     assert torch.equal(single_out, want_single) and torch.equal(single_k, want_single_k)
