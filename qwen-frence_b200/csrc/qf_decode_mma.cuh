@@ -327,15 +327,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
       // ROPE: the page that takes the step's new token (the last token of the sequence)
-      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) {
-        // (not when the length was cut to the table's capacity: the token's slot is then
-        // outside the table, and nothing is written for it)
-        if (load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) == work.length[sequence]) {
-          last_of = sequence;
-        } else {
-          atomicExch(p.status, kStatusPositionPastTable);
-        }
-      }
+      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
       // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
       if (ROPE) {
         const int64_t at = load_index(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
@@ -363,9 +355,16 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     float x1, x2, y1, y2;
     uint4 v_bits;
     int64_t row;  // byte offset of the pool row (the same in both pools)
+    bool write;   // false: the sequence's length was cut to the table's capacity
   };
   auto load_new_row = [&](int sequence, int id, int rows, int position) {
     NewRow r;
+    // Not when the length was cut to the table's capacity: the token's slot is then outside
+    // the table, and nothing is written for it.  Only a length equal to the capacity can have
+    // been cut, and only then is the given length looked at again.
+    r.write = work.length[sequence] < p.max_tokens ||
+              load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) == work.length[sequence];
+    if (!r.write && lane == 0) atomicExch(p.status, kStatusPositionPastTable);
     r.row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
             kv_head * p.k_head_bytes;
     const unsigned char* row_in = rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes;
@@ -380,6 +379,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     return r;
   };
   auto finish_new_row = [&](const NewRow& r) {
+    if (!r.write) return;  // the same for every lane
     T* to = reinterpret_cast<T*>(const_cast<unsigned char*>(p.k_pool) + r.row);
     to[lane] = from_float<T>(__fsub_rn(__fmul_rn(r.x1, r.cs_lo.x), __fmul_rn(r.x2, r.cs_lo.y)));
     to[lane + 64] = from_float<T>(__fadd_rn(__fmul_rn(r.x2, r.cs_lo.x), __fmul_rn(r.x1, r.cs_lo.y)));
