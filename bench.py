@@ -565,11 +565,17 @@ def main():
 
         kernel_name, ctas_per_head = cabi.fused_kernel_plan(arg_sets[0])
 
-        def launch_partials():
+        plain_sets = arg_sets
+        if step.fused_write:  # the same pass without the write, on rotated queries, for comparison
+            plain_sets = [splitk.fill_attention_args(
+                cabi, q, step.k_pools[layer], step.v_pools[layer], step.block_table, step.seq_lens,
+                split_k=step.split_k, scale=128 ** -0.5, partials=partials, out=out) for layer in range(step.layers)]
+
+        def launch_partials(with_write=True):
             # the partial pass of the fused attention call, without its combine
             stream = cabi.stream_pointer(device)
-            for arg in arg_sets:
-                if step.fused_write:
+            for arg in (arg_sets if with_write else plain_sets):
+                if step.fused_write and with_write:
                     cabi.check(lib.qf_packed_rope_decode_attention(
                         ctypes.byref(arg), step.positions.data_ptr(), cabi.torch_index_code(step.positions.dtype),
                         1, step.rope_table.data_ptr(), step.rope_table.shape[0], cabi.STAGE_PARTIAL, stream))
@@ -577,21 +583,30 @@ def main():
                     cabi.check(lib.qf_grouped_splitk_decode_attention_stages(
                         ctypes.byref(arg), cabi.STAGE_PARTIAL, stream))
 
-        side = torch.cuda.Stream(device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            launch_partials()
-        side.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            launch_partials()
-        torch.cuda.current_stream(device).wait_stream(side)
-        for _ in range(3):
-            graph.replay()
-        kernel_ms = timed(graph.replay, args.steps) / args.steps / step.layers
+        def per_launch_ms(with_write):
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                launch_partials(with_write)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                launch_partials(with_write)
+            torch.cuda.current_stream(device).wait_stream(side)
+            for _ in range(3):
+                graph.replay()
+            return timed(graph.replay, args.steps) / args.steps / step.layers
+
+        kernel_ms = per_launch_ms(True)
         peak, peak_kind = measured_peak_gbs()
         launch_bytes = partial_kernel_bytes(package, workload, step.split_k, step.fp8, kernel_name,
                                             ctas_per_head)
+        without_write = None
+        if step.fused_write:
+            plain_ms = per_launch_ms(False)
+            without_write = {"us_per_launch": plain_ms * 1e3, "algorithmic_bytes_per_launch": launch_bytes,
+                             "achieved": launch_bytes / (plain_ms * 1e-3) / 1e9,
+                             "frac": launch_bytes / (plain_ms * 1e-3) / 1e9 / peak}
         if step.fused_write:
             # instead of rotated Q (12 x 128 x 2 B, already counted): the packed row (2048 x 2 B), a position
             # and its 512 B of the rotation table are read, the new K and V rows (2 x 2 x 128 x 2 B) written
@@ -605,6 +620,7 @@ def main():
                 (args.workload, args.seed, kernel_name + ("+rope" if step.fused_write else "")))
             if world == 1 and step.split_k == 10 else None,  # the captured launch used split_k 10
             "fused_write": step.fused_write,
+            "same_pass_without_the_write": without_write,
             "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,
             "kv_bytes_per_launch": package.kv_layout.kv_bytes_per_layer(
                 workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2),
