@@ -578,19 +578,18 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       issue_tile();
       if constexpr (ROPE) {
         // the tile holds the six unrotated query heads of the group: rotate them in place,
-        // each lane its two frequencies of every head
+        // each lane the frequencies 2 lane and 2 lane + 1 of every head (one 32-bit word of
+        // each half of a head; their cos / sin are the 16 bytes this lane copied)
+        unsigned char* tile = ring + read_slot * Ring::kSlotBytes;
+        const float4 cs = reinterpret_cast<const float4*>(tile + kQTileBytes)[lane];  // c0 s0 c1 s1
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int f = lane + 32 * half;
-          const float2 cs = reinterpret_cast<const float2*>(ring + read_slot * Ring::kSlotBytes + kQTileBytes)[f];
-          const float c = cs.x, sn = cs.y;
-#pragma unroll
-          for (int head = 0; head < QF_GQA_GROUP; ++head) {
-            T* row = reinterpret_cast<T*>(ring + read_slot * Ring::kSlotBytes + head * kQRowBytes);
-            const float x1 = to_float(row[f]), x2 = to_float(row[f + 64]);
-            row[f] = from_float<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
-            row[f + 64] = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
-          }
+        for (int head = 0; head < QF_GQA_GROUP; ++head) {
+          uint32_t* row = reinterpret_cast<uint32_t*>(tile + head * kQRowBytes);
+          const float2 x1 = unpack2<T>(row[lane]), x2 = unpack2<T>(row[lane + 32]);
+          row[lane] = pack2<T>(__fsub_rn(__fmul_rn(x1.x, cs.x), __fmul_rn(x2.x, cs.y)),
+                               __fsub_rn(__fmul_rn(x1.y, cs.z), __fmul_rn(x2.y, cs.w)));
+          row[lane + 32] = pack2<T>(__fadd_rn(__fmul_rn(x2.x, cs.x), __fmul_rn(x1.x, cs.y)),
+                                    __fadd_rn(__fmul_rn(x2.y, cs.z), __fmul_rn(x1.y, cs.w)));
         }
         __syncwarp();
       }
