@@ -339,6 +339,89 @@ __global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReducePa
   }
 }
 
+// Combine for 32 < split_k <= 256 (few long sequences cut into many pieces): the small
+// kernel's scheme with up to eight slots per lane.  Every warp reads all statistics in one
+// trip (lane l holds slots l, l + 32, ...), finds the filled slots, the top offset, the
+// weights and the total with shuffles; warp 0 leaves the weights in shared memory (the one
+// block barrier), and each thread then sums its head dimension over the filled slots
+// sixteen independent loads at a time.  Chained to the partial pass like the small kernel.
+constexpr int kMediumReduceSlots = 256;
+constexpr int kMediumSlotsPerLane = kMediumReduceSlots / 32;
+
+template <typename T, bool STREAMED>
+__global__ void __launch_bounds__(256) splitk_reduce_medium_kernel(const ReduceParams p) {
+  constexpr unsigned kFull = 0xffffffffu;
+  __shared__ float s_weight[kMediumReduceSlots];
+  release_dependents();
+  dependency_wait();  // the partials come from the kernel before this one
+  const int sequence = blockIdx.x / p.q_heads;
+  const int head = blockIdx.x - sequence * p.q_heads;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const float* pm = p.pm + sequence * p.pm_sb + head * p.pm_sh;
+  const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
+  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + tid * p.po_sd;
+  T* out = static_cast<T*>(p.out) + sequence * p.o_sb + head * p.o_sh + tid * p.o_sd;
+
+  int64_t length = 1;
+  if (STREAMED) length = min(load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride), p.max_tokens);
+  float sum[kMediumSlotsPerLane], offset[kMediumSlotsPerLane];
+#pragma unroll
+  for (int j = 0; j < kMediumSlotsPerLane; ++j) {
+    const int k = lane + 32 * j;
+    sum[j] = 0.f, offset[j] = -INFINITY;
+    if (k < p.split_k) sum[j] = ps[k * p.pm_sk], offset[j] = pm[k * p.pm_sk];
+  }
+  if (STREAMED && length <= 0) {
+    if (tid < p.head_dim) *out = from_float<T>(0.f);  // no tokens: no slot was written
+    return;
+  }
+  int filled = p.split_k;
+  if (STREAMED) {
+    // the slot after a sequence's last piece carries sum = -1
+#pragma unroll
+    for (int j = kMediumSlotsPerLane - 1; j >= 0; --j) {
+      const unsigned marks = __ballot_sync(kFull, lane + 32 * j < p.split_k && sum[j] < 0.f);
+      if (marks != 0) filled = 32 * j + __ffs(marks) - 1;
+    }
+  }
+  float top = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMediumSlotsPerLane; ++j) {
+    if (lane + 32 * j < filled && sum[j] > 0.f) top = fmaxf(top, offset[j]);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
+  float total = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMediumSlotsPerLane; ++j) {
+    const bool used = lane + 32 * j < filled && sum[j] > 0.f;
+    const float weight = used ? expf(offset[j] - top) : 0.f;
+    if (used) total += sum[j] * weight;
+    if (tid < 32) s_weight[lane + 32 * j] = weight;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(kFull, total, off);
+  __syncthreads();
+
+  if (tid < p.head_dim) {
+    float acc = 0.f;
+    for (int first = 0; first < filled; first += 16) {
+      float part[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int k = first + i;
+        part[i] = (k < filled && s_weight[k] != 0.f) ? po[k * p.po_sk] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int k = first + i;
+        if (k < filled && s_weight[k] != 0.f) acc += part[i] * s_weight[k];
+      }
+    }
+    *out = from_float<T>(acc / (total > 0.f ? total : 1.f));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -397,7 +480,7 @@ int launch_stream(const FastParams& p, cudaStream_t stream) {
                                static_cast<int>(smem)));
   const int resident = stream_ctas_on_current_device();
   QF_REQUIRE(resident >= p.kv_heads, "could not size the streamed kernel for this device");
-  StreamParams sp{p, resident / p.kv_heads};
+  StreamParams sp{p, resident / p.kv_heads, 0};
   kernel<<<static_cast<unsigned>(sp.ctas_per_head * p.kv_heads), kFastThreads, smem, stream>>>(sp);
   QF_CUDA(cudaGetLastError());
   return QF_OK;
@@ -423,7 +506,11 @@ int launch_mma(const FastParams& p, cudaStream_t stream, const RopeInputs& rope 
                                static_cast<int>(smem)));
   const int resident = mma_ctas_on_current_device(FP8);
   QF_REQUIRE(resident >= p.kv_heads, "could not size the tensor-core kernel for this device");
-  StreamParams sp{p, resident / p.kv_heads};
+  // The fused step is a decode step by contract: one new token per sequence, stored by this
+  // very kernel, and every older K / V row written before the step began.  Its kernel may
+  // therefore request tiles of the older pages before its dependency wait.  The plain
+  // attention call makes no such promise about the kernel in front of it.
+  StreamParams sp{p, resident / p.kv_heads, ROPE ? 1 : 0};
   QF_CUDA(launch_chained(kernel, dim3(static_cast<unsigned>(sp.ctas_per_head * p.kv_heads)),
                          dim3(kFastThreads), smem, stream, sp, rope));
   QF_CUDA(cudaGetLastError());
@@ -544,7 +631,8 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   const bool same_strides = a->k_stride_page == a->v_stride_page && a->k_stride_tok == a->v_stride_tok &&
                             a->k_stride_head == a->v_stride_head &&
                             a->k_stride_tok * (a->kv_fp8 ? 1 : 2) * QF_PAGE_SIZE < (1LL << 31);
-  const bool tensor_core = mode != 3 && same_strides;
+  // ... and stores a piece's partial rows as 16-byte vectors
+  const bool tensor_core = mode != 3 && same_strides && aligned16(a->partial_out);
   if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
   if (!tensor_core && mode == 0) return FusedKernel::kPartitioned;  // pools with different strides
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
@@ -631,7 +719,12 @@ void launch_reduce_typed(const ReduceParams& r, unsigned blocks, int threads, bo
                          cudaStream_t stream) {
   // head_dim is a multiple of 32 on this path, so whole warps take part in the shuffles
   const bool small = r.split_k <= kSmallReduceSlots && (r.head_dim & 31) == 0;
-  if (small && streamed) {
+  const bool medium = !small && r.split_k <= kMediumReduceSlots && (r.head_dim & 31) == 0;
+  if (medium && streamed) {
+    (void)launch_chained(splitk_reduce_medium_kernel<T, true>, dim3(blocks), dim3(threads), 0, stream, r);
+  } else if (medium) {
+    (void)launch_chained(splitk_reduce_medium_kernel<T, false>, dim3(blocks), dim3(threads), 0, stream, r);
+  } else if (small && streamed) {
     (void)launch_chained(splitk_reduce_small_kernel<T, true>, dim3(blocks), dim3(threads), 0, stream, r);
   } else if (small) {
     (void)launch_chained(splitk_reduce_small_kernel<T, false>, dim3(blocks), dim3(threads), 0, stream, r);
@@ -911,6 +1004,10 @@ extern "C" int qf_grouped_splitk_decode_attention_static(const qf_decode_attenti
   QF_REQUIRE(args != nullptr, "args must not be null");
   QF_REQUIRE(args->batch >= 0 && args->split_k >= 1 && args->q_heads >= 1 && args->head_dim >= 1,
              "invalid batch, split or head counts");
+  // the factors are bounded one by one, so that the byte count below cannot wrap
+  QF_REQUIRE(args->split_k <= 65535 && args->head_dim <= 256, "split_k must be <= 65535 and head_dim <= 256");
+  QF_REQUIRE(static_cast<long long>(args->batch) * args->q_heads < (1LL << 31),
+             "batch * q_heads exceeds the grid limit");
   const unsigned long long rows = static_cast<unsigned long long>(args->batch) *
                                   static_cast<unsigned long long>(args->split_k) *
                                   static_cast<unsigned long long>(args->q_heads);

@@ -326,8 +326,9 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
                                           : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
       id = static_cast<uint64_t>(raw) < static_cast<uint64_t>(pool_pages) ? static_cast<int>(raw) : -2;
       rows = min(QF_PAGE_SIZE, work.length[sequence] - in_sequence * QF_PAGE_SIZE);
-      // ROPE: the page that takes the step's new token (the last token of the sequence)
-      if (ROPE && in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
+      // the page that takes the step's new token (the last token of the sequence): ROPE stores
+      // that token's row itself; no variant copies this page before the dependency wait
+      if (in_sequence == (work.length[sequence] - 1) / QF_PAGE_SIZE) last_of = sequence;
       // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
       if (ROPE) {
         const int64_t at = load_index(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
@@ -406,10 +407,32 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       if (lane == source) last_of = -1;
     }
   };
-  auto issue_tile = [&]() {
+  // The Q rows of sequence `q_of` (and, ROPE, its position's cos / sin) into ring slot `dst`.
+  auto copy_q_tile = [&](unsigned char* dst, int q_of, int position) {
+    // 6 heads x 256 bytes = 96 chunks: three per lane
+    const unsigned char* src = q_base + static_cast<int64_t>(q_of) * p.q_sb * 2;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int chunk = lane + 32 * j, head = chunk >> 4, c = chunk & 15;
+      copy_chunk_async<false>(dst + head * kQRowBytes + c * 16, src + head * p.q_sh * 2 + c * 16);
+    }
+    if constexpr (ROPE) {
+      // the position's (cos, sin) of all 64 frequencies ride behind the tile: 32 chunks
+      copy_chunk_async<false>(dst + kQTileBytes + lane * 16,
+                              reinterpret_cast<const unsigned char*>(
+                                  rope.table + static_cast<int64_t>(position) * (QF_HEAD_DIM / 2)) + lane * 16);
+    }
+  };
+  // early: called before the dependency wait.  Only tiles of pages that no kernel of this
+  // step writes may be copied then: K and V of pages that do not hold a sequence's newest
+  // token.  The warp's first Q tile (ring slot 0) is left for later (`deferred_q`); the call
+  // returns false, without having issued anything, at the first tile that has to wait.
+  int deferred_q = -1, deferred_pos = 0;
+  auto issue_tile = [&](bool early = false) -> bool {
     int id = -3;
     while (fill_page < my_pages) {
       if (fill_stage == 0 && (fill_page & 31) == 0 && fill_page > 0) {
+        if (early) return false;
         id_now = id_next, rows_now = rows_next, q_now = q_next, last_now = last_next, pos_now = pos_next;
         describe((fill_page >> 5) + 1, id_next, rows_next, q_next, last_next, pos_next);
         // ROPE: the new rows of the 32 units just described, well before their pages are copied
@@ -419,26 +442,22 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       if (id != -3) break;
       ++fill_page;  // an empty unit (only met at stage 0): nothing to load
     }
+    if (early && fill_page >= my_pages) return false;
     if (fill_page < my_pages) {
       int rows = __shfl_sync(kFull, rows_now, fill_page & 31);
       const int q_of = __shfl_sync(kFull, q_now, fill_page & 31);
       if (fill_stage == 0 && q_of < 0) fill_stage = 1;
+      if (early) {
+        if (fill_stage == 0) {
+          if (fill_slot != 0 || deferred_q >= 0) return false;  // a later sequence's Q rows
+          deferred_q = q_of, deferred_pos = __shfl_sync(kFull, pos_now, fill_page & 31);
+          fill_stage = 1, fill_slot = 1;  // slot 0 is filled after the wait
+        }
+        if (id < 0 || __shfl_sync(kFull, last_now, fill_page & 31) >= 0) return false;
+      }
       unsigned char* dst = ring + fill_slot * Ring::kSlotBytes;
       if (fill_stage == 0) {
-        // 6 heads x 256 bytes = 96 chunks: three per lane
-        const unsigned char* src = q_base + static_cast<int64_t>(q_of) * p.q_sb * 2;
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-          const int chunk = lane + 32 * j, head = chunk >> 4, c = chunk & 15;
-          copy_chunk_async<false>(dst + head * kQRowBytes + c * 16, src + head * p.q_sh * 2 + c * 16);
-        }
-        if constexpr (ROPE) {
-          // the position's (cos, sin) of all 64 frequencies ride behind the tile: 32 chunks
-          const int position = __shfl_sync(kFull, pos_now, fill_page & 31);
-          copy_chunk_async<false>(dst + kQTileBytes + lane * 16,
-                                  reinterpret_cast<const unsigned char*>(
-                                      rope.table + static_cast<int64_t>(position) * (QF_HEAD_DIM / 2)) + lane * 16);
-        }
+        copy_q_tile(dst, q_of, ROPE ? __shfl_sync(kFull, pos_now, fill_page & 31) : 0);
       } else {
         if (id < 0) {
           rows = 0;  // bad or missing id: the page reads as zeros
@@ -485,10 +504,29 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     }
     commit_copies();  // always, so that group counting stays uniform
     fill_slot = fill_slot == Ring::kSlots - 1 ? 0 : fill_slot + 1;
+    return true;
   };
+  // Before the wait: up to kAhead - 1 K / V tiles of pages that nothing in flight can write
+  // (the caller's promise, see StreamParams::early_tiles) start their trip to shared memory
+  // while the kernels before this one drain.
+  int issued = 0;
+  if (sp.early_tiles) {
+#pragma unroll 1
+    while (issued < kAhead - 1 && issue_tile(true)) ++issued;
+  }
+  bool first_tiles_out_of_order = issued > 0;  // groups: early tiles first, then the Q tile
   // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
   // newest K/V rows) and writes the partial buffers the previous combine read.
   dependency_wait();
+  auto issue_first_tiles = [&]() {
+    if (deferred_q >= 0) {
+      copy_q_tile(ring, deferred_q, deferred_pos);
+      commit_copies();
+      ++issued;
+    }
+#pragma unroll 1
+    for (; issued < kAhead; ++issued) issue_tile();
+  };
   if constexpr (ROPE) {
     // the first four tiles (Q K V of a page, then Q or K of the next) touch the warp's first
     // two units that are pages: only their new rows have to be in place before any copy
@@ -506,14 +544,12 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
                            __shfl_sync(kFull, rows_now, source), __shfl_sync(kFull, pos_now, source));
       if (lane == source) last_now = -1;
     }
-#pragma unroll
-    for (int i = 0; i < kAhead; ++i) issue_tile();
+    issue_first_tiles();
     if (source >= 0) finish_new_row(early);
     store_new_rows_of(id_now, rows_now, last_now, pos_now, kFull);
     store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
   } else {
-#pragma unroll
-    for (int i = 0; i < kAhead; ++i) issue_tile();
+    issue_first_tiles();
   }
 
   // ---- fragments ----
@@ -572,7 +608,12 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     }
     {
       // ---- the piece's Q tile ----
-      wait_tiles_ahead<kAhead>();
+      if (first_tiles_out_of_order) {
+        wait_all_copies();  // the warp's first Q tile was issued behind the early tiles
+        first_tiles_out_of_order = false;
+      } else {
+        wait_tiles_ahead<kAhead>();
+      }
       __syncwarp();
       if (PROFILE && t_first == 0) t_first = global_nanoseconds();
       issue_tile();

@@ -45,6 +45,11 @@ constexpr int kMaxStreamLen = 0x7fffff00;                        // keeps (len +
 struct StreamParams {
   FastParams f;
   int ctas_per_head;  // resident CTAs that share one KV head's pair list
+  // Tensor-core kernel only.  Nonzero: the caller promises that, of the pages this launch
+  // reads, only each sequence's last one (the page of its newest token) can be written by a
+  // kernel still in flight when this one starts; K / V tiles of the other pages may then be
+  // requested before the dependency wait.
+  int early_tiles;
 };
 
 // The launch-wide work list in shared memory: sequences in units of

@@ -126,7 +126,7 @@ class DecodeStep:
         read); FP8 pools are quantised page by page with the library's quantiser."""
         w = self.workload
         live = w.live_pages.to(self.device)
-        generator = torch.Generator(device=self.device).manual_seed(4000 + w.seed)
+        generator = torch.Generator(device=self.device).manual_seed(4000 + w.value_seed)
         chunk = 4096
         for layer in range(self.layers):
             for pool, scales in ((self.k_pools[layer], self.k_scales), (self.v_pools[layer], self.v_scales)):

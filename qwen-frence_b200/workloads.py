@@ -74,6 +74,11 @@ class Workload:
     meta: dict = field(default_factory=dict)
 
     @property
+    def value_seed(self):
+        """Seed of the K/V and packed-row values: differs between ranks."""
+        return self.seed + 7919 * int(self.meta.get("rank", 0))
+
+    @property
     def batch(self):
         return len(self.contexts)
 
@@ -86,8 +91,9 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
                    batch=None, pool_pages=None, shard_policy="snake", reserve_tokens=0):
     """Build rank `rank`'s share of workload `name`.
 
-    scaling "weak": every rank gets its own full-size batch (different seed per
-    rank).  scaling "strong": the global batch is partitioned by sequence with
+    scaling "weak": every rank gets its own full-size batch with the SAME context
+    lengths in the same order (equal cost per rank, so a scaling curve measures the
+    machine and not the draw) but its own page permutation and values.  scaling "strong": the global batch is partitioned by sequence with
     `sharding.partition_sequences`; each rank owns its sequences' pages.
     Page ids are local to the rank.  The pool is filled through a PagePool whose
     free list is randomly permuted first, so block tables are a seeded random
@@ -99,7 +105,7 @@ def build_workload(name, *, rank=0, world_size=1, scaling="weak", seed=0, layers
     spec = WORKLOADS[name]
     layers = spec["layers"] if layers is None else layers
     if scaling == "weak":
-        contexts = context_lengths(name, seed=seed + 7919 * rank, batch=batch)
+        contexts = context_lengths(name, seed=seed, batch=batch)
         global_indices = [rank * len(contexts) + i for i in range(len(contexts))]
     elif scaling == "strong":
         everyone = context_lengths(name, seed=seed, batch=batch)
@@ -163,7 +169,7 @@ def packed_qkv_rows(workload, layer, device, dtype=torch.float16):
     through a random [2048, 1536] * 0.02 projection with bias, as in the
     reference's fusion benchmark (experiments/model/... random-weight geometry;
     no checkpoint is available offline).  Setup work, never timed."""
-    generator = torch.Generator(device="cpu").manual_seed(3000 + workload.seed * 131 + layer)
+    generator = torch.Generator(device="cpu").manual_seed(3000 + workload.value_seed * 131 + layer)
     hidden = torch.randn(workload.batch, kv_layout.HIDDEN, generator=generator)
     weight = torch.randn(2048, kv_layout.HIDDEN, generator=generator) * 0.02
     bias = torch.randn(2048, generator=generator) * 0.1

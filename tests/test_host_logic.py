@@ -273,7 +273,9 @@ def test_workloads_have_the_configured_shapes(package):
     assert 128 <= min(w.contexts) and max(w.contexts) <= 4096
     w2 = build("decode_b64")
     assert w2.contexts == w.contexts and torch.equal(w2.block_table, w.block_table)  # seeded
-    assert build("decode_b64", rank=1, world_size=2).contexts != w.contexts          # weak: own batch
+    other = build("decode_b64", rank=1, world_size=2)  # weak: the same lengths (equal cost), its own pages and values
+    assert other.contexts == w.contexts and not torch.equal(other.block_table, w.block_table)
+    assert other.value_seed != w.value_seed
 
     # pages reserved at admission for the tokens of coming steps: same first step,
     # wider tables that the device-side advance can walk
