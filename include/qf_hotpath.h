@@ -14,8 +14,15 @@
  *   - Strides are in ELEMENTS of the tensor's dtype, like torch's.
  *   - Return value: 0 on success, a negative QF_E* code otherwise;
  *     qf_last_error() then returns a message for the calling thread.
- *   - All functions are thread-safe; a single host thread drives the
- *     reference engine (engine/cpp/include/iteration_loop.hpp:157-161).
+ *   - Threads: every call may be made from any thread, and calls on different
+ *     streams may run concurrently; the error text is per thread.  Three switches
+ *     are process-wide (atomic, but one switch each): qf_set_tuning,
+ *     qf_set_dependent_launch, and the one-shot request of qf_order_next_launch,
+ *     which is consumed by the NEXT chained launch of the process whichever thread
+ *     or stream makes it.  A host with several launching threads must make that
+ *     request and the launch it is meant for on one thread with no other launch of
+ *     this library in between.  The reference engine is driven by a single host
+ *     thread on one stream (engine/cpp/include/iteration_loop.hpp:157-161).
  *
  * Each entry point cites the reference interface it replaces, by path inside
  * the benjaminW2025/qwen-frence tree.
@@ -304,13 +311,15 @@ int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
 int qf_device_status(int32_t* status, int32_t reset);
 
 /* Programmatic dependent launch (on by default).  The RoPE / KV-write kernel, the
- * tensor-core partial pass and the combine for split_k <= 32 are launched with
+ * tensor-core partial pass and the combine for split_k <= 256 are launched with
  * cudaLaunchAttributeProgrammaticStreamSerialization: each may become resident
  * while the previous kernel of the stream is still running, does its index set-up
  * then, and waits (griddepcontrol.wait) for that kernel to complete and flush
- * before it reads any tensor or writes anything.  The one exception: the partial
- * pass reads seq_lens and the block table during that set-up, i.e. possibly before
- * the kernel launched two places earlier on the stream has flushed.  Step metadata
+ * before it reads any tensor or writes anything.  The exceptions: during that set-up
+ * the partial pass reads seq_lens and the block table -- and, in
+ * qf_packed_rope_decode_attention, the positions, and it requests K / V tiles of pages
+ * that do not hold a sequence's newest token (see there) -- i.e. possibly before the
+ * kernel launched two places earlier on the stream has flushed.  Step metadata
  * that arrives by a copy (the usual case) is ordered as usual; metadata that a
  * KERNEL updates in place on the same stream must be followed by
  * qf_order_next_launch() (qf_advance_decode_metadata does that itself).
@@ -441,6 +450,16 @@ int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* time
  * seq_len - 1 of that page -- the slot the engine's slot mapping names
  * (engine/graph/paged_graph_decoder.py:392-417) -- before it copies the page.  Sequences of
  * length 0 write nothing.  No rotated Q is returned.
+ * The slot mapping is NOT an argument: the row goes where block_table and seq_lens say.
+ * A caller whose slot mapping names another place (or -1, "skip this row") for a row of
+ * the batch must use the operator pair; rows duplicated as padding (the reference's
+ * bucketed decoder) are fine, they store identical bytes twice.
+ * Contract on the pools (what makes this a decode step): when the call is enqueued, every
+ * K / V row of the attended tokens EXCEPT each sequence's newest is already in the pools,
+ * written by work that completed before the kernel in front of this call on the stream
+ * started (an earlier step, a prefill).  The kernel relies on it: it requests tiles of
+ * those older pages before its dependency wait, while the kernels before it drain.  The
+ * newest token's page is only copied after this kernel itself has stored the new row.
  * QF_EUNSUPPORTED unless: 16-bit pools, 12 + 2 heads, split_k >= 2, and arguments for
  * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA;
  * callers then run qf_rope_kv_write and qf_grouped_splitk_decode_attention.

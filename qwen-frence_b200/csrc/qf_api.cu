@@ -1,6 +1,7 @@
 // Library-wide plumbing of libqf_hotpath.so: ABI version, per-thread error
 // text, the per-device status word kernels write when they meet a bad page id,
 // and the tuning switches.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -12,19 +13,21 @@ namespace qf {
 namespace {
 thread_local char g_error[512] = "";
 __device__ int g_status_word = 0;
-int g_dependent_launch = 1;
-int g_ordered_launch = 0;
+// Process-wide switches.  They are atomics, so concurrent calls cannot tear them, but they
+// are still ONE switch each: the pending ordered launch is consumed by the next chained
+// launch of the process, whichever thread or stream makes it.  A host that drives several
+// streams from several threads must make the request and the launch it is meant for from the
+// same thread with no other launch of this library in between (the reference's loop is one
+// thread and one stream, engine/cpp/include/iteration_loop.hpp:157-161).
+std::atomic<int> g_dependent_launch{1};
+std::atomic<int> g_ordered_launch{0};
 }  // namespace
 
-void request_ordered_launch() { g_ordered_launch = 1; }
-int take_ordered_launch() {
-  const int taken = g_ordered_launch;
-  g_ordered_launch = 0;
-  return taken;
-}
+void request_ordered_launch() { g_ordered_launch.store(1, std::memory_order_release); }
+int take_ordered_launch() { return g_ordered_launch.exchange(0, std::memory_order_acq_rel); }
 
-int dependent_launch_enabled() { return g_dependent_launch; }
-void disable_dependent_launch() { g_dependent_launch = 0; }
+int dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_acquire); }
+void disable_dependent_launch() { g_dependent_launch.store(0, std::memory_order_release); }
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -55,7 +58,7 @@ int qf_abi_version(void) { return QF_ABI_VERSION; }
 const char* qf_last_error(void) { return qf::g_error; }
 
 int qf_set_dependent_launch(int32_t enabled) {
-  qf::g_dependent_launch = enabled ? 1 : 0;
+  qf::g_dependent_launch.store(enabled ? 1 : 0, std::memory_order_release);
   return QF_OK;
 }
 

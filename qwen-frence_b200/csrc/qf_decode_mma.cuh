@@ -251,8 +251,10 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   const int cta = blockIdx.x - kv_head * sp.ctas_per_head;
 
   // The combine after this kernel may be scheduled as CTAs exit.  Until
-  // dependency_wait() below, only the sequence lengths and the block table are read
-  // (step metadata that no kernel of the layer writes) and nothing is written.
+  // dependency_wait() below, only step metadata that no kernel of the layer writes is
+  // read (the sequence lengths, the block table and, ROPE, the positions) and -- when
+  // sp.early_tiles says the caller vouches for them -- K / V tiles of pages other than
+  // each sequence's last; nothing is written.
   release_dependents();
   if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
   // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----

@@ -61,14 +61,21 @@ def build_rope_table(positions, *, base=1_000_000.0, device=None):
 
 def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, block_table, seq_lens, *,
                               split_k, scale=None, base=1_000_000.0, partials=None, rope_table=None,
-                              require_fused=False):
-    """RoPE Q/K of the packed rows, write K/V at `slot_mapping`, attend over `block_table`.
+                              require_fused=False, check_slots=False):
+    """RoPE Q/K of the packed rows, write K/V at token seq_lens - 1, attend over `block_table`.
 
     packed: (B, 2048) or (B, 1, 2048) fp16 / bf16, rows of [Q0..Q11 | K0 K1 | V0 V1];
     positions, slot_mapping, seq_lens: (B,); pools (pages, 16, 2, 128); block_table
     (B, max_blocks).  `slot_mapping[b]` must name token seq_lens[b] - 1 of sequence b in
     `block_table` (what the engine builds, engine/graph/paged_graph_decoder.py:392-417):
-    the fused kernel derives the slot from the table.  Returns the attention output
+    the fused kernel derives the slot from the table and never reads `slot_mapping`, so a
+    row whose slot is -1 or names another place is still written at the table's slot
+    (the operator pair would skip it, or write elsewhere) -- such batches belong to the
+    pair.  `check_slots=True` compares the two on the host first and raises ValueError on
+    a difference (it synchronises: for debugging, not under graph capture).  It is a decode
+    step: every attended token but the newest of each sequence must already be in the
+    pools, written before the kernel in front of this call started (the kernel requests
+    those older pages early).  Returns the attention output
     (B, 12, 128); the rotated queries are not materialised.  `rope_table`: the result of
     `build_rope_table` covering every position (default: a cached table of as many
     positions as the block table can hold -- build it before capturing a graph; positions
@@ -104,6 +111,13 @@ def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, b
                 and positions.dtype in (torch.int32, torch.int64))
     if not fused_ok:
         return pair()
+    if check_slots:
+        rows = torch.arange(batch, device=packed.device)
+        last = (seq_lens.long() - 1).clamp_min(0)
+        derived = block_table[rows, last // 16].long() * 16 + last % 16
+        wrong = ((slot_mapping.long() != derived) & (seq_lens.long() > 0)).nonzero().flatten().tolist()
+        _require(not wrong, f"slot_mapping differs from the block table's slot for rows {wrong[:8]}; "
+                            "run packed_qkv_rope_cache and grouped_splitk_decode_attention instead")
     q_view = packed.as_strided((batch, Q_HEADS, HEAD_DIM), (packed.stride(0), HEAD_DIM, 1))
     out = torch.empty((batch, Q_HEADS, HEAD_DIM), dtype=packed.dtype, device=packed.device)
     if partials is None:

@@ -489,3 +489,46 @@ def test_length_beyond_the_table_is_cut_not_followed(package, oracle, cuda_devic
     assert_attention_close(out[[0, 2]], expected[[0, 2]])
     # the padded entries of row 1 (-1) are reported as bad page ids, never dereferenced
     assert package.cabi.device_status() == 2
+
+
+@pytest.mark.parametrize("mode", [2, 4], ids=["per_partition", "tensor_core"])
+@pytest.mark.parametrize("split_k", [33, 64, 100, 256])
+def test_many_split_slots_take_the_chained_combine(package, oracle, cuda_device, mode, split_k):
+    """32 < split_k <= 256 (few long sequences cut into many pieces): the combine that keeps
+    up to eight slots per lane, on partials of the per-partition kernel (every slot written,
+    many of them empty) and of the persistent kernel (first few slots and an end mark),
+    including NaN-filled partial buffers, an empty sequence and a one-token sequence."""
+    lengths = [0, 1, 700, 5000, 40, 12000]
+    q, k, v, table, lens = make_paged_inputs(lengths, seed=41, value_scale=0.5, poison=True)
+    dev = cuda_device
+    expected = oracle.paged_attention(q, k, v, table, lens)
+    partials = (torch.full((len(lengths), split_k, 12, 128), float("nan"), device=dev),
+                torch.full((len(lengths), split_k, 12), float("nan"), device=dev),
+                torch.full((len(lengths), split_k, 12), float("nan"), device=dev))
+    package.cabi.set_tuning(force_generic=mode)
+    try:
+        out = package.grouped_splitk_decode_attention(q.to(dev), k.to(dev), v.to(dev), table.to(dev), lens.to(dev),
+                                                      split_k=split_k, partials=partials)
+    finally:
+        package.cabi.set_tuning()
+    assert_attention_close(out, expected)
+    assert (out[0] == 0).all()
+
+
+def test_misaligned_partial_buffer_keeps_off_the_vector_store_kernel(package, cuda_device):
+    """The tensor-core kernel stores partial rows as 16-byte vectors.  A partial buffer that
+    starts on a 4-byte boundary (a slice of a larger fp32 arena) must therefore be planned for
+    the per-partition kernel, whose stores are scalar.  Only the plan is asked: nothing is
+    launched on the misaligned buffer."""
+    q, k, v, table, lens = (t.to(cuda_device) for t in make_paged_inputs([300, 700], seed=5))
+    cabi = package.cabi
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    arena = torch.empty(2 * 8 * 12 * 128 + 4, dtype=torch.float32, device=cuda_device)
+    stats = (torch.empty(2, 8, 12, device=cuda_device), torch.empty(2, 8, 12, device=cuda_device))
+    out = torch.empty_like(q)
+    for offset, kernel in ((0, "decode_mma_kernel"), (1, "decode_partial_kernel"), (4, "decode_mma_kernel")):
+        partial_out = arena[offset:offset + 2 * 8 * 12 * 128].view(2, 8, 12, 128)
+        assert partial_out.data_ptr() % 16 == (4 * offset) % 16
+        args = splitk.fill_attention_args(cabi, q, k, v, table, lens, split_k=8, scale=128 ** -0.5,
+                                          partials=(partial_out, *stats), out=out)
+        assert cabi.fused_kernel_plan(args)[0] == kernel

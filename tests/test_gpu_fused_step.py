@@ -7,7 +7,7 @@ from __future__ import annotations
 import pytest
 import torch
 
-from conftest import assert_attention_close
+from conftest import assert_attention_close, make_paged_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -170,3 +170,25 @@ def test_decode_step_with_the_fused_write(package, cuda_device):
         assert torch.equal(a[live], b[live])
     fused.capture()
     assert torch.equal(fused.replay(), want)
+
+
+def test_slot_check_refuses_rows_the_fused_kernel_would_place_elsewhere(package, cuda_device):
+    """The fused kernel never reads the slot mapping (it writes at the block table's slot), so
+    a batch with a skipped row (slot -1) belongs to the operator pair; `check_slots=True`
+    says so before anything is launched, and passes the engine's own mapping."""
+    lengths = [40, 17, 300]
+    q, k, v, table, lens = (t.to(cuda_device) for t in make_paged_inputs(lengths, seed=9, value_scale=0.5))
+    packed = torch.randn(3, 2048, device=cuda_device).mul_(0.5).half()
+    positions = (lens - 1).to(torch.int32)
+    rows = torch.arange(3, device=cuda_device)
+    slots = table[rows, ((lens - 1) // 16).long()].long() * 16 + ((lens - 1) % 16).long()
+    out = package.packed_qkv_rope_attention(packed, positions, slots, k.clone(), v.clone(), table, lens,
+                                            split_k=4, require_fused=True, check_slots=True)
+    assert out.shape == (3, 12, 128)
+    skipped = slots.clone()
+    skipped[1] = -1
+    k_before = k.clone()
+    with pytest.raises(ValueError, match="slot_mapping differs"):
+        package.packed_qkv_rope_attention(packed, positions, skipped, k, v, table, lens,
+                                          split_k=4, require_fused=True, check_slots=True)
+    assert torch.equal(k, k_before)  # refused before any launch

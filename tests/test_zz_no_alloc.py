@@ -7,7 +7,8 @@ Collected last on purpose, so a run that stops at the first failure has already
 run every other test.  Passes alone in a fresh process and after the other tests:
 it relies on no state but the library's own array, whose old contents must not
 matter, which is why each comparison is made on two calls in a row with different
-inputs."""
+inputs.  Each call is also checked against the CPU oracle, and against the claim in
+its name: device memory in use is the same before and after the call."""
 
 from __future__ import annotations
 
@@ -21,7 +22,10 @@ from conftest import assert_attention_close, make_paged_inputs
 pytestmark = pytest.mark.gpu
 
 
-def _run_both(package, device, lengths, split_k, seed):
+calls_so_far = {"count": 0}
+
+
+def _run_both(package, oracle, device, lengths, split_k, seed):
     q, k, v, table, lens = make_paged_inputs(lengths, seed=seed, value_scale=0.5, poison=True)
     dq, dk, dv, dtable, dlens = (t.to(device) for t in (q, k, v, table, lens))
     reference = package.grouped_splitk_decode_attention(dq, dk, dv, dtable, dlens, split_k=split_k)
@@ -33,19 +37,29 @@ def _run_both(package, device, lengths, split_k, seed):
     args = splitk.fill_attention_args(cabi, dq, dk, dv, dtable, dlens, split_k=split_k,
                                       scale=128 ** -0.5, partials=None, out=out)
     assert not args.partial_out and not args.partial_max and not args.partial_sum
-    status = cabi.library().qf_grouped_splitk_decode_attention_static(
-        ctypes.byref(args), cabi.stream_pointer(device))
+    stream = cabi.stream_pointer(device)
+    torch.cuda.synchronize()
+    # the claim in the name: with the output preallocated, the call takes nothing from any allocator
+    allocated, reserved = torch.cuda.memory_allocated(device), torch.cuda.memory_reserved(device)
+    free_before, _ = torch.cuda.mem_get_info(device)
+    status = cabi.library().qf_grouped_splitk_decode_attention_static(ctypes.byref(args), stream)
     assert status == 0, cabi.library().qf_last_error()
     torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated(device) == allocated and torch.cuda.memory_reserved(device) == reserved
+    if calls_so_far["count"] > 0:  # a first call may make the driver load the kernels' code
+        assert torch.cuda.mem_get_info(device)[0] >= free_before, "the call took device memory"
+    calls_so_far["count"] += 1
+    expected = oracle.paged_attention(q, k, v, table, lens)
+    assert_attention_close(out, expected)
     return out, reference, (dq, dk, dv, dtable, dlens)
 
 
-def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row(package, cuda_device):
-    first, ref_first, _ = _run_both(package, cuda_device, [0, 1, 17, 100, 700, 2048], split_k=6, seed=31)
+def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row(package, oracle, cuda_device):
+    first, ref_first, _ = _run_both(package, oracle, cuda_device, [0, 1, 17, 100, 700, 2048], split_k=6, seed=31)
     assert_attention_close(first, ref_first)
     # second call: other shapes and split count, so stale partials of the first call sit
     # in the array at different offsets than this call's rows
-    second, ref_second, tensors = _run_both(package, cuda_device, [513, 64, 3, 1500], split_k=9, seed=32)
+    second, ref_second, tensors = _run_both(package, oracle, cuda_device, [513, 64, 3, 1500], split_k=9, seed=32)
     assert_attention_close(second, ref_second)
     # same kernels, same data: the two entry points agree to the last bit
     assert torch.equal(first, ref_first) and torch.equal(second, ref_second)
