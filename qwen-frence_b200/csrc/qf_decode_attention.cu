@@ -610,13 +610,15 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
 
 // The tensor-core persistent kernel serves the fused attention entry point whenever
 // the layout is the fast one, split_k >= 2, the batch's prefix fits in its shared
-// memory and both pools share their strides.  A sequence may be cut into at most
-// split_k pieces, so a CTA's share is at least longest / (split_k - 1) units and a
-// batch of few sequences with few slots leaves resident CTAs without work; the
-// per-partition kernel has the same limit (split_k CTAs per sequence and head) and
-// half the speed per page, so the persistent one is used regardless (measured from
-// batch 1 x 4096 tokens, split_k 22: 9.3 us against 12.3 us, upwards).  The CUDA-core
-// persistent kernel is only used when forced (tests, comparisons).
+// memory, both pools share their strides and the partial buffer is 16-byte aligned.  A
+// sequence may be cut into at most split_k pieces, so a CTA's share is at least
+// longest / (split_k - 1) units and a batch of few sequences with few slots leaves
+// resident CTAs without work; the per-partition kernel has the same limit (split_k CTAs
+// per sequence and head) and half the speed per page, so the persistent one is used
+// regardless (measured from batch 1 x 4096 tokens, split_k 22: 9.3 us against 12.3 us,
+// upwards).  Pools whose K and V strides differ (a view of a larger allocation on one
+// side) and partial buffers carved out at a 4-byte offset take the CUDA-core persistent
+// kernel, which keeps separate strides and stores partials element by element.
 enum class FusedKernel { kPartitioned, kStreamed, kTensorCore };
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
@@ -634,7 +636,6 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   // ... and stores a piece's partial rows as 16-byte vectors
   const bool tensor_core = mode != 3 && same_strides && aligned16(a->partial_out);
   if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
-  if (!tensor_core && mode == 0) return FusedKernel::kPartitioned;  // pools with different strides
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 

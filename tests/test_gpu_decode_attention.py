@@ -518,17 +518,44 @@ def test_many_split_slots_take_the_chained_combine(package, oracle, cuda_device,
 def test_misaligned_partial_buffer_keeps_off_the_vector_store_kernel(package, cuda_device):
     """The tensor-core kernel stores partial rows as 16-byte vectors.  A partial buffer that
     starts on a 4-byte boundary (a slice of a larger fp32 arena) must therefore be planned for
-    the per-partition kernel, whose stores are scalar.  Only the plan is asked: nothing is
-    launched on the misaligned buffer."""
+    the CUDA-core persistent kernel, whose stores are scalar.  Only the plan is asked: nothing
+    is launched on the misaligned buffer."""
     q, k, v, table, lens = (t.to(cuda_device) for t in make_paged_inputs([300, 700], seed=5))
     cabi = package.cabi
     splitk = package.kernel_module("paged_decode_grouped_splitk")
     arena = torch.empty(2 * 8 * 12 * 128 + 4, dtype=torch.float32, device=cuda_device)
     stats = (torch.empty(2, 8, 12, device=cuda_device), torch.empty(2, 8, 12, device=cuda_device))
     out = torch.empty_like(q)
-    for offset, kernel in ((0, "decode_mma_kernel"), (1, "decode_partial_kernel"), (4, "decode_mma_kernel")):
+    for offset, kernel in ((0, "decode_mma_kernel"), (1, "decode_stream_kernel"), (4, "decode_mma_kernel")):
         partial_out = arena[offset:offset + 2 * 8 * 12 * 128].view(2, 8, 12, 128)
         assert partial_out.data_ptr() % 16 == (4 * offset) % 16
         args = splitk.fill_attention_args(cabi, q, k, v, table, lens, split_k=8, scale=128 ** -0.5,
                                           partials=(partial_out, *stats), out=out)
         assert cabi.fused_kernel_plan(args)[0] == kernel
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_pools_with_different_strides_take_the_cuda_core_persistent_kernel(package, oracle, cuda_device, dtype):
+    """K in a contiguous pool, V as a view of a larger allocation (every page followed by an
+    unused NaN page): the tensor-core kernel keeps one set of row offsets for both pools, so
+    the fused call runs the CUDA-core persistent kernel, its default path; mixed lengths with
+    NaN-poisoned tails against the oracle, through the plain public call (no forcing)."""
+    generator = torch.Generator().manual_seed(12)
+    lengths = [0, 1, 16, 17, 333, 4000] + torch.randint(1, 900, (40,), generator=generator).tolist()
+    q, k, v, table, lens = make_paged_inputs(lengths, seed=52, value_scale=0.5, poison=True, dtype=dtype)
+    dev = cuda_device
+    v_storage = torch.full((v.shape[0], 2, 16, 2, 128), float("nan"), dtype=dtype, device=dev)
+    v_storage[:, 0] = v.to(dev)
+    v_view = v_storage[:, 0]
+    assert v_view.stride(0) == 2 * k.stride(0)
+    dq, dk, dtable, dlens = q.to(dev), k.to(dev), table.to(dev), lens.to(dev)
+    cabi = package.cabi
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    partials = (torch.empty(len(lengths), 6, 12, 128, device=dev), torch.empty(len(lengths), 6, 12, device=dev),
+                torch.empty(len(lengths), 6, 12, device=dev))
+    args = splitk.fill_attention_args(cabi, dq, dk, v_view, dtable, dlens, split_k=6, scale=128 ** -0.5,
+                                      partials=partials, out=torch.empty_like(dq))
+    assert cabi.fused_kernel_plan(args)[0] == "decode_stream_kernel"
+    out = package.grouped_splitk_decode_attention(dq, dk, v_view, dtable, dlens, split_k=6)
+    assert_attention_close(out, oracle.paged_attention(q, k, v, table, lens))
+    assert torch.isnan(v_storage[:, 1].float()).all()
