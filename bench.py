@@ -87,9 +87,12 @@ def parse_args():
     parser.add_argument("--repeats", type=int, default=5, help="timed regions of --steps replays each (median reported)")
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--workload", default="decode_b64")
-    parser.add_argument("--op", choices=("decode_step", "layer_glue"), default="decode_step",
+    parser.add_argument("--op", choices=("decode_step", "layer_glue", "cta_timeline"), default="decode_step",
                         help="layer_glue: residual-add + RMSNorm and the device-side metadata advance\n"
-                             "(one GPU; prints its own JSON line)")
+                             "cta_timeline: per-CTA time stamps of chained partial-pass launches\n"
+                             "(one GPU; each prints its own JSON line)")
+    parser.add_argument("--uniform-context", type=int, default=0,
+                        help="cta_timeline: give every sequence this context length (equal work per CTA)")
     parser.add_argument("--scaling", choices=("weak", "strong"), default="weak")
     parser.add_argument("--split-k", type=int, default=0, help="0: plan from host bounds")
     parser.add_argument("--layers", type=int, default=0, help="0: the workload's own (28)")
@@ -873,6 +876,80 @@ def release():
     torch.cuda.empty_cache()
 
 
+def run_cta_timeline(args):
+    """--op cta_timeline: `--layers` (default 4) launches of the instrumented tensor-core partial
+    pass, one per layer pool, chained in one graph as the layers of a step are.  Every CTA
+    stamps %globaltimer at entry, when its share is known, when its page ids are known, when its
+    first tile has landed and at exit.  Printed: per launch the min / mean / max of each stamp
+    (microseconds from the first launch's first entry), the histogram of exit times relative to
+    the launch's earliest exit in 1 us bins, and the range of units per CTA."""
+    import ctypes
+
+    import torch
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    package = entry.load_package()
+    cabi = package.cabi
+    launches = args.layers or 4
+    if args.uniform_context:
+        default_batch = package.workloads.WORKLOADS[args.workload]["batch"]
+        package.workloads.context_lengths = (
+            lambda name, seed=0, batch=None: [args.uniform_context] * (batch or default_batch))
+    workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=launches)
+    step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    q = torch.randn(workload.batch, 12, 128, device=device).mul_(0.5).to(step.dtype)
+    out = torch.empty_like(q)
+    scales = lambda layer: (step.k_scales[layer], step.v_scales[layer]) if step.fp8 else None
+    arg_sets = [splitk.fill_attention_args(
+        cabi, q, step.k_pools[layer], step.v_pools[layer], step.block_table, step.seq_lens, split_k=step.split_k,
+        scale=128 ** -0.5, partials=step.partials, out=out, kv_scales=scales(layer)) for layer in range(launches)]
+    _, ctas_per_head = cabi.fused_kernel_plan(arg_sets[0])
+    ctas = ctas_per_head * 2
+    stamps = [torch.zeros((ctas, 10), dtype=torch.int64, device=device) for _ in range(launches)]
+    lib = cabi.library()
+
+    def run():
+        stream = cabi.stream_pointer(device)
+        for layer in range(launches):
+            cabi.check(lib.qf_grouped_splitk_persistent_timeline(
+                ctypes.byref(arg_sets[layer]), stamps[layer].data_ptr(), stream))
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        run()
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        run()
+    torch.cuda.current_stream(device).wait_stream(side)
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    tables = [t.cpu().double() for t in stamps]
+    origin = tables[0][:, 0].min()
+    names = ("entry", "share_known", "ids_known", "first_tile", "exit")
+    rows = []
+    for table in tables:
+        busy = table[:, 5] > 0
+        record = {name: [round(float(((table[busy, i] - origin) / 1e3).min()), 2),
+                         round(float(((table[busy, i] - origin) / 1e3).mean()), 2),
+                         round(float(((table[busy, i] - origin) / 1e3).max()), 2)] for i, name in enumerate(names)}
+        exits = (table[busy, 4] - table[busy, 4].min()) / 1e3
+        record["exit_histogram_1us_bins_from_earliest"] = torch.histc(exits.float(), bins=12, min=0, max=12).int().tolist()
+        record["units_per_cta_min_max"] = [int(table[busy, 5].min()), int(table[busy, 5].max())]
+        full = table[busy, 5] == table[busy, 5].max()
+        record["exit_spread_us_of_ctas_with_a_full_share"] = round(
+            float((table[busy, 4][full].max() - table[busy, 4][full].min()) / 1e3), 2)
+        rows.append(record)
+    print(json.dumps({"op": "cta_timeline", "workload": args.workload, "uniform_context": args.uniform_context or None,
+                      "batch": workload.batch, "split_k": step.split_k, "ctas": ctas, "launches": rows,
+                      "columns": "min / mean / max microseconds over the CTAs, from the first launch's first entry",
+                      "device_status": cabi.device_status()}))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -892,6 +969,10 @@ def main():
     if args.op == "layer_glue":
         if rank == 0:
             run_layer_glue(args)
+        return
+    if args.op == "cta_timeline":
+        if rank == 0:
+            run_cta_timeline(args)
         return
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)

@@ -45,6 +45,11 @@ REFERENCE_FILES = (
     "engine/kvcache/paged_decode_attention.py",
     "engine/kvcache/paged_prefill_attention.py",
     "engine/kvcache/paged_forward.py",
+    # the callers of the path, for the drop-in test (tests/test_gpu_reference_caller.py): the
+    # reference's decode layer loop and graph decoder, its page allocator and its kernel loader
+    "engine/kvcache/paged_kv_cache.py",
+    "engine/graph/paged_graph_decoder.py",
+    "baseline/kernel_dispatch.py",
 )
 
 
