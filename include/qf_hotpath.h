@@ -300,7 +300,9 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 int qf_grouped_gqa_splitk_profile_out(const qf_decode_attention_args* args,
                                       int64_t* cycles, void* stream);
 
-/* Device-side status word of the kernels on the current device: 0; 2 when a
+/* Device-side status word of the kernels on the current device: the LARGEST code any
+ * kernel has recorded since the last reset (kernels record with an atomic maximum, so
+ * a later, smaller code does not hide an earlier, larger one).  0: nothing; 2 when a
  * kernel met a page id outside the pool (such a page is never dereferenced; it
  * reads as zeros); 3 when a warp of the tensor-core persistent kernel gave up its
  * bounded poll for an earlier sequence's merge (the one wait in the library that

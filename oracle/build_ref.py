@@ -29,6 +29,7 @@ import argparse
 import hashlib
 import importlib.util
 import json
+import os
 import shutil
 import sys
 from pathlib import Path
@@ -36,7 +37,8 @@ from pathlib import Path
 ORACLE_DIR = Path(__file__).resolve().parent
 REF_DIR = ORACLE_DIR / "_ref"
 MANIFEST = REF_DIR / "MANIFEST.json"
-DEFAULT_REFERENCE = Path("/root/reference")
+# where the build machine keeps the reference tree; override with --reference or QF_REFERENCE_TREE
+DEFAULT_REFERENCE = Path(os.environ.get("QF_REFERENCE_TREE", "/root/reference"))
 
 # module files the staged functions need at import time (paths inside the reference tree)
 REFERENCE_FILES = (

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kGenericWarps * 32)
     const int64_t page_id =
         load_index(p.block_table, p.table_dtype, sequence * p.bt_sb + logical * p.bt_sp);
     if (page_id < 0 || page_id >= p.num_pages) {
-      if (lane == 0) atomicExch(p.status, kStatusBadPageId);
+      if (lane == 0) atomicMax(p.status, kStatusBadPageId);
       continue;
     }
     const KV* krow = static_cast<const KV*>(p.k_pool) + page_id * p.k_sp + in_page * p.k_st +

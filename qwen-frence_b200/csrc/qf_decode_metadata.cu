@@ -35,12 +35,12 @@ __global__ void __launch_bounds__(kAdvanceThreads) advance_metadata_kernel(Advan
   const int64_t logical_page = position / p.page_size;
   int64_t slot = -1;  // the KV-write kernel skips a row whose slot is out of range
   if (position < 0 || logical_page >= p.table_width) {
-    atomicExch(p.status, kStatusPositionPastTable);
+    atomicMax(p.status, kStatusPositionPastTable);
   } else {
     const int64_t page =
         load_index(p.table, p.table_dtype, b * p.table_stride_b + logical_page * p.table_stride_p);
     if (page < 0 || page >= p.num_pages) {
-      atomicExch(p.status, kStatusBadPageId);
+      atomicMax(p.status, kStatusBadPageId);
     } else {
       slot = page * p.page_size + position % p.page_size;
     }

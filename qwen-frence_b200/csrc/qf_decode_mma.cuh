@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       // ... and the sequence's rotation position, fetched here (32 units ahead of its use)
       if (ROPE) {
         const int64_t at = load_index(rope.positions, rope.pos_dtype, sequence * rope.pos_stride);
-        if (at < 0 || at >= rope.table_positions) atomicExch(p.status, kStatusPositionPastTable);
+        if (at < 0 || at >= rope.table_positions) atomicMax(p.status, kStatusPositionPastTable);
         pos = static_cast<int>(at < 0 ? 0 : (at >= rope.table_positions ? rope.table_positions - 1 : at));
       }
       if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous unit is no page of this sequence
@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     // been cut, and only then is the given length looked at again.
     r.write = work.length[sequence] < p.max_tokens ||
               load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride) == work.length[sequence];
-    if (!r.write && lane == 0) atomicExch(p.status, kStatusPositionPastTable);
+    if (!r.write && lane == 0) atomicMax(p.status, kStatusPositionPastTable);
     r.row = static_cast<int64_t>(id) * page_bytes + static_cast<int64_t>(rows - 1) * p.k_tok_bytes +
             kv_head * p.k_head_bytes;
     const unsigned char* row_in = rope.packed + static_cast<int64_t>(sequence) * rope.row_bytes;
@@ -463,7 +463,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       } else {
         if (id < 0) {
           rows = 0;  // bad or missing id: the page reads as zeros
-          if (id == -2 && lane == 0) atomicExch(p.status, kStatusBadPageId);
+          if (id == -2 && lane == 0) atomicMax(p.status, kStatusBadPageId);
         }
         // K and V pools have the same strides here (the host checks), so one set of row
         // offsets serves both.  A page whose 16 rows all exist (every page but a
@@ -803,7 +803,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       int rounds = 0;
       while (load_acquire(&merged[parity]) < done_rank - 2) {
         if (++rounds > kMergePollRounds) {
-          atomicExch(p.status, kStatusMergeTimeout);
+          atomicMax(p.status, kStatusMergeTimeout);
           break;
         }
         __nanosleep(64);

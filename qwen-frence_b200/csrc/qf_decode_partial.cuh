@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
     const int64_t raw = table_elem == 8 ? *reinterpret_cast<const int64_t*>(at)
                                         : static_cast<int64_t>(*reinterpret_cast<const int32_t*>(at));
     if (static_cast<uint64_t>(raw) >= static_cast<uint64_t>(pool_pages)) {
-      atomicExch(p.status, kStatusBadPageId);
+      atomicMax(p.status, kStatusBadPageId);
       return -1;
     }
     return static_cast<int>(raw);

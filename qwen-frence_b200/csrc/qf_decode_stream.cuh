@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(kFastThreads, QF_MIN_CTAS)
       copy_chunk_async<FP8>(dst, src);
       copy_chunk_async<FP8>(dst + kRowPlus8, src + 8 * tok_bytes);
     } else {
-      if (page_id == -2) atomicExch(p.status, kStatusBadPageId);
+      if (page_id == -2) atomicMax(p.status, kStatusBadPageId);
       if constexpr (FP8) {
         *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
         *reinterpret_cast<uint2*>(dst + kRowPlus8) = make_uint2(0u, 0u);

@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (!is_q) {
         slot = load_index(p.slots, p.slot_dtype, m);
         if (slot < 0 || slot >= p.num_slots) {
-          if (rank == 0) atomicExch(p.status, kStatusBadPageId);
+          if (rank == 0) atomicMax(p.status, kStatusBadPageId);
           slot = -1;
         }
       }
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (try_wait(smem_u32(&acc_bar), 0)) break;
         __nanosleep(64);
       }
-      if (lane == 0) atomicExch(p.status, kStatusPipelineTimeout);
+      if (lane == 0) atomicMax(p.status, kStatusPipelineTimeout);
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));

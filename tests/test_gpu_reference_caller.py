@@ -57,7 +57,7 @@ def reference():
         "paged_kv_cache": load("engine/kvcache/paged_kv_cache.py", "paged_kv_cache"),
         "decoder": load("engine/graph/paged_graph_decoder.py", "paged_graph_decoder"),
     }
-    # the one change a maintainer makes (INTEGRATION.md): the loader's kernel directory
+    # the one change a maintainer makes: the loader's kernel directory
     dispatch = modules["kernel_dispatch"]
     dispatch._KERNEL_DIR = KERNEL_DIR
     dispatch._load.cache_clear()
