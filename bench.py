@@ -93,6 +93,8 @@ def parse_args():
                              "(one GPU; each prints its own JSON line)")
     parser.add_argument("--uniform-context", type=int, default=0,
                         help="cta_timeline: give every sequence this context length (equal work per CTA)")
+    parser.add_argument("--shard-of", type=int, default=1,
+                        help="cta_timeline: look at rank 0's shard of the workload split by sequence over this many ranks")
     parser.add_argument("--scaling", choices=("weak", "strong"), default="weak")
     parser.add_argument("--split-k", type=int, default=0, help="0: plan from host bounds")
     parser.add_argument("--layers", type=int, default=0, help="0: the workload's own (28)")
@@ -896,7 +898,8 @@ def run_cta_timeline(args):
         default_batch = package.workloads.WORKLOADS[args.workload]["batch"]
         package.workloads.context_lengths = (
             lambda name, seed=0, batch=None: [args.uniform_context] * (batch or default_batch))
-    workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=launches)
+    workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=launches,
+                                                world_size=args.shard_of, scaling="strong" if args.shard_of > 1 else "weak")
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
     splitk = package.kernel_module("paged_decode_grouped_splitk")
     q = torch.randn(workload.batch, 12, 128, device=device).mul_(0.5).to(step.dtype)
@@ -943,6 +946,13 @@ def run_cta_timeline(args):
         full = table[busy, 5] == table[busy, 5].max()
         record["exit_spread_us_of_ctas_with_a_full_share"] = round(
             float((table[busy, 4][full].max() - table[busy, 4][full].min()) / 1e3), 2)
+        stream_phase = (table[busy, 4] - table[busy, 3]) / 1e3
+        pieces = table[busy, 6]
+        record["stream_phase_us_by_pieces_of_warp0"] = {
+            int(n): [int((pieces == n).sum()), round(float(stream_phase[pieces == n].mean()), 2),
+                     round(float(stream_phase[pieces == n].max()), 2)] for n in sorted(set(pieces.tolist()))}
+        record["warp0_deposit_us_per_piece"] = round(float(table[busy, 7].sum() / max(float(pieces.sum()), 1.0) / 1e3), 3)
+        record["warp0_us_per_merge"] = round(float(table[busy, 8].sum() / max(float(table[busy, 9].sum()), 1.0) / 1e3), 3)
         rows.append(record)
     print(json.dumps({"op": "cta_timeline", "workload": args.workload, "uniform_context": args.uniform_context or None,
                       "batch": workload.batch, "split_k": step.split_k, "ctas": ctas, "launches": rows,
