@@ -84,7 +84,11 @@ def parse_args():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--repeats", type=int, default=5, help="timed regions of --steps replays each (median reported)")
+    parser.add_argument("--repeats", type=int, default=20,
+                        help="timed regions of --steps replays each; the median region is reported with min and max\n"
+                             "(the reference takes the median of at least 20 graph-amortised samples,\n"
+                             "experiments/decode/benchmark_native_grouped_decode.py:44-68); the other\n"
+                             "configurations take min(repeats, 5) regions")
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--workload", default="decode_b64")
     parser.add_argument("--op", choices=("decode_step", "layer_glue", "cta_timeline"), default="decode_step",
@@ -845,11 +849,11 @@ def measure_workload(package, oracle, name, device, timer, args, world, rank, sc
     step.capture(warmup=2)
     for _ in range(max(args.warmup, 3)):
         step.replay()
-    across, own = timer.per_step(step.replay, args.steps, min(args.repeats, 3))
+    across, own = timer.per_step(step.replay, args.steps, min(args.repeats, 5))
     record["ms_per_step"] = spread(across)
     record["own_ms_per_step"] = statistics.median(own)
     record["tokens_per_s"] = workload.batch / (statistics.median(own) * 1e-3)
-    leg = partial_pass_leg(package, step, timer, args.steps, min(args.repeats, 3), args.seed, world)
+    leg = partial_pass_leg(package, step, timer, args.steps, min(args.repeats, 5), args.seed, world)
     record["roofline"] = {k: leg[k] for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "peak_kind",
                                               "frac_of_nominal_8TBs", "algorithmic_bytes_per_launch",
                                               "us_per_launch", "kv_bytes_per_launch")}
