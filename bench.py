@@ -67,12 +67,14 @@ OTHER_WORKLOADS = ("cpu_single_layer_b8", "sweep_b256", "long_skew_b4", "fp8_b12
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the
 # ncu captures summarised beside this file (same per-launch workload as a full-size launch:
 # one layer of the named workload at seed 0).  Workloads without a capture report null.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    ("decode_b64", 0, "decode_mma_kernel"): 137.52e6 + 4.00e6,          # RoPE / KV write as its own kernel
-    ("decode_b64", 0, "decode_mma_kernel+rope"): 137.57e6 + 4.19e6,     # the default: write folded in
-    ("decode_b64", 0, "decode_partial_kernel"): 137.92e6 + 5.0e6,
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {  # (workload, seed, kernel): (bytes, split_k of the captured launches)
+    ("decode_b64", 0, "decode_mma_kernel"): (137.52e6 + 4.00e6, 10),      # RoPE / KV write as its own kernel
+    ("decode_b64", 0, "decode_mma_kernel+rope"): (137.57e6 + 4.19e6, 10),  # the default: write folded in
+    ("decode_b64", 0, "decode_partial_kernel"): (137.92e6 + 5.0e6, 10),
+    ("sweep_b256", 0, "decode_mma_kernel"): (409.63e6 + 3.54e6, 3),
+    ("long_skew_b4", 0, "decode_mma_kernel+rope"): (55.17e6 + 0.01e6, 148),  # the partials stay in L2
+    ("fp8_b128", 0, "decode_mma_kernel"): (135.19e6 + 1.92e6, 5),
 }
-TRAFFIC_CAPTURE_SPLIT_K = 10  # the captured launches used split_k 10
 
 
 # --kernel -> qf_set_tuning mode: profiling and A/B runs of the other partial-pass kernels
@@ -805,9 +807,9 @@ def partial_pass_leg(package, step, timer, steps, repeats, seed, world):
         launch_bytes += workload.batch * ((2048 - 1536) * 2 + 4 + 512 + 2 * 2 * 128 * 2)
     achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
     traffic = None
-    if world == 1 and step.split_k == TRAFFIC_CAPTURE_SPLIT_K and step.layers == LAYERS:
-        traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH.get(
-            (workload.name, seed, kernel_name + ("+rope" if step.fused_write else "")))
+    captured = NCU_TRAFFIC_BYTES_PER_LAUNCH.get((workload.name, seed, kernel_name + ("+rope" if step.fused_write else "")))
+    if world == 1 and captured is not None and step.split_k == captured[1] and step.layers == LAYERS:
+        traffic = captured[0]
     return {
         "bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
@@ -855,7 +857,7 @@ def measure_workload(package, oracle, name, device, timer, args, world, rank, sc
     record["tokens_per_s"] = workload.batch / (statistics.median(own) * 1e-3)
     leg = partial_pass_leg(package, step, timer, args.steps, min(args.repeats, 5), args.seed, world)
     record["roofline"] = {k: leg[k] for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "peak_kind",
-                                              "frac_of_nominal_8TBs", "algorithmic_bytes_per_launch",
+                                              "frac_of_nominal_8TBs", "traffic", "algorithmic_bytes_per_launch",
                                               "us_per_launch", "kv_bytes_per_launch")}
     step_bytes = step_algorithmic_bytes(package, step, leg)
     record["step_gbs"] = step_bytes / (statistics.median(own) * 1e-3) / 1e9
