@@ -230,12 +230,16 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
  * arguments on the current device, without launching anything: *kernel is
  * QF_KERNEL_PARTITIONED (one CTA per sequence, KV head and split; also the
  * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math; only when forced
- * with qf_set_tuning) or QF_KERNEL_PERSISTENT_MMA (tensor-core math, 16-bit and FP8
- * pools); *ctas_per_head is the number of
- * resident CTAs that share one KV head's pages (0 for QF_KERNEL_PARTITIONED). */
+ * with qf_set_tuning), QF_KERNEL_PERSISTENT_MMA (tensor-core math, 16-bit and FP8
+ * pools) or QF_KERNEL_PERSISTENT_MMA_SOLO (the same kernel with every warp keeping its
+ * pieces of the sequences to itself: block tables of at most 64 pages and
+ * batch * (split_k - 1) >= 8 * ctas_per_head, i.e. many short sequences); *ctas_per_head
+ * is the number of resident CTAs that share one KV head's pages (0 for
+ * QF_KERNEL_PARTITIONED). */
 #define QF_KERNEL_PARTITIONED 0
 #define QF_KERNEL_PERSISTENT 1
 #define QF_KERNEL_PERSISTENT_MMA 2
+#define QF_KERNEL_PERSISTENT_MMA_SOLO 3
 int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args, int32_t* kernel,
                                             int32_t* ctas_per_head);
 
@@ -463,7 +467,8 @@ int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* time
  * those older pages before its dependency wait, while the kernels before it drain.  The
  * newest token's page is only copied after this kernel itself has stored the new row.
  * QF_EUNSUPPORTED unless: 16-bit pools, 12 + 2 heads, split_k >= 2, and arguments for
- * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA;
+ * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA (or its
+ * _SOLO variant: the fused step then still runs the kernel whose warps share their pieces);
  * callers then run qf_rope_kv_write and qf_grouped_splitk_decode_attention.
  * `stages`: QF_STAGE_PARTIAL | QF_STAGE_COMBINE for the whole step; one of them alone
  * launches only that kernel (timing). */
@@ -482,7 +487,8 @@ int qf_build_rope_table(float* table, int32_t positions, double base, void* stre
  * force_generic: 0 automatic choice; 1 every attention call goes through the
  * stride-generic kernel; 2 fast per-partition kernel only, no persistent kernel;
  * 3 / 4 the persistent CUDA-core / tensor-core kernel whenever the layout allows,
- * whatever the number of split slots.  `stages` is accepted and recorded but the
+ * whatever the number of split slots; 5 the tensor-core kernel's solo variant whenever the
+ * layout allows (4 never picks that variant).  `stages` is accepted and recorded but the
  * kernels' shared-memory rings have fixed depths chosen at compile time. */
 int qf_set_tuning(int32_t stages, int32_t force_generic);
 

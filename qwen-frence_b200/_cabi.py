@@ -38,7 +38,7 @@ EXPORTED_SYMBOLS = (
     "qf_qkv_rope_cache_timeline", "qf_packed_rope_decode_attention",
     "qf_build_rope_table",
 )
-KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel")
+KERNEL_NAMES = ("decode_partial_kernel", "decode_stream_kernel", "decode_mma_kernel", "decode_mma_kernel (solo)")
 STAGE_PARTIAL, STAGE_COMBINE = 1, 2
 GEMM_TIMELINE_COLUMNS = 10
 STATIC_SCRATCH_BYTES = 16 << 20
@@ -268,6 +268,6 @@ def set_tuning(stages=0, force_generic=False):
     """Kernel selection for tests: force_generic 1 (or True) sends every launch to the
     stride-generic kernel, 2 keeps the fast per-partition kernel but turns the
     persistent ones off, 3 / 4 use the persistent CUDA-core / tensor-core kernel
-    whenever the layout allows (also for batches with few split slots); 0 restores
-    the defaults."""
+    whenever the layout allows (also for batches with few split slots), 5 the
+    tensor-core kernel's solo variant (4 never picks it); 0 restores the defaults."""
     check(library().qf_set_tuning(int(stages), int(force_generic)))

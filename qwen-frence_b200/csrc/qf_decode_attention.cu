@@ -339,6 +339,68 @@ __global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReducePa
   }
 }
 
+// The same combine for large batches (thousands of (sequence, head) rows): one WARP per row
+// instead of one CTA, eight rows per CTA, a lane four dimensions (one 16-byte load per slot).
+// Same operations in the same order as the kernel above, so the same bits; needs head_dim
+// 128, unit dimension strides and 16-byte aligned rows.  At 512 sequences the one-CTA-per-row
+// grid is 6 144 CTAs and takes 7.6 us per layer, at 1 024 sequences 14 us.
+constexpr int kRowsReduceMinRows = 2048;
+
+template <typename T, bool STREAMED>
+__global__ void __launch_bounds__(256) splitk_reduce_rows_kernel(const ReduceParams p, int rows) {
+  constexpr unsigned kFull = 0xffffffffu;
+  release_dependents();
+  dependency_wait();  // the partials come from the kernel before this one
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int sequence = row / p.q_heads;
+  const int head = row - sequence * p.q_heads;
+  const float* pm = p.pm + sequence * p.pm_sb + head * p.pm_sh;
+  const float* ps = p.ps + sequence * p.pm_sb + head * p.pm_sh;
+  const float* po = p.po + sequence * p.po_sb + head * p.po_sh + 4 * lane;
+  T* out = static_cast<T*>(p.out) + sequence * p.o_sb + head * p.o_sh + 4 * lane;
+  auto store = [&](float a, float b, float c, float d) {
+    __align__(8) T packed[4] = {from_float<T>(a), from_float<T>(b), from_float<T>(c), from_float<T>(d)};
+    *reinterpret_cast<uint2*>(out) = *reinterpret_cast<const uint2*>(packed);
+  };
+
+  int64_t length = 1;
+  if (STREAMED) length = min(load_index(p.seq_lens, p.lens_dtype, sequence * p.lens_stride), p.max_tokens);
+  float sum = 0.f, offset = -INFINITY;
+  if (lane < p.split_k) sum = ps[lane * p.pm_sk], offset = pm[lane * p.pm_sk];
+  if (STREAMED && length <= 0) {
+    store(0.f, 0.f, 0.f, 0.f);  // no tokens: no slot was written
+    return;
+  }
+  int filled = p.split_k;
+  if (STREAMED) {
+    const unsigned marks = __ballot_sync(kFull, lane < p.split_k && sum < 0.f);
+    if (marks != 0) filled = __ffs(marks) - 1;
+  }
+  const bool used = lane < filled && sum > 0.f;
+  float top = used ? offset : -INFINITY;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
+  const float weight = used ? expf(offset - top) : 0.f;
+  float total = sum * weight;
+  if (!used) total = 0.f;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(kFull, total, off);
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int k = 0; k < filled; ++k) {
+    const float w = __shfl_sync(kFull, weight, k);
+    if (w != 0.f) {
+      const float4 part = *reinterpret_cast<const float4*>(po + k * p.po_sk);
+      acc.x += part.x * w, acc.y += part.y * w, acc.z += part.z * w, acc.w += part.w * w;
+    }
+  }
+  const float divisor = total > 0.f ? total : 1.f;
+  store(acc.x / divisor, acc.y / divisor, acc.z / divisor, acc.w / divisor);
+}
+
 // Combine for 32 < split_k <= 256 (few long sequences cut into many pieces): the small
 // kernel's scheme with up to eight slots per lane.  Every warp reads all statistics in one
 // trip (lane l holds slots l, l + 32, ...), finds the filled slots, the top offset, the
@@ -498,9 +560,9 @@ size_t mma_smem_bytes(bool fp8) {
 }
 
 // One CTA per SM for 16-bit pools (its rings take most of the shared memory), two for FP8.
-template <typename T, bool FP8, bool PROFILE, bool ROPE = false>
+template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = false>
 int launch_mma(const FastParams& p, cudaStream_t stream, const RopeInputs& rope = RopeInputs{}) {
-  auto kernel = decode_mma_kernel<T, FP8, PROFILE, ROPE>;
+  auto kernel = decode_mma_kernel<T, FP8, PROFILE, ROPE, SOLO>;
   const size_t smem = mma_smem_bytes(FP8);
   QF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
@@ -520,6 +582,11 @@ int launch_mma(const FastParams& p, cudaStream_t stream, const RopeInputs& rope 
 template <typename T, bool PROFILE>
 int launch_mma_for_pools(const FastParams& p, bool fp8, cudaStream_t stream) {
   return fp8 ? launch_mma<T, true, PROFILE>(p, stream) : launch_mma<T, false, PROFILE>(p, stream);
+}
+// the variant in which every warp keeps its pieces to itself
+template <typename T>
+int launch_mma_solo(const FastParams& p, bool fp8, cudaStream_t stream) {
+  return fp8 ? launch_mma<T, true, false, false, true>(p, stream) : launch_mma<T, false, false, false, true>(p, stream);
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
@@ -619,11 +686,12 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
 // upwards).  Pools whose K and V strides differ (a view of a larger allocation on one
 // side) and partial buffers carved out at a 4-byte offset take the CUDA-core persistent
 // kernel, which keeps separate strides and stores partials element by element.
-enum class FusedKernel { kPartitioned, kStreamed, kTensorCore };
+enum class FusedKernel { kPartitioned, kStreamed, kTensorCore, kTensorCoreSolo };
+constexpr int64_t kSoloTablePages = 64;  // block tables up to this width (1 024 tokens) may take the solo variant
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
-  const int mode = g_force_generic;  // 0 automatic, 3 / 4 force a persistent kernel (tests)
-  if ((mode != 0 && mode != 3 && mode != 4) || !fast_path_ok(a) || a->split_k < 2) {
+  const int mode = g_force_generic;  // 0 automatic, 3 / 4 / 5 force a persistent kernel (tests)
+  if ((mode != 0 && mode != 3 && mode != 4 && mode != 5) || !fast_path_ok(a) || a->split_k < 2) {
     return FusedKernel::kPartitioned;
   }
   if (a->batch > kMaxStreamBatch || a->kv_heads > 64) return FusedKernel::kPartitioned;
@@ -635,7 +703,22 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
                             a->k_stride_tok * (a->kv_fp8 ? 1 : 2) * QF_PAGE_SIZE < (1LL << 31);
   // ... and stores a piece's partial rows as 16-byte vectors
   const bool tensor_core = mode != 3 && same_strides && aligned16(a->partial_out);
-  if (mode == 4 && !tensor_core) return FusedKernel::kPartitioned;
+  if ((mode == 4 || mode == 5) && !tensor_core) return FusedKernel::kPartitioned;
+  if (tensor_core && mode != 4) {
+    // Many short sequences: every warp keeps its pieces to itself.  Chosen from what the host
+    // knows -- no sequence is longer than the table is wide (at most kSoloTablePages pages),
+    // and even if every sequence were that long each warp of the grid would get a block of
+    // its own without a sequence needing more than split_k slots: batch * (split_k - 1) >=
+    // warps per KV head.  Measured against the variant that shares pieces among a CTA's warps
+    // (partial pass per layer): 512 x 100 tokens 12.3 against 24.7 us, 1 024 x 60 14.9 against
+    // 35.2, 256 x 200 11.8 against 18.8, 512 x 400 36.8 against 46.0; equal at 128 x 700
+    // (20.2 / 20.1) and slower below the batch bound (64 x 200: 9.4 against 7.5).
+    const int64_t warps_per_head =
+        static_cast<int64_t>(mma_ctas_on_current_device(a->kv_fp8 != 0) / a->kv_heads) * 8;
+    const bool many_short = a->table_width <= kSoloTablePages &&
+                            static_cast<int64_t>(a->batch) * (a->split_k - 1) >= warps_per_head;
+    if (mode == 5 || many_short) return FusedKernel::kTensorCoreSolo;
+  }
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 
@@ -648,6 +731,10 @@ int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kin
     QF_REQUIRE(kind == FusedKernel::kTensorCore, "only the tensor-core kernel has a timeline variant");
     return a->dtype == QF_DTYPE_F16 ? launch_mma_for_pools<__half, true>(p, a->kv_fp8 != 0, stream)
                                     : launch_mma_for_pools<__nv_bfloat16, true>(p, a->kv_fp8 != 0, stream);
+  }
+  if (kind == FusedKernel::kTensorCoreSolo) {
+    return a->dtype == QF_DTYPE_F16 ? launch_mma_solo<__half>(p, a->kv_fp8 != 0, stream)
+                                    : launch_mma_solo<__nv_bfloat16>(p, a->kv_fp8 != 0, stream);
   }
   if (kind == FusedKernel::kTensorCore) {
     return a->dtype == QF_DTYPE_F16 ? launch_mma_for_pools<__half, false>(p, a->kv_fp8 != 0, stream)
@@ -721,7 +808,18 @@ void launch_reduce_typed(const ReduceParams& r, unsigned blocks, int threads, bo
   // head_dim is a multiple of 32 on this path, so whole warps take part in the shuffles
   const bool small = r.split_k <= kSmallReduceSlots && (r.head_dim & 31) == 0;
   const bool medium = !small && r.split_k <= kMediumReduceSlots && (r.head_dim & 31) == 0;
-  if (medium && streamed) {
+  const bool vector_rows = r.head_dim == 128 && r.po_sd == 1 && r.o_sd == 1 && aligned16(r.po) &&
+                           ((r.po_sb | r.po_sk | r.po_sh | r.o_sb | r.o_sh) & 3) == 0 &&
+                           (reinterpret_cast<uintptr_t>(r.out) & 7) == 0;
+  if (small && vector_rows && blocks >= static_cast<unsigned>(kRowsReduceMinRows)) {
+    const int rows = static_cast<int>(blocks);
+    const dim3 grid((blocks + 7) / 8), cta(256);
+    if (streamed) {
+      (void)launch_chained(splitk_reduce_rows_kernel<T, true>, grid, cta, 0, stream, r, rows);
+    } else {
+      (void)launch_chained(splitk_reduce_rows_kernel<T, false>, grid, cta, 0, stream, r, rows);
+    }
+  } else if (medium && streamed) {
     (void)launch_chained(splitk_reduce_medium_kernel<T, true>, dim3(blocks), dim3(threads), 0, stream, r);
   } else if (medium) {
     (void)launch_chained(splitk_reduce_medium_kernel<T, false>, dim3(blocks), dim3(threads), 0, stream, r);
@@ -832,8 +930,9 @@ int qf_grouped_splitk_decode_attention_plan(const qf_decode_attention_args* args
   const qf::FusedKernel kind = qf::choose_fused_kernel(args);
   if (kind == qf::FusedKernel::kPartitioned) return QF_OK;
   const int resident = qf::stream_ctas_on_current_device();
-  const bool mma = kind == qf::FusedKernel::kTensorCore;
+  const bool mma = kind == qf::FusedKernel::kTensorCore || kind == qf::FusedKernel::kTensorCoreSolo;
   *kernel = mma ? QF_KERNEL_PERSISTENT_MMA : QF_KERNEL_PERSISTENT;
+  if (kind == qf::FusedKernel::kTensorCoreSolo) *kernel = QF_KERNEL_PERSISTENT_MMA_SOLO;
   *ctas_per_head = (mma ? qf::mma_ctas_on_current_device(args->kv_fp8 != 0) : resident) / args->kv_heads;
   return QF_OK;
 }
@@ -844,7 +943,9 @@ int qf_grouped_splitk_persistent_timeline(const qf_decode_attention_args* args, 
   if (rc != QF_OK) return rc;
   QF_REQUIRE(timeline != nullptr, "timeline must not be null");
   QF_REQUIRE(args->split_k >= 2 && args->batch >= 1, "the persistent kernels need split_k >= 2 and a batch");
-  const qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  // (the instrumented variant is the one whose warps share their pieces)
+  if (kind == qf::FusedKernel::kTensorCoreSolo) kind = qf::FusedKernel::kTensorCore;
   QF_REQUIRE(kind == qf::FusedKernel::kTensorCore,
              "these arguments do not select the tensor-core persistent kernel");
   return qf::launch_persistent_partial(args, kind, static_cast<cudaStream_t>(stream),
@@ -880,7 +981,8 @@ int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const 
   // q points at the packed rows: 16 segments of 128, the query heads first
   if (args->kv_fp8 || args->q_heads != 12 || args->kv_heads != 2 || args->q_stride_h != QF_HEAD_DIM ||
       args->q_stride_b < 16 * QF_HEAD_DIM || args->split_k < 2 ||
-      qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCore) {
+      (qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCore &&
+       qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCoreSolo)) {
     return qf::fail(QF_EUNSUPPORTED,
                     "the fused step needs 16-bit pools, the packed 12 + 2 + 2 head layout, split_k >= 2 and a "
                     "layout the tensor-core kernel takes; run the RoPE / KV write and the attention separately");
@@ -953,7 +1055,7 @@ int qf_grouped_gqa_splitk_diagnostics(int32_t device, int32_t dtype, int32_t kv_
 
 int qf_set_tuning(int32_t stages, int32_t force_generic) {
   QF_REQUIRE(stages >= 0 && stages <= 64, "stages must be in [0, 64]");
-  QF_REQUIRE(force_generic >= 0 && force_generic <= 4, "force_generic must be in [0, 4]");
+  QF_REQUIRE(force_generic >= 0 && force_generic <= 5, "force_generic must be in [0, 5]");
   qf::g_tuned_stages = stages;
   qf::g_force_generic = force_generic;
   return QF_OK;

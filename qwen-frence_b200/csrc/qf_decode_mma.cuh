@@ -219,10 +219,22 @@ struct RopeInputs {
   int table_positions;
 };
 
-template <typename T, bool FP8, bool PROFILE, bool ROPE = false>
+//
+// SOLO (batches of many short sequences): warp w owns the CONSECUTIVE units begin + w * block
+// .. of the CTA's share (block = share / 8) instead of every eighth, the list has no empty
+// units, and every stretch of one sequence inside a warp's block is a piece of its own that the
+// warp stores straight to a split slot (slot = the block's number minus the number of the block
+// that holds the sequence's first page): no deposits, no arrival counters, no merge, nothing
+// shared between warps after the work list.  A block is at least longest / (split_k - 1) units,
+// so a sequence never needs more than split_k slots.  What a short sequence costs is then one
+// Q tile and one store for one warp, not for each of eight.
+template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = false>
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
   static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
+  static_assert(!(SOLO && (ROPE || PROFILE)), "the solo variant is the plain attention pass");
+  constexpr int kOverhead = SOLO ? 0 : kPieceOverhead;  // empty units in front of a sequence
+  constexpr int kStep = SOLO ? 1 : kMmaWarps;          // distance between a warp's units
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
   using Ring = RingShape<FP8>;
   constexpr int kAhead = Ring::kAhead;
@@ -259,8 +271,8 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   if (tid < 2) arrived[tid] = 0, merged[tid] = tid - 2;  // pieces -2 and -1 count as merged
   // ---- the page list of this launch and this CTA's share of it (two CTA-wide barriers) ----
   const int longest =
-      build_work_list<QF_PAGE_SIZE, kPieceOverhead>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch,
-                                                    p.max_tokens);
+      build_work_list<QF_PAGE_SIZE, kOverhead>(work, p.seq_lens, p.lens_dtype, p.lens_stride, p.batch,
+                                               p.max_tokens);
   const int* first_page = work.first_unit;  // first unit of a sequence; its pages follow its empty units
   const int total = first_page[kMaxStreamBatch];
   if (PROFILE) t_list = global_nanoseconds();
@@ -268,8 +280,14 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     dependency_wait();  // keeps the chain of completions intact even without work
     return;
   }
-  const int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
-                        (longest + p.split_k - 2) / (p.split_k - 1));
+  int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
+                  (longest + p.split_k - 2) / (p.split_k - 1));
+  int block = 0;  // SOLO: units per warp
+  if constexpr (SOLO) {
+    block = max(((total + sp.ctas_per_head - 1) / sp.ctas_per_head + kMmaWarps - 1) / kMmaWarps,
+                (longest + p.split_k - 2) / (p.split_k - 1));
+    share = block * kMmaWarps;
+  }
   const int begin = cta * share;
   if (begin >= total) {
     dependency_wait();
@@ -277,8 +295,11 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   }
   const int count = min(share, total - begin);
   const int end = begin + count;
-  // This warp's units: begin + warp + 8 k, k = 0 .. my_pages - 1 (pages, or empty units).
-  const int my_pages = count > warp ? (count - warp + kMmaWarps - 1) / kMmaWarps : 0;
+  // This warp's units: begin + warp + 8 k, k = 0 .. my_pages - 1 (pages, or empty units);
+  // SOLO: begin + warp * block + k.
+  const int my_first = SOLO ? begin + warp * block : begin + warp;
+  const int my_pages = SOLO ? min(max(count - warp * block, 0), block)
+                            : (count > warp ? (count - warp + kMmaWarps - 1) / kMmaWarps : 0);
 
   // ---- loads ----
   const int pool_pages = static_cast<int>(p.num_pages);
@@ -313,10 +334,10 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     const int k = chunk * 32 + lane;
     id = -1, rows = 0, q_of = -1, last_of = -1, pos = 0;
     if (k < my_pages) {
-      const int unit = begin + warp + kMmaWarps * k;
+      const int unit = my_first + kStep * k;
       const int sequence = sequence_of_unit(work, p.batch, unit);
       const int in_sequence = unit - first_page[sequence] -
-                              sequence_overhead<kPieceOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
+                              sequence_overhead<kOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
       // page index within the sequence; < 0: an empty unit
       if (in_sequence < 0) {
         id = -3;
@@ -337,7 +358,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         if (at < 0 || at >= rope.table_positions) atomicMax(p.status, kStatusPositionPastTable);
         pos = static_cast<int>(at < 0 ? 0 : (at >= rope.table_positions ? rope.table_positions - 1 : at));
       }
-      if (k == 0 || in_sequence < kMmaWarps) q_of = sequence;  // the warp's previous unit is no page of this sequence
+      if (k == 0 || in_sequence < kStep) q_of = sequence;  // the warp's previous unit is no page of this sequence
     }
   };
   int id_now, rows_now, q_now, last_now, id_next, rows_next, q_next, last_next;
@@ -641,13 +662,14 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   // the same list but only stops at pieces that hold some of its pages.
   int piece_seq = sequence_of_unit(work, p.batch, begin);
   int rank = 0;
-  int page = begin + warp;  // this warp's next unit
+  int page = my_first;  // this warp's next unit
+  const int my_end = SOLO ? min(end, my_first + block) : end;  // end of this warp's units
   int read_slot = 0;
   // Move (piece_seq, rank) forward to the sequence that holds unit `target` (< end).  Only
   // sequences with a page inside the share count as pieces.
   auto first_data_unit = [&](int sequence) {
     return first_page[sequence] +
-           sequence_overhead<kPieceOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
+           sequence_overhead<kOverhead>((work.length[sequence] + QF_PAGE_SIZE - 1) / QF_PAGE_SIZE);
   };
   auto advance_to = [&](int target) {
     while (piece_seq < p.batch - 1 && first_page[piece_seq + 1] <= target) {
@@ -656,7 +678,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     }
   };
 
-  while (page < end) {
+  while (page < my_end) {
     advance_to(page);
     const int seq_first = first_data_unit(piece_seq);  // unit of the sequence's first page
     if (page < seq_first) {
@@ -718,10 +740,10 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     float v_reference = 0.f, v_reference_inverse = 0.f;  // FP8: V scale of the warp's first page of the piece
     const int seq_len = work.length[piece_seq];
     const int piece_begin = max(seq_first, begin);  // first page of the piece (as a unit)
-    const int piece_end = min(first_page[piece_seq + 1], end);
+    const int piece_end = min(first_page[piece_seq + 1], my_end);
     const int done_seq = piece_seq, done_rank = rank;
 
-    for (; page < piece_end; page += kMmaWarps) {
+    for (; page < piece_end; page += kStep) {
       // ---- scores S^T = K Q^T ----
       wait_tiles_ahead<kAhead>();
       __syncwarp();
@@ -850,6 +872,53 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         for (int i = 0; i < 4; ++i) acc[j][i] *= v_reference;
     }
 
+    if constexpr (SOLO) {
+      // ---- the piece is this warp's alone: through its deposit buffer (so that rows leave as
+      // 16-byte vectors) to its split slot ----
+      float* mine = deposits + warp * kDepositFloats;  // [6 heads][dim]
+      if (q < QF_GQA_GROUP / 2) {
+        float* even = mine + (2 * q) * kDepositHeadStride + (FP8 ? 2 * g : g);
+        float* odd = even + kDepositHeadStride;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          even[16 * j] = acc[j][0], odd[16 * j] = acc[j][1];
+          even[16 * j + (FP8 ? 1 : 8)] = acc[j][2], odd[16 * j + (FP8 ? 1 : 8)] = acc[j][3];
+        }
+      }
+      float total[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        total[h] = sum[h];
+        total[h] += __shfl_xor_sync(kFull, total[h], 4);
+        total[h] += __shfl_xor_sync(kFull, total[h], 8);
+        total[h] += __shfl_xor_sync(kFull, total[h], 16);
+      }
+      __syncwarp();
+      const int split_slot = cta * kMmaWarps + warp - seq_first / block;
+      const bool slot_ok = split_slot >= 0 && split_slot < p.split_k;  // holds by the choice of `block`
+      if (slot_ok) {
+        const int64_t partial_row =
+            (static_cast<int64_t>(done_seq) * p.split_k + split_slot) * p.q_heads +
+            static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
+        float4* row = reinterpret_cast<float4*>(p.partial_out + partial_row * QF_HEAD_DIM) + lane;
+#pragma unroll
+        for (int head = 0; head < QF_GQA_GROUP; ++head) {
+          row[head * (QF_HEAD_DIM / 4)] = *reinterpret_cast<const float4*>(mine + head * kDepositHeadStride + 4 * lane);
+        }
+        if (g == 0 && q < QF_GQA_GROUP / 2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            p.partial_max[partial_row + 2 * q + h] = offset[h] * kLn2;  // natural-log units for the combine
+            p.partial_sum[partial_row + 2 * q + h] = total[h];
+            if (first_page[done_seq + 1] <= my_end && split_slot + 1 < p.split_k) {
+              p.partial_sum[partial_row + p.q_heads + 2 * q + h] = -1.f;  // no further pieces of this sequence
+            }
+          }
+        }
+      }
+      __syncwarp();  // the buffer is read before the next piece overwrites it
+      continue;
+    }
     // ---- deposit this warp's state of the piece; the last warp to arrive merges ----
     long long t_piece = 0;
     if (PROFILE) t_piece = global_nanoseconds(), ++pieces;

@@ -128,7 +128,7 @@ def packed_qkv_rope_attention(packed, positions, slot_mapping, k_pool, v_pool, b
     args = attention.fill_attention_args(
         cabi, q_view, k_pool, v_pool, block_table, seq_lens, split_k=int(split_k),
         scale=HEAD_DIM ** -0.5 if scale is None else scale, partials=partials, out=out)
-    if cabi.fused_kernel_plan(args)[0] != "decode_mma_kernel":
+    if not cabi.fused_kernel_plan(args)[0].startswith("decode_mma_kernel"):
         return pair()
     positions = positions.contiguous()
     if rope_table is None:

@@ -134,7 +134,20 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
     pages = -(-max_context_length // page_size)
     wanted = -(-(sm_count * ctas_per_sm * waves) // (batch * kv_heads))
     cap = max(1, pages // min_pages_per_split)
-    return int(max(1, min(wanted, cap, 65535)))
+    split_k = int(max(1, min(wanted, cap, 65535)))
+    # Many short sequences: the tensor-core kernel's solo variant (every warp keeps its pieces
+    # to itself) takes block tables of up to SOLO_TABLE_PAGES pages when batch * (split_k - 1)
+    # covers the warps that share a KV head; a slot it does not fill costs nothing.
+    if pages <= SOLO_TABLE_PAGES and batch >= SOLO_MIN_BATCH:
+        warps_per_head = sm_count * 8 // kv_heads
+        split_k = max(split_k, -(-warps_per_head // batch) + 1)
+    return split_k
+
+
+# Widest block table (pages) and smallest batch for which plan_split_k aims at the solo
+# variant of the tensor-core kernel (kSoloTablePages in csrc/qf_decode_attention.cu).
+SOLO_TABLE_PAGES = 64
+SOLO_MIN_BATCH = 256
 
 
 # Empty units the tensor-core persistent kernel counts per sequence when it cuts the

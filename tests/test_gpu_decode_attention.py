@@ -515,6 +515,92 @@ def test_many_split_slots_take_the_chained_combine(package, oracle, cuda_device,
     assert (out[0] == 0).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("batch,split_k", [(300, 3), (600, 2), (90, 8)])
+def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device, dtype, batch, split_k):
+    """Block tables of at most 64 pages and batch * (split_k - 1) >= the warps that share a KV
+    head: every warp keeps its stretch of the page list to itself and stores each sequence's
+    part of it to a split slot of its own.  Lengths from 0 tokens to the full table, page
+    boundaries on both sides, NaN tails, NaN-filled partial buffers; 300 and 600 rows of 12
+    heads also take the one-warp-per-row combine."""
+    generator = torch.Generator().manual_seed(batch + split_k)
+    lengths = torch.randint(0, 1025, (batch,), generator=generator).tolist()
+    lengths[:8] = [0, 1, 15, 16, 17, 1023, 1024, 0]
+    host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=batch, value_scale=0.5, poison=True)
+    assert host[3].shape[1] <= 64
+    cabi = package.cabi
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    partials = (torch.full((batch, split_k, 12, 128), float("nan"), device=cuda_device),
+                torch.full((batch, split_k, 12), float("nan"), device=cuda_device),
+                torch.full((batch, split_k, 12), float("nan"), device=cuda_device))
+    args = splitk.fill_attention_args(cabi, *dev, split_k=split_k, scale=128 ** -0.5, partials=partials,
+                                      out=torch.empty_like(dev[0]))
+    assert cabi.fused_kernel_plan(args)[0] == "decode_mma_kernel (solo)"
+    out = package.grouped_splitk_decode_attention(*dev, split_k=split_k, partials=partials)
+    assert cabi.device_status() == 0
+    expected = oracle.paged_attention(*host)
+    assert_attention_close(out, expected, dtype=dtype)
+    assert (out[0] == 0).all() and (out[7] == 0).all()
+    # slots: filled from 0 without gaps, then the end mark (sum -1) unless every slot is used
+    sums = partials[2][:, :, 0].cpu()
+    for row, length in enumerate(lengths):
+        if length == 0:
+            continue
+        filled = 0
+        while filled < split_k and sums[row, filled] > 0:
+            filled += 1
+        assert filled >= 1
+        if filled < split_k:
+            assert sums[row, filled] == -1
+    # the variant whose warps share their pieces gives the same attention (other rounding order)
+    cabi.set_tuning(force_generic=4)
+    try:
+        shared = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+    finally:
+        cabi.set_tuning()
+    assert_attention_close(shared, expected, dtype=dtype)
+
+
+def test_solo_variant_with_too_few_slots_for_an_even_split(package, oracle, cuda_device):
+    """Forced onto a batch it would not be chosen for: one long sequence among short ones and
+    two slots only, so a warp's block grows to the longest sequence and most warps idle.  Slow,
+    but every sequence still fits its slots and the result is the oracle's."""
+    lengths = [2000] + [40] * 30 + [0, 700]
+    host, dev = _fast_path_inputs(cuda_device, lengths, seed=77, value_scale=0.5, poison=True)
+    expected = oracle.paged_attention(*host)
+    for split_k in (2, 5):
+        package.cabi.set_tuning(force_generic=5)
+        try:
+            out = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
+        finally:
+            package.cabi.set_tuning()
+        assert package.cabi.device_status() == 0
+        assert_attention_close(out, expected)
+
+
+def test_row_per_warp_combine_equals_row_per_cta_combine(package, cuda_device):
+    """2 048 or more (sequence, head) rows take the combine that gives a row to a warp; same
+    operations in the same order as the one-CTA-per-row kernel, so the same bits.  Checked on
+    the same partials through the combine entry point: 171 sequences (2 052 rows) at once, and
+    in two halves that each stay below the bound."""
+    torch.manual_seed(9)
+    batch, split_k = 171, 6
+    po = torch.randn(batch, split_k, 12, 128, device=cuda_device)
+    pm = torch.randn(batch, split_k, 12, device=cuda_device) * 3
+    ps = torch.rand(batch, split_k, 12, device=cuda_device) + 0.1
+    pm[3, 2:] = float("-inf")
+    ps[3, 2:] = 0
+    ps[5] = 0  # a row without any mass
+    splitk = package.kernel_module("paged_decode_grouped_splitk")
+    whole = splitk.splitk_reduce(po, pm, ps, torch.full((batch, 12, 128), float("nan"), dtype=torch.float16,
+                                                        device=cuda_device))
+    halves = torch.full_like(whole, float("nan"))
+    splitk.splitk_reduce(po[:90], pm[:90], ps[:90], halves[:90])
+    splitk.splitk_reduce(po[90:], pm[90:], ps[90:], halves[90:])
+    assert torch.isfinite(whole.float()).all()
+    assert torch.equal(whole, halves)
+
+
 def test_misaligned_partial_buffer_keeps_off_the_vector_store_kernel(package, cuda_device):
     """The tensor-core kernel stores partial rows as 16-byte vectors.  A partial buffer that
     starts on a 4-byte boundary (a slice of a larger fp32 arena) must therefore be planned for

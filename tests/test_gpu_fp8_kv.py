@@ -112,10 +112,10 @@ def test_fp8_fixed_scale_write(package, oracle, cuda_device):
     assert torch.equal(k8_b, k8_dev) and torch.equal(v8_b, v8_dev)
 
 
-@pytest.mark.parametrize("mode", [3, 4], ids=["cuda_core", "tensor_core"])
+@pytest.mark.parametrize("mode", [3, 4, 5], ids=["cuda_core", "tensor_core", "tensor_core_solo"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_fp8_persistent_kernels(package, oracle, cuda_device, mode, dtype):
-    """Both persistent kernels on FP8 pools (forced, whatever the batch size): mixed
+    """The persistent kernels on FP8 pools (forced, whatever the batch size): mixed
     lengths with empty and one-token sequences, NaN bytes in the unused tail of every
     last page, per-page scales that differ by orders of magnitude, a bad page id."""
     generator = torch.Generator().manual_seed(17)
@@ -136,7 +136,7 @@ def test_fp8_persistent_kernels(package, oracle, cuda_device, mode, dtype):
             v8[page, length % 16:] = 0x7F
     expected = oracle.paged_attention(q, oracle.dequantize_pages(k8.cpu(), ks.cpu(), dtype=dtype),
                                       oracle.dequantize_pages(v8.cpu(), vs.cpu(), dtype=dtype), table, lens)
-    for split_k in (2, 5):
+    for split_k in (2, 5, 22):
         package.cabi.set_tuning(force_generic=mode)
         try:
             out = package.grouped_splitk_decode_attention_fp8(

@@ -42,9 +42,17 @@ def _inputs(device, lengths, dtype=torch.float16, seed=0, index_dtype=torch.int3
 
 
 def _pair(package, case, split_k):
+    """The two operators; the attention through the variant of the tensor-core kernel that the
+    fused step is built on (warps share their pieces), so that the results can be compared bit
+    for bit also where the plain call would pick the solo variant (many short sequences)."""
     k_pool, v_pool = case["k_pool"].clone(), case["v_pool"].clone()
     q = package.packed_qkv_rope_cache(case["packed"], case["positions"], case["slots"], k_pool, v_pool)
-    out = package.grouped_splitk_decode_attention(q, k_pool, v_pool, case["table"], case["lens"], split_k=split_k)
+    if split_k > 1:
+        package.cabi.set_tuning(force_generic=4)
+    try:
+        out = package.grouped_splitk_decode_attention(q, k_pool, v_pool, case["table"], case["lens"], split_k=split_k)
+    finally:
+        package.cabi.set_tuning()
     return out, k_pool, v_pool
 
 
