@@ -27,7 +27,9 @@ Rank 0 prints ONE JSON line.
              time, measured here with CUDA events over a graph of one launch per
              layer (28 different pools, 3.9 GB: nothing is served from L2).
   workloads  the other four benchmark configurations, each with its own parity check,
-             step time and partial-pass roofline (one GPU).
+             step time and partial-pass roofline (one GPU); and `short_b512`, which is
+             not one of the five: 512 sequences of 100 tokens, the regime in which the
+             attention call picks the tensor-core kernel's solo variant.
   strong_sweep_b256  the batch of 256 sequences partitioned by sequence over the N
              ranks (snake dealing by length), tokens/s = 256 / slowest rank's step.
   cpu_baseline  the reference's own PyTorch path (staged under oracle/_ref/) on the
@@ -63,7 +65,8 @@ LAYERS = 28
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126e6
-OTHER_WORKLOADS = ("cpu_single_layer_b8", "sweep_b256", "long_skew_b4", "fp8_b128")
+# the other four benchmark configurations, and one extra: the many-short-sequences regime
+OTHER_WORKLOADS = ("cpu_single_layer_b8", "sweep_b256", "long_skew_b4", "fp8_b128", "short_b512")
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the
 # ncu captures summarised beside this file (same per-launch workload as a full-size launch:
 # one layer of the named workload at seed 0).  Workloads without a capture report null.
@@ -240,6 +243,9 @@ def partial_kernel_bytes(package, workload, split_k, fp8, kernel, ctas_per_head)
         return total + batch * 12 * 128 * 2
     if kernel == "decode_partial_kernel":
         return total + batch * split_k * 12 * 130 * 4
+    if kernel == "decode_mma_kernel (solo)":
+        _, pieces = package.kv_layout.solo_schedule(lengths, split_k=split_k, ctas_per_head=ctas_per_head)
+        return total + 2 * len(pieces) * 6 * 130 * 4
     tensor_core = kernel == "decode_mma_kernel"
     _, pieces = package.kv_layout.persistent_schedule(
         lengths, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=16 if tensor_core else 32,

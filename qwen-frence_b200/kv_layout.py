@@ -197,6 +197,34 @@ def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SI
     return share, pieces
 
 
+def solo_schedule(seq_lens, *, split_k, ctas_per_head, warps=8, unit_tokens=PAGE_SIZE):
+    """Host restatement of how the tensor-core kernel's solo variant cuts one KV head's work.
+
+    The sequences' pages are concatenated (no empty units); warp w of CTA c takes pages
+    [(c * warps + w) * block, +block) with block = max(ceil(ceil(total / ctas_per_head) /
+    warps), ceil(longest / (split_k - 1))), and every stretch of one sequence inside a block
+    is a piece that goes to split slot (its block) - (the block of the sequence's first page).
+    Returns (block, pieces), a piece being (block number, sequence, first page within the
+    sequence, pages, split slot)."""
+    if split_k < 2 or ctas_per_head < 1:
+        raise ValueError("the persistent kernels need split_k >= 2 and at least one CTA per head")
+    data = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
+    total, longest = sum(data), max(data, default=0)
+    if total == 0:
+        return 0, []
+    block = max(-(-(-(-total // ctas_per_head)) // warps), -(-longest // (split_k - 1)))
+    pieces, first = [], 0
+    for sequence, count in enumerate(data):
+        position = first
+        while position < first + count:
+            number = position // block
+            stop = min(first + count, (number + 1) * block)
+            pieces.append((number, sequence, position - first, stop - position, number - first // block))
+            position = stop
+        first += count
+    return block, pieces
+
+
 def kv_bytes_per_layer(seq_lens, *, kv_heads=KV_HEADS, head_dim=HEAD_DIM, elem_bytes=2):
     """Unique K+V bytes one layer's attention must read: sum_b T_b * 2 * kv * D * e
     (same count as unique_bytes in

@@ -31,6 +31,9 @@ WORKLOADS = {
                          doc="28 layers, batch 4, contexts 32768/16384/4096/512"),
     "fp8_b128": dict(layers=28, batch=128, fp8=True,
                      doc="28 layers, batch 128, context 2048, e4m3 pools with per-page scales"),
+    # not one of the five benchmark configurations: the many-short-sequences regime
+    "short_b512": dict(layers=28, batch=512, fp8=False,
+                       doc="28 layers, batch 512, context 100 (seven pages per sequence)"),
 }
 
 
@@ -52,6 +55,8 @@ def context_lengths(name, seed=0, batch=None):
         return [base[i % 4] for i in range(batch)]
     if name == "fp8_b128":
         return [2048] * batch
+    if name == "short_b512":
+        return [100] * batch
     raise KeyError(name)
 
 

@@ -541,17 +541,19 @@ def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device
     expected = oracle.paged_attention(*host)
     assert_attention_close(out, expected, dtype=dtype)
     assert (out[0] == 0).all() and (out[7] == 0).all()
-    # slots: filled from 0 without gaps, then the end mark (sum -1) unless every slot is used
+    # slots: those of the host restatement of the schedule, filled from 0 without gaps, then
+    # the end mark (sum -1) unless every slot is used
+    ctas_per_head = cabi.fused_kernel_plan(args)[1]
+    block, pieces = package.kv_layout.solo_schedule(lengths, split_k=split_k, ctas_per_head=ctas_per_head)
+    slots = [0] * batch
+    for _, sequence, _, _, slot in pieces:
+        assert slot == slots[sequence] and slot < split_k
+        slots[sequence] += 1
     sums = partials[2][:, :, 0].cpu()
     for row, length in enumerate(lengths):
-        if length == 0:
-            continue
-        filled = 0
-        while filled < split_k and sums[row, filled] > 0:
-            filled += 1
-        assert filled >= 1
-        if filled < split_k:
-            assert sums[row, filled] == -1
+        assert (sums[row, :slots[row]] > 0).all()
+        if length and slots[row] < split_k:
+            assert sums[row, slots[row]] == -1
     # the variant whose warps share their pieces gives the same attention (other rounding order)
     cabi.set_tuning(force_generic=4)
     try:

@@ -358,3 +358,35 @@ def test_persistent_schedule_respects_split_slots(package):
         assert all(s == list(range(len(s))) for s in slots.values())
     with pytest.raises(ValueError):
         schedule([5], split_k=1, ctas_per_head=4)
+
+
+def test_solo_schedule_covers_every_page_once_within_the_slots(package):
+    """Host restatement of the solo variant's cut: every page of every sequence in exactly one
+    piece, a warp's pieces inside its block, slots counted from 0 per sequence without gaps and
+    below split_k -- also when the slot limit, not the page count, sets the block."""
+    import random
+
+    kv_layout = package.kv_layout
+    random.seed(3)
+    for split_k, ctas, lengths in (
+            (3, 74, [random.randint(0, 1024) for _ in range(300)]),
+            (2, 74, [100] * 600),
+            (2, 74, [2000] + [40] * 30 + [0, 700]),
+            (8, 148, [1] * 90),
+            (4, 74, [0, 0, 0])):
+        block, pieces = kv_layout.solo_schedule(lengths, split_k=split_k, ctas_per_head=ctas)
+        pages = [-(-n // 16) for n in lengths]
+        if sum(pages) == 0:
+            assert pieces == []
+            continue
+        assert block * 8 * ctas >= sum(pages) and block * (split_k - 1) >= max(pages)
+        seen = [0] * len(lengths)
+        next_slot = [0] * len(lengths)
+        for number, sequence, first, count, slot in pieces:
+            assert count >= 1 and first == seen[sequence]
+            seen[sequence] += count
+            assert slot == next_slot[sequence] < split_k
+            next_slot[sequence] += 1
+            start = sum(pages[:sequence]) + first
+            assert number * block <= start and start + count <= (number + 1) * block
+        assert seen == pages
