@@ -77,6 +77,7 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {  # (workload, seed, kernel): (bytes, split_k of
     ("sweep_b256", 0, "decode_mma_kernel"): (409.63e6 + 3.54e6, 3),
     ("long_skew_b4", 0, "decode_mma_kernel+rope"): (55.17e6 + 0.01e6, 148),  # the partials stay in L2
     ("fp8_b128", 0, "decode_mma_kernel"): (135.19e6 + 1.92e6, 5),
+    ("short_b512", 0, "decode_mma_kernel (solo)"): (54.60e6 + 0.17e6, 3),  # the partials stay in L2
 }
 
 
