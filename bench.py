@@ -82,7 +82,8 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {  # (workload, seed, kernel): (bytes, split_k of
 
 
 # --kernel -> qf_set_tuning mode: profiling and A/B runs of the other partial-pass kernels
-KERNEL_MODES = {"auto": 0, "partitioned": 2, "persistent_cuda_core": 3, "persistent_mma": 4}
+KERNEL_MODES = {"auto": 0, "partitioned": 2, "persistent_cuda_core": 3, "persistent_mma": 4,
+                "persistent_mma_solo": 5}
 
 
 def parse_args():

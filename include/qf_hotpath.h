@@ -232,8 +232,10 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
  * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math; only when forced
  * with qf_set_tuning), QF_KERNEL_PERSISTENT_MMA (tensor-core math, 16-bit and FP8
  * pools) or QF_KERNEL_PERSISTENT_MMA_SOLO (the same kernel with every warp keeping its
- * pieces of the sequences to itself: block tables of at most 64 pages and
- * batch * (split_k - 1) >= 8 * ctas_per_head, i.e. many short sequences); *ctas_per_head
+ * pieces of the sequences to itself, chosen when there are split slots enough for that:
+ * batch * (split_k - 1) >= 16 * ctas_per_head for 16-bit pools, or 8 * ctas_per_head for
+ * block tables of at most 64 pages (16-bit and FP8 pools);
+ * kv_layout.plan_split_k_for_lengths picks split_k accordingly); *ctas_per_head
  * is the number of resident CTAs that share one KV head's pages (0 for
  * QF_KERNEL_PARTITIONED). */
 #define QF_KERNEL_PARTITIONED 0
@@ -467,8 +469,8 @@ int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* time
  * those older pages before its dependency wait, while the kernels before it drain.  The
  * newest token's page is only copied after this kernel itself has stored the new row.
  * QF_EUNSUPPORTED unless: 16-bit pools, 12 + 2 heads, split_k >= 2, and arguments for
- * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA (or its
- * _SOLO variant: the fused step then still runs the kernel whose warps share their pieces);
+ * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA or its
+ * _SOLO variant (the fused step runs the same variant);
  * callers then run qf_rope_kv_write and qf_grouped_splitk_decode_attention.
  * `stages`: QF_STAGE_PARTIAL | QF_STAGE_COMBINE for the whole step; one of them alone
  * launches only that kernel (timing). */

@@ -339,12 +339,13 @@ __global__ void __launch_bounds__(256) splitk_reduce_small_kernel(const ReducePa
   }
 }
 
-// The same combine for large batches (thousands of (sequence, head) rows): one WARP per row
-// instead of one CTA, eight rows per CTA, a lane four dimensions (one 16-byte load per slot).
-// Same operations in the same order as the kernel above, so the same bits; needs head_dim
-// 128, unit dimension strides and 16-byte aligned rows.  At 512 sequences the one-CTA-per-row
-// grid is 6 144 CTAs and takes 7.6 us per layer, at 1 024 sequences 14 us.
-constexpr int kRowsReduceMinRows = 2048;
+// The same combine with one WARP per (sequence, head) row instead of one CTA: eight rows per
+// CTA, a lane four dimensions (one 16-byte load per slot).  Same operations in the same order
+// as the kernel above, so the same bits; needs head_dim 128, unit dimension strides and
+// 16-byte aligned rows, and is then used for every batch: at 512 sequences the one-CTA-per-row
+// grid is 6 144 CTAs and took 7.6 us per layer against 3.4 (1 024 sequences: 14 against 5),
+// and at 64 sequences with ten filled slots per row a step of 28 layers went from 0.837 to
+// 0.829 ms.
 
 template <typename T, bool STREAMED>
 __global__ void __launch_bounds__(256) splitk_reduce_rows_kernel(const ReduceParams p, int rows) {
@@ -687,7 +688,7 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
 // side) and partial buffers carved out at a 4-byte offset take the CUDA-core persistent
 // kernel, which keeps separate strides and stores partials element by element.
 enum class FusedKernel { kPartitioned, kStreamed, kTensorCore, kTensorCoreSolo };
-constexpr int64_t kSoloTablePages = 64;  // block tables up to this width (1 024 tokens) may take the solo variant
+constexpr int64_t kSoloTablePages = 64;  // block tables up to this width (1 024 tokens): the lower slot bound
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   const int mode = g_force_generic;  // 0 automatic, 3 / 4 / 5 force a persistent kernel (tests)
@@ -705,19 +706,28 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   const bool tensor_core = mode != 3 && same_strides && aligned16(a->partial_out);
   if ((mode == 4 || mode == 5) && !tensor_core) return FusedKernel::kPartitioned;
   if (tensor_core && mode != 4) {
-    // Many short sequences: every warp keeps its pieces to itself.  Chosen from what the host
-    // knows -- no sequence is longer than the table is wide (at most kSoloTablePages pages),
-    // and even if every sequence were that long each warp of the grid would get a block of
-    // its own without a sequence needing more than split_k slots: batch * (split_k - 1) >=
-    // warps per KV head.  Measured against the variant that shares pieces among a CTA's warps
-    // (partial pass per layer): 512 x 100 tokens 12.3 against 24.7 us, 1 024 x 60 14.9 against
-    // 35.2, 256 x 200 11.8 against 18.8, 512 x 400 36.8 against 46.0; equal at 128 x 700
-    // (20.2 / 20.1) and slower below the batch bound (64 x 200: 9.4 against 7.5).
+    // Every warp keeps its pieces to itself (no deposits, no merges, no empty units) when there
+    // are split slots enough for it: a warp's block must hold longest / (split_k - 1) pages,
+    // and it should not have to be larger than an even share of the pages for that.  The host
+    // only knows that no sequence is longer than the table is wide.  If every sequence had
+    // that length, batch * (split_k - 1) >= warps per KV head would do; the test asks for
+    // twice that (sequences half the table's width on average), except for tables of at most
+    // kSoloTablePages pages, where a block that comes out too large costs little.  Measured
+    // against the variant that shares pieces among a CTA's warps (partial pass per layer):
+    // 512 x 100 tokens 12.3 against 24.7 us, 1 024 x 60 14.9 against 35.2, 256 x 200 11.8
+    // against 18.8, 512 x 400 36.8 against 46.0, equal at 128 x 700 (20.2 / 20.1), slower below
+    // the bound (64 x 200: 9.4 against 7.5); 64 x U[128, 4096] tokens with 24 slots 24.1 against
+    // 26.2 (with 12 slots, below the bound, 27.2), 256 x log-uniform [64, 8192] with 14 slots
+    // 68.7 against 75.3; 4 sequences of up to 32 768 tokens never have the slots (17.7
+    // against 14.5 us with 148).
     const int64_t warps_per_head =
         static_cast<int64_t>(mma_ctas_on_current_device(a->kv_fp8 != 0) / a->kv_heads) * 8;
-    const bool many_short = a->table_width <= kSoloTablePages &&
-                            static_cast<int64_t>(a->batch) * (a->split_k - 1) >= warps_per_head;
-    if (mode == 5 || many_short) return FusedKernel::kTensorCoreSolo;
+    const int64_t slots = static_cast<int64_t>(a->batch) * (a->split_k - 1);
+    // (FP8 pools, wide tables: the partial pass gains 1 us of 28 on 128 x 2 048 tokens, the
+    // combine, with ten slots to read per row instead of three, loses 2: not chosen)
+    const bool enough_slots = a->table_width <= kSoloTablePages ? slots >= warps_per_head
+                                                                : !a->kv_fp8 && slots >= 2 * warps_per_head;
+    if (mode == 5 || enough_slots) return FusedKernel::kTensorCoreSolo;
   }
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
@@ -811,7 +821,7 @@ void launch_reduce_typed(const ReduceParams& r, unsigned blocks, int threads, bo
   const bool vector_rows = r.head_dim == 128 && r.po_sd == 1 && r.o_sd == 1 && aligned16(r.po) &&
                            ((r.po_sb | r.po_sk | r.po_sh | r.o_sb | r.o_sh) & 3) == 0 &&
                            (reinterpret_cast<uintptr_t>(r.out) & 7) == 0;
-  if (small && vector_rows && blocks >= static_cast<unsigned>(kRowsReduceMinRows)) {
+  if (small && vector_rows) {
     const int rows = static_cast<int>(blocks);
     const dim3 grid((blocks + 7) / 8), cta(256);
     if (streamed) {
@@ -997,8 +1007,13 @@ int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const 
   rope.table = reinterpret_cast<const float2*>(rope_table), rope.table_positions = table_positions;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (stages & QF_STAGE_PARTIAL) {
-    rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true>(p, s, rope)
-                                     : qf::launch_mma<__nv_bfloat16, false, false, true>(p, s, rope);
+    if (qf::choose_fused_kernel(args) == qf::FusedKernel::kTensorCoreSolo) {
+      rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true, true>(p, s, rope)
+                                       : qf::launch_mma<__nv_bfloat16, false, false, true, true>(p, s, rope);
+    } else {
+      rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true>(p, s, rope)
+                                       : qf::launch_mma<__nv_bfloat16, false, false, true>(p, s, rope);
+    }
     if (rc != QF_OK) return rc;
   }
   if (!(stages & QF_STAGE_COMBINE)) return QF_OK;

@@ -232,7 +232,7 @@ template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = fal
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
   static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
-  static_assert(!(SOLO && (ROPE || PROFILE)), "the solo variant is the plain attention pass");
+  static_assert(!(SOLO && PROFILE), "the instrumented variant is the one whose warps share their pieces");
   constexpr int kOverhead = SOLO ? 0 : kPieceOverhead;  // empty units in front of a sequence
   constexpr int kStep = SOLO ? 1 : kMmaWarps;          // distance between a warp's units
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;

@@ -144,6 +144,36 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
     return split_k
 
 
+def plan_split_k_for_lengths(seq_lens, *, table_pages=None, fp8=False, kv_heads=KV_HEADS, page_size=PAGE_SIZE,
+                             sm_count=148, max_slots=32):
+    """Split count from the batch's actual lengths, which a scheduler knows on the host.
+
+    Aims at the tensor-core kernel's solo variant (every warp keeps its pieces to itself, the
+    faster one wherever it has the slots): enough slots that a warp's block need not be larger
+    than an even share of the pages, ceil(longest / block) + 1 with block = ceil(ceil(total /
+    CTAs per head) / 8), and enough for the library to choose the variant, batch * (split_k - 1)
+    >= 2 * warps per head (1 * for block tables of at most SOLO_TABLE_PAGES pages).  Batches that
+    would need more than `max_slots` (few very long sequences) keep plan_split_k's choice."""
+    lengths = [max(int(t), 0) for t in seq_lens]
+    batch = len(lengths)
+    if batch == 0:
+        return 1
+    fallback = plan_split_k(batch, max(max(lengths), 1), kv_heads=kv_heads, page_size=page_size, sm_count=sm_count)
+    pages = [-(-t // page_size) for t in lengths]
+    total, longest = sum(pages), max(pages)
+    if total == 0:
+        return fallback
+    ctas_per_head = max(1, sm_count * (2 if fp8 else 1) // kv_heads)
+    warps_per_head = ctas_per_head * 8
+    block = -(-(-(-total // ctas_per_head)) // 8)
+    width = longest if table_pages is None else int(table_pages)
+    if fp8 and width > SOLO_TABLE_PAGES:
+        return fallback  # the library keeps FP8 pools with wide tables on the variant that shares pieces
+    factor = 1 if width <= SOLO_TABLE_PAGES else 2
+    split_k = max(-(-longest // block) + 1, -(-factor * warps_per_head // batch) + 1)
+    return split_k if split_k <= max_slots else fallback
+
+
 # Widest block table (pages) and smallest batch for which plan_split_k aims at the solo
 # variant of the tensor-core kernel (kSoloTablePages in csrc/qf_decode_attention.cu).
 SOLO_TABLE_PAGES = 64

@@ -521,8 +521,7 @@ def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device
     """Block tables of at most 64 pages and batch * (split_k - 1) >= the warps that share a KV
     head: every warp keeps its stretch of the page list to itself and stores each sequence's
     part of it to a split slot of its own.  Lengths from 0 tokens to the full table, page
-    boundaries on both sides, NaN tails, NaN-filled partial buffers; 300 and 600 rows of 12
-    heads also take the one-warp-per-row combine."""
+    boundaries on both sides, NaN tails, NaN-filled partial buffers."""
     generator = torch.Generator().manual_seed(batch + split_k)
     lengths = torch.randint(0, 1025, (batch,), generator=generator).tolist()
     lengths[:8] = [0, 1, 15, 16, 17, 1023, 1024, 0]
@@ -581,10 +580,10 @@ def test_solo_variant_with_too_few_slots_for_an_even_split(package, oracle, cuda
 
 
 def test_row_per_warp_combine_equals_row_per_cta_combine(package, cuda_device):
-    """2 048 or more (sequence, head) rows take the combine that gives a row to a warp; same
-    operations in the same order as the one-CTA-per-row kernel, so the same bits.  Checked on
-    the same partials through the combine entry point: 171 sequences (2 052 rows) at once, and
-    in two halves that each stay below the bound."""
+    """Contiguous partials and output take the combine that gives a (sequence, head) row to a
+    warp; an output whose rows are 130 elements apart (no 8-byte stores possible) keeps the
+    one-CTA-per-row kernel.  Same operations in the same order, so the same bits, on the same
+    partials through the combine entry point."""
     torch.manual_seed(9)
     batch, split_k = 171, 6
     po = torch.randn(batch, split_k, 12, 128, device=cuda_device)
@@ -593,14 +592,16 @@ def test_row_per_warp_combine_equals_row_per_cta_combine(package, cuda_device):
     pm[3, 2:] = float("-inf")
     ps[3, 2:] = 0
     ps[5] = 0  # a row without any mass
+    po[7, 4:] = float("nan")  # slots without mass may hold anything
+    ps[7, 4:] = 0
     splitk = package.kernel_module("paged_decode_grouped_splitk")
-    whole = splitk.splitk_reduce(po, pm, ps, torch.full((batch, 12, 128), float("nan"), dtype=torch.float16,
-                                                        device=cuda_device))
-    halves = torch.full_like(whole, float("nan"))
-    splitk.splitk_reduce(po[:90], pm[:90], ps[:90], halves[:90])
-    splitk.splitk_reduce(po[90:], pm[90:], ps[90:], halves[90:])
-    assert torch.isfinite(whole.float()).all()
-    assert torch.equal(whole, halves)
+    by_warp = splitk.splitk_reduce(po, pm, ps, torch.full((batch, 12, 128), float("nan"), dtype=torch.float16,
+                                                          device=cuda_device))
+    padded = torch.full((batch, 12, 130), float("nan"), dtype=torch.float16, device=cuda_device)
+    by_cta = splitk.splitk_reduce(po, pm, ps, padded[:, :, :128])
+    assert torch.isfinite(by_warp.float()).all()
+    assert torch.equal(by_warp, by_cta)
+    assert torch.isnan(padded[:, :, 128:].float()).all()
 
 
 def test_misaligned_partial_buffer_keeps_off_the_vector_store_kernel(package, cuda_device):

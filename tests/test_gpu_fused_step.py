@@ -42,17 +42,12 @@ def _inputs(device, lengths, dtype=torch.float16, seed=0, index_dtype=torch.int3
 
 
 def _pair(package, case, split_k):
-    """The two operators; the attention through the variant of the tensor-core kernel that the
-    fused step is built on (warps share their pieces), so that the results can be compared bit
-    for bit also where the plain call would pick the solo variant (many short sequences)."""
+    """The two operators.  The attention call and the fused step pick the variant of the
+    tensor-core kernel by the same rule (warps sharing their pieces, or each keeping its own
+    where the split slots allow), so their results can be compared bit for bit."""
     k_pool, v_pool = case["k_pool"].clone(), case["v_pool"].clone()
     q = package.packed_qkv_rope_cache(case["packed"], case["positions"], case["slots"], k_pool, v_pool)
-    if split_k > 1:
-        package.cabi.set_tuning(force_generic=4)
-    try:
-        out = package.grouped_splitk_decode_attention(q, k_pool, v_pool, case["table"], case["lens"], split_k=split_k)
-    finally:
-        package.cabi.set_tuning()
+    out = package.grouped_splitk_decode_attention(q, k_pool, v_pool, case["table"], case["lens"], split_k=split_k)
     return out, k_pool, v_pool
 
 
@@ -70,7 +65,9 @@ def _fused(package, case, split_k):
     ([513] * 8, 4),
     ([700, 9, 31, 1500, 64, 65, 3, 48, 1024, 1025, 250, 16], 6),
     ([9000], 3),                                    # one sequence cut into pieces by the slot limit
-    (list(range(1, 130)), 10),                      # many short sequences: several pieces per CTA
+    (list(range(1, 130)), 10),                      # many short sequences: the solo variant (slots to spare)
+    (list(range(1, 130)), 4),                       # ... and, with few slots, the variant that shares pieces
+    ([3000, 100, 2000, 16, 4096] * 16, 32),         # long sequences with slots enough for the solo variant
 ])
 def test_same_pools_and_output_as_the_two_operators(package, oracle, cuda_device, dtype, lengths, split_k):
     case = _inputs(cuda_device, lengths, dtype=dtype, seed=len(lengths))
