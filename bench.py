@@ -816,6 +816,7 @@ def partial_pass_leg(package, step, timer, steps, repeats, seed, world):
         # and its 512 B of the rotation table are read, the new K and V rows (2 x 2 x 128 x 2 B) written
         launch_bytes += workload.batch * ((2048 - 1536) * 2 + 4 + 512 + 2 * 2 * 128 * 2)
     achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
+    kv_bytes = package.kv_layout.kv_bytes_per_layer(workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2)
     traffic = None
     captured = NCU_TRAFFIC_BYTES_PER_LAUNCH.get((workload.name, seed, kernel_name + ("+rope" if step.fused_write else "")))
     if world == 1 and captured is not None and step.split_k == captured[1] and step.layers == LAYERS:
@@ -827,8 +828,9 @@ def partial_pass_leg(package, step, timer, steps, repeats, seed, world):
         "fused_write": step.fused_write, "same_pass_without_the_write": without_write,
         "algorithmic_bytes_per_launch": launch_bytes, "us_per_launch": kernel_ms * 1e3,
         "us_per_launch_min_max": [min(launch_ms) * 1e3, max(launch_ms) * 1e3],
-        "kv_bytes_per_launch": package.kv_layout.kv_bytes_per_layer(
-            workload.seq_lens.tolist(), elem_bytes=1 if step.fp8 else 2),
+        "kv_bytes_per_launch": kv_bytes,
+        # the K/V bytes alone over the same time (the pieces a launch writes are not counted)
+        "frac_kv_only": kv_bytes / (kernel_ms * 1e-3) / 1e9 / peak,
     }
 
 
@@ -868,7 +870,7 @@ def measure_workload(package, oracle, name, device, timer, args, world, rank, sc
     leg = partial_pass_leg(package, step, timer, args.steps, min(args.repeats, 5), args.seed, world)
     record["roofline"] = {k: leg[k] for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "peak_kind",
                                               "frac_of_nominal_8TBs", "traffic", "algorithmic_bytes_per_launch",
-                                              "us_per_launch", "kv_bytes_per_launch")}
+                                              "us_per_launch", "kv_bytes_per_launch", "frac_kv_only")}
     step_bytes = step_algorithmic_bytes(package, step, leg)
     record["step_gbs"] = step_bytes / (statistics.median(own) * 1e-3) / 1e9
     record["step_frac"] = record["step_gbs"] / leg["peak"]

@@ -145,7 +145,7 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
 
 
 def plan_split_k_for_lengths(seq_lens, *, table_pages=None, fp8=False, kv_heads=KV_HEADS, page_size=PAGE_SIZE,
-                             sm_count=148, max_slots=32):
+                             sm_count=148, max_slots=64):
     """Split count from the batch's actual lengths, which a scheduler knows on the host.
 
     Aims at the tensor-core kernel's solo variant (every warp keeps its pieces to itself, the
@@ -153,7 +153,9 @@ def plan_split_k_for_lengths(seq_lens, *, table_pages=None, fp8=False, kv_heads=
     than an even share of the pages, ceil(longest / block) + 1 with block = ceil(ceil(total /
     CTAs per head) / 8), and enough for the library to choose the variant, batch * (split_k - 1)
     >= 2 * warps per head (1 * for block tables of at most SOLO_TABLE_PAGES pages).  Batches that
-    would need more than `max_slots` (few very long sequences) keep plan_split_k's choice."""
+    would need more than `max_slots` (few very long sequences) keep plan_split_k's choice: measured
+    on by-sequence shards of 256 log-uniform lengths, 64 sequences with 46 slots gain 4 % per step
+    over that choice, 32 sequences with 96 slots lose 7 %."""
     lengths = [max(int(t), 0) for t in seq_lens]
     batch = len(lengths)
     if batch == 0:
