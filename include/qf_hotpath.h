@@ -231,11 +231,10 @@ int qf_grouped_splitk_decode_attention_stages(const qf_decode_attention_args* ar
  * QF_KERNEL_PARTITIONED (one CTA per sequence, KV head and split; also the
  * stride-generic kernel), QF_KERNEL_PERSISTENT (CUDA-core math; only when forced
  * with qf_set_tuning), QF_KERNEL_PERSISTENT_MMA (tensor-core math, 16-bit and FP8
- * pools) or QF_KERNEL_PERSISTENT_MMA_SOLO (the same kernel with every warp keeping its
- * pieces of the sequences to itself, chosen when there are split slots enough for that:
- * batch * (split_k - 1) >= 16 * ctas_per_head for 16-bit pools, or 8 * ctas_per_head for
- * block tables of at most 64 pages (16-bit and FP8 pools);
- * kv_layout.plan_split_k_for_lengths picks split_k accordingly); *ctas_per_head
+ * pools; only behind qf_set_tuning mode 4 and as the instrumented kernel) or
+ * QF_KERNEL_PERSISTENT_MMA_SOLO (the tensor-core kernel of every call whose layout allows
+ * it: each warp streams a block of consecutive pages on its own, and what a CTA's warps hold
+ * of one sequence is merged once, at the CTA's end); *ctas_per_head
  * is the number of resident CTAs that share one KV head's pages (0 for
  * QF_KERNEL_PARTITIONED). */
 #define QF_KERNEL_PARTITIONED 0

@@ -688,7 +688,6 @@ FastParams fast_params(const qf_decode_attention_args* a, void* out, long long* 
 // side) and partial buffers carved out at a 4-byte offset take the CUDA-core persistent
 // kernel, which keeps separate strides and stores partials element by element.
 enum class FusedKernel { kPartitioned, kStreamed, kTensorCore, kTensorCoreSolo };
-constexpr int64_t kSoloTablePages = 64;  // block tables up to this width (1 024 tokens): the lower slot bound
 
 FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   const int mode = g_force_generic;  // 0 automatic, 3 / 4 / 5 force a persistent kernel (tests)
@@ -705,30 +704,15 @@ FusedKernel choose_fused_kernel(const qf_decode_attention_args* a) {
   // ... and stores a piece's partial rows as 16-byte vectors
   const bool tensor_core = mode != 3 && same_strides && aligned16(a->partial_out);
   if ((mode == 4 || mode == 5) && !tensor_core) return FusedKernel::kPartitioned;
-  if (tensor_core && mode != 4) {
-    // Every warp keeps its pieces to itself (no deposits, no merges, no empty units) when there
-    // are split slots enough for it: a warp's block must hold longest / (split_k - 1) pages,
-    // and it should not have to be larger than an even share of the pages for that.  The host
-    // only knows that no sequence is longer than the table is wide.  If every sequence had
-    // that length, batch * (split_k - 1) >= warps per KV head would do; the test asks for
-    // twice that (sequences half the table's width on average), except for tables of at most
-    // kSoloTablePages pages, where a block that comes out too large costs little.  Measured
-    // against the variant that shares pieces among a CTA's warps (partial pass per layer):
-    // 512 x 100 tokens 12.3 against 24.7 us, 1 024 x 60 14.9 against 35.2, 256 x 200 11.8
-    // against 18.8, 512 x 400 36.8 against 46.0, equal at 128 x 700 (20.2 / 20.1), slower below
-    // the bound (64 x 200: 9.4 against 7.5); 64 x U[128, 4096] tokens with 24 slots 24.1 against
-    // 26.2 (with 12 slots, below the bound, 27.2), 256 x log-uniform [64, 8192] with 14 slots
-    // 68.7 against 75.3; 4 sequences of up to 32 768 tokens never have the slots (17.7
-    // against 14.5 us with 148).
-    const int64_t warps_per_head =
-        static_cast<int64_t>(mma_ctas_on_current_device(a->kv_fp8 != 0) / a->kv_heads) * 8;
-    const int64_t slots = static_cast<int64_t>(a->batch) * (a->split_k - 1);
-    // (FP8 pools, wide tables: the partial pass gains 1 us of 28 on 128 x 2 048 tokens, the
-    // combine, with ten slots to read per row instead of three, loses 2: not chosen)
-    const bool enough_slots = a->table_width <= kSoloTablePages ? slots >= warps_per_head
-                                                                : !a->kv_fp8 && slots >= 2 * warps_per_head;
-    if (mode == 5 || enough_slots) return FusedKernel::kTensorCoreSolo;
-  }
+  // The solo variant (every warp streams a block of consecutive pages on its own; what a CTA's
+  // warps hold of one sequence is merged once, at the CTA's end) is the tensor-core kernel of
+  // every call; the variant whose warps interleave over the pages and merge piece by piece
+  // remains as the instrumented kernel and behind mode 4.  Measured step times, solo against
+  // interleaved, same split counts: 64 x U[128, 4096] tokens 0.782 against 0.824 ms, 256 x
+  // log-uniform [64, 8192] 2.120 against 2.346, 4 sequences of up to 32 768 tokens 0.530 against
+  // 0.531, FP8 128 x 2 048 1.022 against 1.032, 8 x 513 tokens (one layer) 14.6 against 14.5 us;
+  // 512 x 100 tokens: partial pass 11.8 against 24.7 us.
+  if (tensor_core && mode != 4) return FusedKernel::kTensorCoreSolo;
   return tensor_core ? FusedKernel::kTensorCore : FusedKernel::kStreamed;
 }
 

@@ -220,14 +220,20 @@ struct RopeInputs {
 };
 
 //
-// SOLO (batches of many short sequences): warp w owns the CONSECUTIVE units begin + w * block
-// .. of the CTA's share (block = share / 8) instead of every eighth, the list has no empty
-// units, and every stretch of one sequence inside a warp's block is a piece of its own that the
-// warp stores straight to a split slot (slot = the block's number minus the number of the block
-// that holds the sequence's first page): no deposits, no arrival counters, no merge, nothing
-// shared between warps after the work list.  A block is at least longest / (split_k - 1) units,
-// so a sequence never needs more than split_k slots.  What a short sequence costs is then one
-// Q tile and one store for one warp, not for each of eight.
+// SOLO (the variant every call runs; the other one is the instrumented kernel): warp w owns the
+// CONSECUTIVE units begin + w * block .. of the CTA's share (block = share / 8, the share
+// rounded up to eight blocks) instead of every eighth, and the list has no empty units.  Every
+// stretch of one sequence inside a warp's block is a piece the warp computes on its own: one Q
+// tile, its pages, no deposits, arrival counters or polls on the way.  A piece whose sequence
+// neither began in the block of the warp before nor goes on in the block of the warp after is
+// stored straight to its split slot.  The others -- at most a warp's first and last -- stay in
+// the warp's two deposit buffers until the CTA's end, where, after the kernel's only CTA-wide
+// barrier past the work list, the warp that holds the first of a sequence's consecutive pieces
+// sums them (up to eight deposits, weights by shuffle) and stores ONE piece per CTA and
+// sequence: the slots, the bound share >= longest / (split_k - 1) and the end-of-sequence mark
+// are exactly those of the variant above, and so is what the combine reads.  What a sequence
+// boundary costs is one Q tile and one store for one warp instead of a Q tile and a deposit for
+// each of eight plus a merge in the middle of the stream.
 template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = false>
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
@@ -284,8 +290,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
                   (longest + p.split_k - 2) / (p.split_k - 1));
   int block = 0;  // SOLO: units per warp
   if constexpr (SOLO) {
-    block = max(((total + sp.ctas_per_head - 1) / sp.ctas_per_head + kMmaWarps - 1) / kMmaWarps,
-                (longest + p.split_k - 2) / (p.split_k - 1));
+    block = (share + kMmaWarps - 1) / kMmaWarps;
     share = block * kMmaWarps;
   }
   const int begin = cta * share;
@@ -664,6 +669,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   int rank = 0;
   int page = my_first;  // this warp's next unit
   const int my_end = SOLO ? min(end, my_first + block) : end;  // end of this warp's units
+  int chain_seq = -1, chain_buffer = 0;  // SOLO: the sequence whose pieces this warp merges at the CTA's end
   int read_slot = 0;
   // Move (piece_seq, rank) forward to the sequence that holds unit `target` (< end).  Only
   // sequences with a page inside the share count as pieces.
@@ -873,9 +879,16 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     }
 
     if constexpr (SOLO) {
-      // ---- the piece is this warp's alone: through its deposit buffer (so that rows leave as
-      // 16-byte vectors) to its split slot ----
-      float* mine = deposits + warp * kDepositFloats;  // [6 heads][dim]
+      // ---- the piece is this warp's alone.  If the sequence neither reaches into the block of
+      // the warp before nor into that of the warp after (within this CTA), it goes to its split
+      // slot now; otherwise its state is left in shared memory for the merge at the CTA's end.
+      // Buffer 0 of a warp holds its first piece, buffer 1 stages the others (the last one, if
+      // it reaches into the next block, stays there). ----
+      const bool first_piece = max(seq_first, my_first) == my_first;
+      const bool open_left = first_piece && seq_first < my_first && my_first > begin;
+      const bool open_right = first_page[done_seq + 1] > my_end && my_end < end;
+      const int buffer = first_piece ? 0 : 1;
+      float* mine = deposits + (buffer * kMmaWarps + warp) * kDepositFloats;  // [6 heads][dim]
       if (q < QF_GQA_GROUP / 2) {
         float* even = mine + (2 * q) * kDepositHeadStride + (FP8 ? 2 * g : g);
         float* odd = even + kDepositHeadStride;
@@ -893,9 +906,20 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         total[h] += __shfl_xor_sync(kFull, total[h], 8);
         total[h] += __shfl_xor_sync(kFull, total[h], 16);
       }
+      if (open_left || open_right) {
+        if (g == 0) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            warp_offset[buffer][warp][2 * q + h] = offset[h], warp_sum[buffer][warp][2 * q + h] = total[h];
+          }
+        }
+        if (open_right && !open_left) chain_seq = done_seq, chain_buffer = buffer;  // this warp merges the chain
+        __syncwarp();
+        continue;
+      }
       __syncwarp();
-      const int split_slot = cta * kMmaWarps + warp - seq_first / block;
-      const bool slot_ok = split_slot >= 0 && split_slot < p.split_k;  // holds by the choice of `block`
+      const int split_slot = cta - seq_first / share;
+      const bool slot_ok = split_slot >= 0 && split_slot < p.split_k;  // holds by the choice of `share`
       if (slot_ok) {
         const int64_t partial_row =
             (static_cast<int64_t>(done_seq) * p.split_k + split_slot) * p.q_heads +
@@ -910,7 +934,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
           for (int h = 0; h < 2; ++h) {
             p.partial_max[partial_row + 2 * q + h] = offset[h] * kLn2;  // natural-log units for the combine
             p.partial_sum[partial_row + 2 * q + h] = total[h];
-            if (first_page[done_seq + 1] <= my_end && split_slot + 1 < p.split_k) {
+            if (first_page[done_seq + 1] <= end && split_slot + 1 < p.split_k) {
               p.partial_sum[partial_row + p.q_heads + 2 * q + h] = -1.f;  // no further pieces of this sequence
             }
           }
@@ -1030,6 +1054,71 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     if (PROFILE && last) t_merge += global_nanoseconds() - t_arrived, ++merges;
   }
   wait_all_copies();
+  if constexpr (SOLO) {
+    // ---- pieces of one sequence in consecutive blocks of this CTA become one piece: the warp
+    // whose block holds the first of them (chain_seq) sums the deposits of the warps up to the
+    // one that holds the sequence's (or the share's) end.  The CTA's only barrier. ----
+    __syncthreads();
+    if (chain_seq >= 0) {
+      const int seq_first = first_page[chain_seq];
+      const int chain_end = min(first_page[chain_seq + 1], end);         // unit after the chain's last page
+      const int participants = (chain_end - 1 - begin) / block - warp + 1;  // this warp and the ones after it
+      // lane = (member m = lane / 4, head pair q): weight of m's deposit, per head
+      const int m = lane >> 2;
+      const bool took_part = m < participants;
+      const int member_buffer = m == 0 ? chain_buffer : 0;
+      float top[2], total[2], weight[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float mw = took_part ? warp_offset[member_buffer][warp + m][2 * q + h] : -INFINITY;
+        float best = mw;
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 4));
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 8));
+        best = fmaxf(best, __shfl_xor_sync(kFull, best, 16));
+        weight[h] = mw == -INFINITY ? 0.f : fast_exp2(mw - best);
+        float part = took_part ? warp_sum[member_buffer][warp + m][2 * q + h] * weight[h] : 0.f;
+        part += __shfl_xor_sync(kFull, part, 4);
+        part += __shfl_xor_sync(kFull, part, 8);
+        part += __shfl_xor_sync(kFull, part, 16);
+        top[h] = best, total[h] = part;
+      }
+      const int split_slot = cta - seq_first / share;
+      if (split_slot >= 0 && split_slot < p.split_k) {  // holds by the choice of `share`
+        const int64_t partial_row =
+            (static_cast<int64_t>(chain_seq) * p.split_k + split_slot) * p.q_heads +
+            static_cast<int64_t>(kv_head) * QF_GQA_GROUP;
+        // A lane sums four dims (4 lane .. 4 lane + 3) of each head over the deposits.
+        float4 value[QF_GQA_GROUP];
+#pragma unroll
+        for (int head = 0; head < QF_GQA_GROUP; ++head) value[head] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < participants; ++k) {
+          const float* from = deposits + (((k == 0 ? chain_buffer : 0) * kMmaWarps) + warp + k) * kDepositFloats + 4 * lane;
+#pragma unroll
+          for (int head = 0; head < QF_GQA_GROUP; ++head) {
+            const float even = __shfl_sync(kFull, weight[0], 4 * k + (head >> 1));
+            const float odd = __shfl_sync(kFull, weight[1], 4 * k + (head >> 1));
+            const float w = (head & 1) ? odd : even;
+            const float4 part = *reinterpret_cast<const float4*>(from + head * kDepositHeadStride);
+            value[head].x += part.x * w, value[head].y += part.y * w;
+            value[head].z += part.z * w, value[head].w += part.w * w;
+          }
+        }
+        float4* row = reinterpret_cast<float4*>(p.partial_out + partial_row * QF_HEAD_DIM) + lane;
+#pragma unroll
+        for (int head = 0; head < QF_GQA_GROUP; ++head) row[head * (QF_HEAD_DIM / 4)] = value[head];
+        if (m == 0 && q < QF_GQA_GROUP / 2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            p.partial_max[partial_row + 2 * q + h] = top[h] * kLn2;
+            p.partial_sum[partial_row + 2 * q + h] = total[h];
+            if (first_page[chain_seq + 1] <= end && split_slot + 1 < p.split_k) {
+              p.partial_sum[partial_row + p.q_heads + 2 * q + h] = -1.f;  // no further pieces of this sequence
+            }
+          }
+        }
+      }
+    }
+  }
   if (PROFILE) {
     __syncthreads();  // the CTA's exit time is that of its last warp
     if (p.cycles != nullptr && tid == 0) {

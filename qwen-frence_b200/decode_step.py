@@ -38,9 +38,8 @@ class DecodeStep:
         self.fp8 = workload.fp8
         self.layers = workload.layers
         self.batch = workload.batch
-        # the scheduler's view: the lengths are known on the host
-        self.split_k = int(split_k) if split_k else kv_layout.plan_split_k_for_lengths(
-            [c + 1 for c in workload.contexts], table_pages=workload.block_table.shape[1], fp8=self.fp8,
+        self.split_k = int(split_k) if split_k else kv_layout.plan_split_k(
+            max(self.batch, 1), workload.max_context,
             sm_count=torch.cuda.get_device_properties(self.device).multi_processor_count)
         # fused_write: RoPE + KV write inside the attention partial pass (two launches per
         # layer instead of three) where the tensor-core kernel applies

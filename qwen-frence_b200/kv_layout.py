@@ -135,51 +135,19 @@ def plan_split_k(batch, max_context_length, *, kv_heads=KV_HEADS, page_size=PAGE
     wanted = -(-(sm_count * ctas_per_sm * waves) // (batch * kv_heads))
     cap = max(1, pages // min_pages_per_split)
     split_k = int(max(1, min(wanted, cap, 65535)))
-    # Many short sequences: the tensor-core kernel's solo variant (every warp keeps its pieces
-    # to itself) takes block tables of up to SOLO_TABLE_PAGES pages when batch * (split_k - 1)
-    # covers the warps that share a KV head; a slot it does not fill costs nothing.
-    if pages <= SOLO_TABLE_PAGES and batch >= SOLO_MIN_BATCH:
-        warps_per_head = sm_count * 8 // kv_heads
-        split_k = max(split_k, -(-warps_per_head // batch) + 1)
+    # Many short sequences: the persistent kernel (which needs split_k >= 2; a slot it does not
+    # fill costs nothing) instead of one CTA per sequence and KV head.
+    if pages <= SHORT_TABLE_PAGES and batch >= SHORT_MIN_BATCH:
+        split_k = max(split_k, 3)
     return split_k
 
 
-def plan_split_k_for_lengths(seq_lens, *, table_pages=None, fp8=False, kv_heads=KV_HEADS, page_size=PAGE_SIZE,
-                             sm_count=148, max_slots=64):
-    """Split count from the batch's actual lengths, which a scheduler knows on the host.
-
-    Aims at the tensor-core kernel's solo variant (every warp keeps its pieces to itself, the
-    faster one wherever it has the slots): enough slots that a warp's block need not be larger
-    than an even share of the pages, ceil(longest / block) + 1 with block = ceil(ceil(total /
-    CTAs per head) / 8), and enough for the library to choose the variant, batch * (split_k - 1)
-    >= 2 * warps per head (1 * for block tables of at most SOLO_TABLE_PAGES pages).  Batches that
-    would need more than `max_slots` (few very long sequences) keep plan_split_k's choice: measured
-    on by-sequence shards of 256 log-uniform lengths, 64 sequences with 46 slots gain 4 % per step
-    over that choice, 32 sequences with 96 slots lose 7 %."""
-    lengths = [max(int(t), 0) for t in seq_lens]
-    batch = len(lengths)
-    if batch == 0:
-        return 1
-    fallback = plan_split_k(batch, max(max(lengths), 1), kv_heads=kv_heads, page_size=page_size, sm_count=sm_count)
-    pages = [-(-t // page_size) for t in lengths]
-    total, longest = sum(pages), max(pages)
-    if total == 0:
-        return fallback
-    ctas_per_head = max(1, sm_count * (2 if fp8 else 1) // kv_heads)
-    warps_per_head = ctas_per_head * 8
-    block = -(-(-(-total // ctas_per_head)) // 8)
-    width = longest if table_pages is None else int(table_pages)
-    if fp8 and width > SOLO_TABLE_PAGES:
-        return fallback  # the library keeps FP8 pools with wide tables on the variant that shares pieces
-    factor = 1 if width <= SOLO_TABLE_PAGES else 2
-    split_k = max(-(-longest // block) + 1, -(-factor * warps_per_head // batch) + 1)
-    return split_k if split_k <= max_slots else fallback
-
-
-# Widest block table (pages) and smallest batch for which plan_split_k aims at the solo
-# variant of the tensor-core kernel (kSoloTablePages in csrc/qf_decode_attention.cu).
-SOLO_TABLE_PAGES = 64
-SOLO_MIN_BATCH = 256
+# Widest block table (pages) and smallest batch for which plan_split_k keeps a batch of short
+# sequences on the persistent kernel (split_k >= 3) instead of one CTA per sequence and KV head
+# (split_k 1): measured per layer, attention call alone, 256 x 200 tokens 15.4 against 26.1 us,
+# 512 x 100 15.7 against 30.2, 1 024 x 60 19.8 against 40.6; 64 x 200 13.1 against 10.9.
+SHORT_TABLE_PAGES = 64
+SHORT_MIN_BATCH = 256
 
 
 # Empty units the tensor-core persistent kernel counts per sequence when it cuts the
@@ -232,26 +200,28 @@ def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SI
 def solo_schedule(seq_lens, *, split_k, ctas_per_head, warps=8, unit_tokens=PAGE_SIZE):
     """Host restatement of how the tensor-core kernel's solo variant cuts one KV head's work.
 
-    The sequences' pages are concatenated (no empty units); warp w of CTA c takes pages
-    [(c * warps + w) * block, +block) with block = max(ceil(ceil(total / ctas_per_head) /
-    warps), ceil(longest / (split_k - 1))), and every stretch of one sequence inside a block
-    is a piece that goes to split slot (its block) - (the block of the sequence's first page).
-    Returns (block, pieces), a piece being (block number, sequence, first page within the
-    sequence, pages, split slot)."""
+    The sequences' pages are concatenated (no empty units).  CTA c takes pages [c * share,
+    (c + 1) * share) with share = warps * block, block = ceil(max(ceil(total / ctas_per_head),
+    ceil(longest / (split_k - 1))) / warps); warp w of the CTA streams pages [w * block,
+    (w + 1) * block) of that share on its own, and what the CTA's warps hold of one sequence is
+    merged at the CTA's end into ONE piece, which goes to split slot (the CTA) - (the CTA that
+    holds the sequence's first page).  Returns (block, pieces), a piece being (cta, sequence,
+    first page within the sequence, pages, split slot)."""
     if split_k < 2 or ctas_per_head < 1:
         raise ValueError("the persistent kernels need split_k >= 2 and at least one CTA per head")
     data = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
     total, longest = sum(data), max(data, default=0)
     if total == 0:
         return 0, []
-    block = max(-(-(-(-total // ctas_per_head)) // warps), -(-longest // (split_k - 1)))
+    block = -(-max(-(-total // ctas_per_head), -(-longest // (split_k - 1))) // warps)
+    share = block * warps
     pieces, first = [], 0
     for sequence, count in enumerate(data):
         position = first
         while position < first + count:
-            number = position // block
-            stop = min(first + count, (number + 1) * block)
-            pieces.append((number, sequence, position - first, stop - position, number - first // block))
+            cta = position // share
+            stop = min(first + count, (cta + 1) * share)
+            pieces.append((cta, sequence, position - first, stop - position, cta - first // share))
             position = stop
         first += count
     return block, pieces

@@ -261,9 +261,10 @@ def test_bad_page_id_is_reported_not_dereferenced(package, cuda_device):
 # ---------------------------------------------------------------------------
 # The persistent kernels behind the fused entry point (split_k >= 2): CTAs share
 # the batch's pages equally, so a CTA's share crosses sequence boundaries.  Mode 3
-# is the CUDA-core kernel (what FP8 pools use), mode 4 the tensor-core kernel.
+# is the CUDA-core kernel, mode 4 the tensor-core kernel whose warps interleave over the
+# pages (the instrumented variant), mode 5 its solo variant (what every call runs).
 # ---------------------------------------------------------------------------
-PERSISTENT = pytest.mark.parametrize("mode", [3, 4], ids=["cuda_core", "tensor_core"])
+PERSISTENT = pytest.mark.parametrize("mode", [3, 4, 5], ids=["cuda_core", "tensor_core", "tensor_core_solo"])
 
 
 def _persistent(package, mode, dev, split_k, **kwargs):
@@ -395,14 +396,15 @@ def test_persistent_kernel_bad_page_id(package, cuda_device, mode):
 
 
 def test_automatic_choice_runs_persistent_kernel_on_a_wide_batch(package, oracle, cuda_device):
-    """64 sequences x split_k 10: the default path is the tensor-core kernel; it must
-    agree with the forced one bit for bit and with the oracle."""
+    """64 sequences x split_k 10: the default path is the tensor-core kernel's solo variant; it
+    must agree with the forced one bit for bit, and it and the interleaving variant with the oracle."""
     generator = torch.Generator().manual_seed(3)
     lengths = torch.randint(1, 900, (64,), generator=generator).tolist()
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=28)
     automatic = package.grouped_splitk_decode_attention(*dev, split_k=10)
-    assert torch.equal(automatic, _persistent(package, 4, dev, 10))
+    assert torch.equal(automatic, _persistent(package, 5, dev, 10))
     assert_attention_close(automatic, oracle.paged_attention(*host))
+    assert_attention_close(_persistent(package, 4, dev, 10), oracle.paged_attention(*host))
 
 
 def test_persistent_timeline(package, cuda_device):
@@ -442,7 +444,8 @@ def test_stages_and_plan_entry_points(package, oracle, cuda_device):
     host, dev = _fast_path_inputs(cuda_device, lengths, seed=31)
     cabi = package.cabi
     splitk = package.kernel_module("paged_decode_grouped_splitk")
-    for split_k, mode, kernel in ((8, 0, "decode_mma_kernel"), (2, 0, "decode_mma_kernel"),
+    for split_k, mode, kernel in ((8, 0, "decode_mma_kernel (solo)"), (2, 0, "decode_mma_kernel (solo)"),
+                                  (8, 4, "decode_mma_kernel"), (8, 5, "decode_mma_kernel (solo)"),
                                   (4, 2, "decode_partial_kernel"), (4, 3, "decode_stream_kernel")):
         cabi.set_tuning(force_generic=mode)
         try:
@@ -516,17 +519,18 @@ def test_many_split_slots_take_the_chained_combine(package, oracle, cuda_device,
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("batch,split_k", [(300, 3), (600, 2), (90, 8)])
-def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device, dtype, batch, split_k):
-    """Block tables of at most 64 pages and batch * (split_k - 1) >= the warps that share a KV
-    head: every warp keeps its stretch of the page list to itself and stores each sequence's
-    part of it to a split slot of its own.  Lengths from 0 tokens to the full table, page
-    boundaries on both sides, NaN tails, NaN-filled partial buffers."""
+@pytest.mark.parametrize("batch,split_k,longest", [(300, 3, 1024), (600, 2, 1024), (90, 8, 1024), (40, 6, 6000), (7, 2, 3000)])
+def test_solo_variant_pieces_and_slots(package, oracle, cuda_device, dtype, batch, split_k, longest):
+    """The tensor-core kernel of every call: each warp streams a block of consecutive pages on
+    its own and what a CTA's warps hold of one sequence is merged at the CTA's end.  Many short
+    sequences (several whole sequences per warp), long ones (a sequence over many warps and
+    several CTAs), few slots (the share set by the slot bound, idle CTAs): lengths from 0 tokens
+    up, page boundaries on both sides, NaN tails, NaN-filled partial buffers.  The filled slots
+    are those of the host restatement of the schedule."""
     generator = torch.Generator().manual_seed(batch + split_k)
-    lengths = torch.randint(0, 1025, (batch,), generator=generator).tolist()
-    lengths[:8] = [0, 1, 15, 16, 17, 1023, 1024, 0]
+    lengths = torch.randint(0, longest + 1, (batch,), generator=generator).tolist()
+    lengths[:7] = [0, 1, 15, 16, 17, longest - 1, longest]
     host, dev = _fast_path_inputs(cuda_device, lengths, dtype=dtype, seed=batch, value_scale=0.5, poison=True)
-    assert host[3].shape[1] <= 64
     cabi = package.cabi
     splitk = package.kernel_module("paged_decode_grouped_splitk")
     partials = (torch.full((batch, split_k, 12, 128), float("nan"), device=cuda_device),
@@ -539,7 +543,7 @@ def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device
     assert cabi.device_status() == 0
     expected = oracle.paged_attention(*host)
     assert_attention_close(out, expected, dtype=dtype)
-    assert (out[0] == 0).all() and (out[7] == 0).all()
+    assert (out[0] == 0).all()
     # slots: those of the host restatement of the schedule, filled from 0 without gaps, then
     # the end mark (sum -1) unless every slot is used
     ctas_per_head = cabi.fused_kernel_plan(args)[1]
@@ -553,30 +557,13 @@ def test_many_short_sequences_take_the_solo_variant(package, oracle, cuda_device
         assert (sums[row, :slots[row]] > 0).all()
         if length and slots[row] < split_k:
             assert sums[row, slots[row]] == -1
-    # the variant whose warps share their pieces gives the same attention (other rounding order)
+    # the variant whose warps interleave over the pages gives the same attention (other rounding order)
     cabi.set_tuning(force_generic=4)
     try:
         shared = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
     finally:
         cabi.set_tuning()
     assert_attention_close(shared, expected, dtype=dtype)
-
-
-def test_solo_variant_with_too_few_slots_for_an_even_split(package, oracle, cuda_device):
-    """Forced onto a batch it would not be chosen for: one long sequence among short ones and
-    two slots only, so a warp's block grows to the longest sequence and most warps idle.  Slow,
-    but every sequence still fits its slots and the result is the oracle's."""
-    lengths = [2000] + [40] * 30 + [0, 700]
-    host, dev = _fast_path_inputs(cuda_device, lengths, seed=77, value_scale=0.5, poison=True)
-    expected = oracle.paged_attention(*host)
-    for split_k in (2, 5):
-        package.cabi.set_tuning(force_generic=5)
-        try:
-            out = package.grouped_splitk_decode_attention(*dev, split_k=split_k)
-        finally:
-            package.cabi.set_tuning()
-        assert package.cabi.device_status() == 0
-        assert_attention_close(out, expected)
 
 
 def test_row_per_warp_combine_equals_row_per_cta_combine(package, cuda_device):
@@ -615,7 +602,7 @@ def test_misaligned_partial_buffer_keeps_off_the_vector_store_kernel(package, cu
     arena = torch.empty(2 * 8 * 12 * 128 + 4, dtype=torch.float32, device=cuda_device)
     stats = (torch.empty(2, 8, 12, device=cuda_device), torch.empty(2, 8, 12, device=cuda_device))
     out = torch.empty_like(q)
-    for offset, kernel in ((0, "decode_mma_kernel"), (1, "decode_stream_kernel"), (4, "decode_mma_kernel")):
+    for offset, kernel in ((0, "decode_mma_kernel (solo)"), (1, "decode_stream_kernel"), (4, "decode_mma_kernel (solo)")):
         partial_out = arena[offset:offset + 2 * 8 * 12 * 128].view(2, 8, 12, 128)
         assert partial_out.data_ptr() % 16 == (4 * offset) % 16
         args = splitk.fill_attention_args(cabi, q, k, v, table, lens, split_k=8, scale=128 ** -0.5,

@@ -81,11 +81,10 @@ def _plain_error(out_dev, out_ref):
 @pytest.mark.parametrize("name", ["decode_b64", "long_skew_b4", "sweep_b256"])
 def test_full_size_single_layer(package, oracle, cuda_device, name, fused_write):
     """Full batch, context lengths and POOL of the large configurations, one layer, through
-    the launches the benchmark times (split count as DecodeStep plans it from the lengths --
-    20 for decode_b64 and 13 for sweep_b256, which select the tensor-core kernel's solo
-    variant, 148 for long_skew_b4, which cannot -- with the RoPE / KV write as its own kernel
-    and folded into the partial pass): checked against the oracle row by row, and split-count
-    invariance (half the slots: the variant whose warps share their pieces).  sweep_b256
+    the launches the benchmark times (split count as DecodeStep plans it -- 10 for decode_b64,
+    3 for sweep_b256, 148 for long_skew_b4 -- with the RoPE / KV write as its own kernel and
+    folded into the partial pass): checked against the oracle row by row, and split-count
+    invariance.  sweep_b256
     runs in its real pool of 131 072 pages (1 GiB per tensor): page ids above 65 535 and
     byte offsets above 2^30 are indexed."""
     workload = package.workloads.build_workload(name, layers=1)
@@ -94,7 +93,7 @@ def test_full_size_single_layer(package, oracle, cuda_device, name, fused_write)
     step = package.decode_step.DecodeStep(workload, cuda_device, package=package,
                                           fused_write="always" if fused_write else False)
     assert step.fused_write == fused_write
-    assert step.split_k == {"decode_b64": 20, "sweep_b256": 13, "long_skew_b4": 148}[name]
+    assert step.split_k == {"decode_b64": 10, "sweep_b256": 3, "long_skew_b4": 148}[name]
     step.load_packed_rows()
     out = step.step().clone()
     _check_layer(oracle, step, 0, out)

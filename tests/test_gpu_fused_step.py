@@ -42,9 +42,8 @@ def _inputs(device, lengths, dtype=torch.float16, seed=0, index_dtype=torch.int3
 
 
 def _pair(package, case, split_k):
-    """The two operators.  The attention call and the fused step pick the variant of the
-    tensor-core kernel by the same rule (warps sharing their pieces, or each keeping its own
-    where the split slots allow), so their results can be compared bit for bit."""
+    """The two operators.  The attention call and the fused step run the same variant of the
+    tensor-core kernel, so their results can be compared bit for bit."""
     k_pool, v_pool = case["k_pool"].clone(), case["v_pool"].clone()
     q = package.packed_qkv_rope_cache(case["packed"], case["positions"], case["slots"], k_pool, v_pool)
     out = package.grouped_splitk_decode_attention(q, k_pool, v_pool, case["table"], case["lens"], split_k=split_k)
@@ -65,9 +64,9 @@ def _fused(package, case, split_k):
     ([513] * 8, 4),
     ([700, 9, 31, 1500, 64, 65, 3, 48, 1024, 1025, 250, 16], 6),
     ([9000], 3),                                    # one sequence cut into pieces by the slot limit
-    (list(range(1, 130)), 10),                      # many short sequences: the solo variant (slots to spare)
-    (list(range(1, 130)), 4),                       # ... and, with few slots, the variant that shares pieces
-    ([3000, 100, 2000, 16, 4096] * 16, 32),         # long sequences with slots enough for the solo variant
+    (list(range(1, 130)), 10),                      # many short sequences: several whole sequences per warp
+    (list(range(1, 130)), 4),
+    ([3000, 100, 2000, 16, 4096] * 16, 32),         # sequences over many warps and several CTAs
 ])
 def test_same_pools_and_output_as_the_two_operators(package, oracle, cuda_device, dtype, lengths, split_k):
     case = _inputs(cuda_device, lengths, dtype=dtype, seed=len(lengths))
@@ -197,3 +196,23 @@ def test_slot_check_refuses_rows_the_fused_kernel_would_place_elsewhere(package,
         package.packed_qkv_rope_attention(packed, positions, skipped, k, v, table, lens,
                                           split_k=4, require_fused=True, check_slots=True)
     assert torch.equal(k, k_before)  # refused before any launch
+
+
+def test_fused_step_on_the_interleaving_variant(package, oracle, cuda_device):
+    """qf_set_tuning mode 4 keeps the variant of the tensor-core kernel whose warps interleave
+    over the pages (the instrumented one): fused step and operator pair agree bit for bit there
+    too, and with the default variant within the attention tolerance."""
+    lengths = [700, 9, 31, 1500, 64, 65, 3, 48, 1024, 1025, 250, 16] * 3
+    case = _inputs(cuda_device, lengths, dtype=torch.float16, seed=11)
+    default_out, default_k, default_v = _fused(package, case, 6)
+    package.cabi.set_tuning(force_generic=4)
+    try:
+        want_out, want_k, want_v = _pair(package, case, 6)
+        got_out, got_k, got_v = _fused(package, case, 6)
+    finally:
+        package.cabi.set_tuning()
+    assert torch.equal(got_out, want_out)
+    assert torch.equal(got_k.view(torch.int16), want_k.view(torch.int16))
+    assert torch.equal(got_v.view(torch.int16), want_v.view(torch.int16))
+    assert torch.equal(got_k.view(torch.int16), default_k.view(torch.int16))
+    assert_attention_close(got_out, default_out)

@@ -362,8 +362,8 @@ def test_persistent_schedule_respects_split_slots(package):
 
 def test_solo_schedule_covers_every_page_once_within_the_slots(package):
     """Host restatement of the solo variant's cut: every page of every sequence in exactly one
-    piece, a warp's pieces inside its block, slots counted from 0 per sequence without gaps and
-    below split_k -- also when the slot limit, not the page count, sets the block."""
+    piece, a piece inside its CTA's share (eight warp blocks), slots counted from 0 per sequence
+    without gaps and below split_k -- also when the slot limit, not the page count, sets the share."""
     import random
 
     kv_layout = package.kv_layout
@@ -379,7 +379,7 @@ def test_solo_schedule_covers_every_page_once_within_the_slots(package):
         if sum(pages) == 0:
             assert pieces == []
             continue
-        assert block * 8 * ctas >= sum(pages) and block * (split_k - 1) >= max(pages)
+        assert block * 8 * ctas >= sum(pages) and block * 8 * (split_k - 1) >= max(pages)
         seen = [0] * len(lengths)
         next_slot = [0] * len(lengths)
         for number, sequence, first, count, slot in pieces:
@@ -388,5 +388,5 @@ def test_solo_schedule_covers_every_page_once_within_the_slots(package):
             assert slot == next_slot[sequence] < split_k
             next_slot[sequence] += 1
             start = sum(pages[:sequence]) + first
-            assert number * block <= start and start + count <= (number + 1) * block
+            assert number * 8 * block <= start and start + count <= (number + 1) * 8 * block
         assert seen == pages
