@@ -918,6 +918,7 @@ def run_cta_timeline(args):
             lambda name, seed=0, batch=None: [args.uniform_context] * (batch or default_batch))
     workload = package.workloads.build_workload(args.workload, seed=args.seed, layers=launches,
                                                 world_size=args.shard_of, scaling="strong" if args.shard_of > 1 else "weak")
+    cabi.set_tuning(force_generic=KERNEL_MODES[args.kernel])  # auto: the solo variant; persistent_mma: the interleaving one
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package)
     splitk = package.kernel_module("paged_decode_grouped_splitk")
     q = torch.randn(workload.batch, 12, 128, device=device).mul_(0.5).to(step.dtype)
@@ -926,7 +927,7 @@ def run_cta_timeline(args):
     arg_sets = [splitk.fill_attention_args(
         cabi, q, step.k_pools[layer], step.v_pools[layer], step.block_table, step.seq_lens, split_k=step.split_k,
         scale=128 ** -0.5, partials=step.partials, out=out, kv_scales=scales(layer)) for layer in range(launches)]
-    _, ctas_per_head = cabi.fused_kernel_plan(arg_sets[0])
+    kernel_name, ctas_per_head = cabi.fused_kernel_plan(arg_sets[0])
     ctas = ctas_per_head * 2
     stamps = [torch.zeros((ctas, 10), dtype=torch.int64, device=device) for _ in range(launches)]
     lib = cabi.library()
@@ -950,7 +951,7 @@ def run_cta_timeline(args):
         graph.replay()
     torch.cuda.synchronize()
     tables = [t.cpu().double() for t in stamps]
-    origin = tables[0][:, 0].min()
+    origin = tables[0][tables[0][:, 5] > 0, 0].min()  # CTAs without work leave no stamps
     names = ("entry", "share_known", "ids_known", "first_tile", "exit")
     rows = []
     for table in tables:
@@ -969,10 +970,20 @@ def run_cta_timeline(args):
         record["stream_phase_us_by_pieces_of_warp0"] = {
             int(n): [int((pieces == n).sum()), round(float(stream_phase[pieces == n].mean()), 2),
                      round(float(stream_phase[pieces == n].max()), 2)] for n in sorted(set(pieces.tolist()))}
-        record["warp0_deposit_us_per_piece"] = round(float(table[busy, 7].sum() / max(float(pieces.sum()), 1.0) / 1e3), 3)
-        record["warp0_us_per_merge"] = round(float(table[busy, 8].sum() / max(float(table[busy, 9].sum()), 1.0) / 1e3), 3)
+        if kernel_name.endswith("(solo)"):
+            # columns 7 to 9 of the solo variant: warp 0's wait at the barrier at the CTA's end, its merge
+            # there (if it had one), and whether it had one
+            record["warp0_wait_at_the_end_barrier_us_mean_max"] = [
+                round(float(table[busy, 7].mean() / 1e3), 3), round(float(table[busy, 7].max() / 1e3), 3)]
+            merging = table[busy, 9] > 0
+            record["warp0_end_merges"] = int(merging.sum())
+            record["warp0_us_per_end_merge"] = round(float(table[busy, 8][merging].mean() / 1e3), 3) if merging.any() else None
+        else:
+            record["warp0_deposit_us_per_piece"] = round(float(table[busy, 7].sum() / max(float(pieces.sum()), 1.0) / 1e3), 3)
+            record["warp0_us_per_merge"] = round(float(table[busy, 8].sum() / max(float(table[busy, 9].sum()), 1.0) / 1e3), 3)
         rows.append(record)
-    print(json.dumps({"op": "cta_timeline", "workload": args.workload, "uniform_context": args.uniform_context or None,
+    print(json.dumps({"op": "cta_timeline", "workload": args.workload, "kernel": kernel_name,
+                      "uniform_context": args.uniform_context or None,
                       "batch": workload.batch, "split_k": step.split_k, "ctas": ctas, "launches": rows,
                       "columns": "min / mean / max microseconds over the CTAs, from the first launch's first entry",
                       "device_status": cabi.device_status()}))

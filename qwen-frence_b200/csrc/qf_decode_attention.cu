@@ -722,7 +722,13 @@ int launch_persistent_partial(const qf_decode_attention_args* a, FusedKernel kin
   QF_REQUIRE(status != nullptr, "could not resolve the device status word");
   const FastParams p = fast_params(a, nullptr, timeline, status);
   if (timeline != nullptr) {
-    QF_REQUIRE(kind == FusedKernel::kTensorCore, "only the tensor-core kernel has a timeline variant");
+    QF_REQUIRE(kind == FusedKernel::kTensorCore || kind == FusedKernel::kTensorCoreSolo,
+               "only the tensor-core kernel has a timeline variant");
+    if (kind == FusedKernel::kTensorCoreSolo) {
+      QF_REQUIRE(!a->kv_fp8, "the instrumented solo variant is built for 16-bit pools");
+      return a->dtype == QF_DTYPE_F16 ? launch_mma<__half, false, true, false, true>(p, stream)
+                                      : launch_mma<__nv_bfloat16, false, true, false, true>(p, stream);
+    }
     return a->dtype == QF_DTYPE_F16 ? launch_mma_for_pools<__half, true>(p, a->kv_fp8 != 0, stream)
                                     : launch_mma_for_pools<__nv_bfloat16, true>(p, a->kv_fp8 != 0, stream);
   }
@@ -938,9 +944,9 @@ int qf_grouped_splitk_persistent_timeline(const qf_decode_attention_args* args, 
   QF_REQUIRE(timeline != nullptr, "timeline must not be null");
   QF_REQUIRE(args->split_k >= 2 && args->batch >= 1, "the persistent kernels need split_k >= 2 and a batch");
   qf::FusedKernel kind = qf::choose_fused_kernel(args);
-  // (the instrumented variant is the one whose warps share their pieces)
-  if (kind == qf::FusedKernel::kTensorCoreSolo) kind = qf::FusedKernel::kTensorCore;
-  QF_REQUIRE(kind == qf::FusedKernel::kTensorCore,
+  // FP8 pools: the instrumented kernel is the variant whose warps interleave over the pages
+  if (kind == qf::FusedKernel::kTensorCoreSolo && args->kv_fp8) kind = qf::FusedKernel::kTensorCore;
+  QF_REQUIRE(kind == qf::FusedKernel::kTensorCore || kind == qf::FusedKernel::kTensorCoreSolo,
              "these arguments do not select the tensor-core persistent kernel");
   return qf::launch_persistent_partial(args, kind, static_cast<cudaStream_t>(stream),
                                        reinterpret_cast<long long*>(timeline));

@@ -220,25 +220,25 @@ struct RopeInputs {
 };
 
 //
-// SOLO (the variant every call runs; the other one is the instrumented kernel): warp w owns the
-// CONSECUTIVE units begin + w * block .. of the CTA's share (block = share / 8, the share
-// rounded up to eight blocks) instead of every eighth, and the list has no empty units.  Every
+// SOLO (the variant every call runs): warp w owns the CONSECUTIVE units begin + block_start(w) ..
+// of the CTA's share (eight blocks of share / 8 units, the first share % 8 of them one more)
+// instead of every eighth, and the list has no empty units.  Every
 // stretch of one sequence inside a warp's block is a piece the warp computes on its own: one Q
 // tile, its pages, no deposits, arrival counters or polls on the way.  A piece whose sequence
 // neither began in the block of the warp before nor goes on in the block of the warp after is
 // stored straight to its split slot.  The others -- at most a warp's first and last -- stay in
 // the warp's two deposit buffers until the CTA's end, where, after the kernel's only CTA-wide
-// barrier past the work list, the warp that holds the first of a sequence's consecutive pieces
-// sums them (up to eight deposits, weights by shuffle) and stores ONE piece per CTA and
-// sequence: the slots, the bound share >= longest / (split_k - 1) and the end-of-sequence mark
-// are exactly those of the variant above, and so is what the combine reads.  What a sequence
+// barrier past the work list, a sequence's consecutive pieces (a "chain") are summed and stored
+// as ONE piece per CTA and sequence -- by the warp that holds the first of them when the chain
+// is short (many chains: all at once), by six warps, a query head each, when it is long -- so
+// the slots, the bound share >= longest / (split_k - 1) and the end-of-sequence mark are exactly
+// those of the variant above, and so is what the combine reads.  What a sequence
 // boundary costs is one Q tile and one store for one warp instead of a Q tile and a deposit for
 // each of eight plus a merge in the middle of the stream.
 template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = false>
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
   static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
-  static_assert(!(SOLO && PROFILE), "the instrumented variant is the one whose warps share their pieces");
   constexpr int kOverhead = SOLO ? 0 : kPieceOverhead;  // empty units in front of a sequence
   constexpr int kStep = SOLO ? 1 : kMmaWarps;          // distance between a warp's units
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
@@ -255,6 +255,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   __shared__ float warp_weight[2][kMmaWarps][kPaddedHeads];
   __shared__ int arrived[2];
   __shared__ int merged[2];
+  __shared__ int chain_of[kMmaWarps][3];  // SOLO: per warp, the chain it heads: sequence (-1: none), buffer, warps
 
   constexpr unsigned kFull = 0xffffffffu;
   long long t_entry = 0, t_list = 0, t_ids = 0, t_first = 0, t_deposit = 0, t_merge = 0;
@@ -286,13 +287,13 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     dependency_wait();  // keeps the chain of completions intact even without work
     return;
   }
-  int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
-                  (longest + p.split_k - 2) / (p.split_k - 1));
-  int block = 0;  // SOLO: units per warp
-  if constexpr (SOLO) {
-    block = (share + kMmaWarps - 1) / kMmaWarps;
-    share = block * kMmaWarps;
-  }
+  const int share = max((total + sp.ctas_per_head - 1) / sp.ctas_per_head,
+                        (longest + p.split_k - 2) / (p.split_k - 1));
+  // SOLO: warp w's block is base + 1 units for w < extra, base units otherwise, and starts at
+  // block_start(w) units into the share; unit o of the share lies in the block of warp_of(o).
+  const int base = share / kMmaWarps, extra = share - base * kMmaWarps;
+  auto block_start = [&](int w) { return w * base + min(w, extra); };
+  auto warp_of = [&](int o) { return o < extra * (base + 1) ? o / (base + 1) : extra + (o - extra * (base + 1)) / max(base, 1); };
   const int begin = cta * share;
   if (begin >= total) {
     dependency_wait();
@@ -301,9 +302,9 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   const int count = min(share, total - begin);
   const int end = begin + count;
   // This warp's units: begin + warp + 8 k, k = 0 .. my_pages - 1 (pages, or empty units);
-  // SOLO: begin + warp * block + k.
-  const int my_first = SOLO ? begin + warp * block : begin + warp;
-  const int my_pages = SOLO ? min(max(count - warp * block, 0), block)
+  // SOLO: begin + block_start(warp) + k.
+  const int my_first = SOLO ? begin + block_start(warp) : begin + warp;
+  const int my_pages = SOLO ? min(max(count - block_start(warp), 0), base + (warp < extra ? 1 : 0))
                             : (count > warp ? (count - warp + kMmaWarps - 1) / kMmaWarps : 0);
 
   // ---- loads ----
@@ -668,7 +669,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   int piece_seq = sequence_of_unit(work, p.batch, begin);
   int rank = 0;
   int page = my_first;  // this warp's next unit
-  const int my_end = SOLO ? min(end, my_first + block) : end;  // end of this warp's units
+  const int my_end = SOLO ? my_first + my_pages : end;  // end of this warp's units
   int chain_seq = -1, chain_buffer = 0;  // SOLO: the sequence whose pieces this warp merges at the CTA's end
   int read_slot = 0;
   // Move (piece_seq, rank) forward to the sequence that holds unit `target` (< end).  Only
@@ -884,6 +885,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
       // slot now; otherwise its state is left in shared memory for the merge at the CTA's end.
       // Buffer 0 of a warp holds its first piece, buffer 1 stages the others (the last one, if
       // it reaches into the next block, stays there). ----
+      if (PROFILE) ++pieces;
       const bool first_piece = max(seq_first, my_first) == my_first;
       const bool open_left = first_piece && seq_first < my_first && my_first > begin;
       const bool open_right = first_page[done_seq + 1] > my_end && my_end < end;
@@ -1055,14 +1057,29 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   }
   wait_all_copies();
   if constexpr (SOLO) {
-    // ---- pieces of one sequence in consecutive blocks of this CTA become one piece: the warp
-    // whose block holds the first of them (chain_seq) sums the deposits of the warps up to the
-    // one that holds the sequence's (or the share's) end.  The CTA's only barrier. ----
+    // ---- pieces of one sequence in consecutive blocks of this CTA become one piece.  The warp
+    // whose block holds the first of them (chain_seq) announces the chain; after the CTA's only
+    // barrier past the work list, the warps share the (chain, query head) pairs: one of them
+    // sums that head over the deposits of the warps up to the one that holds the sequence's (or
+    // the share's) end, a lane four dims, the weights recomputed by every lane from the offsets. ----
+    // A chain of up to kSoloOwnChain warps is summed by its first warp alone (many short chains:
+    // all of them at once); a longer one is announced and its six heads are shared out (few long
+    // chains).  Measured per 28-layer step, first warp alone / all shared / this rule: 64 x
+    // U[128, 4096] tokens 0.800 / 0.786 ms, 256 x log-uniform [64, 8192] 2.142 / 2.158 ms.
+    constexpr int kSoloOwnChain = 3;
+    const int chain_warps = chain_seq >= 0 ? warp_of(min(first_page[chain_seq + 1], end) - 1 - begin) - warp + 1 : 0;
+    const bool own_chain = chain_warps > 0 && chain_warps <= kSoloOwnChain;
+    if (lane == 0) {
+      chain_of[warp][0] = own_chain ? -1 : chain_seq, chain_of[warp][1] = chain_buffer, chain_of[warp][2] = chain_warps;
+    }
+    long long t_loop_end = 0, t_barrier = 0;
+    if (PROFILE) t_loop_end = global_nanoseconds();
     __syncthreads();
-    if (chain_seq >= 0) {
+    if (PROFILE) t_barrier = global_nanoseconds(), t_deposit = t_barrier - t_loop_end;  // warp 0's wait at the barrier
+    if (own_chain) {
       const int seq_first = first_page[chain_seq];
       const int chain_end = min(first_page[chain_seq + 1], end);         // unit after the chain's last page
-      const int participants = (chain_end - 1 - begin) / block - warp + 1;  // this warp and the ones after it
+      const int participants = chain_warps;                              // this warp and the ones after it
       // lane = (member m = lane / 4, head pair q): weight of m's deposit, per head
       const int m = lane >> 2;
       const bool took_part = m < participants;
@@ -1118,6 +1135,54 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         }
       }
     }
+    // items (chain headed by warp `first`, query head): item t goes to warp t % 8, so the six
+    // heads of a chain are summed by six warps at once
+    for (int t = warp; t < kMmaWarps * QF_GQA_GROUP; t += kMmaWarps) {
+      const int first = t / QF_GQA_GROUP, head = t - first * QF_GQA_GROUP;
+      const int sequence = chain_of[first][0];
+      if (sequence < 0) continue;
+      if (PROFILE) ++merges;
+      const int first_buffer = chain_of[first][1], participants = chain_of[first][2];
+      // every load unconditional (of a member that exists in shared memory, whether or not it
+      // belongs to the chain) and independent of the others; what does not belong is selected away
+      float member_offset[kMmaWarps], member_sum[kMmaWarps], best = -INFINITY;
+      float4 part[kMmaWarps];
+#pragma unroll
+      for (int k = 0; k < kMmaWarps; ++k) {
+        const int member = min(first + k, kMmaWarps - 1), buffer = k == 0 ? first_buffer : 0;
+        member_offset[k] = warp_offset[buffer][member][head];
+        member_sum[k] = warp_sum[buffer][member][head];
+        part[k] = *reinterpret_cast<const float4*>(deposits + (buffer * kMmaWarps + member) * kDepositFloats +
+                                                   head * kDepositHeadStride + 4 * lane);
+        if (k >= participants) member_offset[k] = -INFINITY;
+        best = fmaxf(best, member_offset[k]);
+      }
+      float total = 0.f;
+      float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < kMmaWarps; ++k) {
+        const bool in = k < participants && member_offset[k] != -INFINITY;
+        const float w = in ? fast_exp2(member_offset[k] - best) : 0.f;
+        total += in ? member_sum[k] * w : 0.f;
+        value.x += in ? part[k].x * w : 0.f, value.y += in ? part[k].y * w : 0.f;
+        value.z += in ? part[k].z * w : 0.f, value.w += in ? part[k].w * w : 0.f;
+      }
+      const int split_slot = cta - first_page[sequence] / share;
+      if (split_slot >= 0 && split_slot < p.split_k) {  // holds by the choice of `share`
+        const int64_t partial_row =
+            (static_cast<int64_t>(sequence) * p.split_k + split_slot) * p.q_heads +
+            static_cast<int64_t>(kv_head) * QF_GQA_GROUP + head;
+        reinterpret_cast<float4*>(p.partial_out + partial_row * QF_HEAD_DIM)[lane] = value;
+        if (lane == 0) {
+          p.partial_max[partial_row] = best * kLn2;  // natural-log units for the combine
+          p.partial_sum[partial_row] = total;
+          if (first_page[sequence + 1] <= end && split_slot + 1 < p.split_k) {
+            p.partial_sum[partial_row + p.q_heads] = -1.f;  // no further pieces of this sequence
+          }
+        }
+      }
+    }
+    if (PROFILE) t_merge = global_nanoseconds() - t_barrier;  // warp 0's share of the merges
   }
   if (PROFILE) {
     __syncthreads();  // the CTA's exit time is that of its last warp

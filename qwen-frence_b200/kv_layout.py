@@ -197,34 +197,18 @@ def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SI
     return share, pieces
 
 
-def solo_schedule(seq_lens, *, split_k, ctas_per_head, warps=8, unit_tokens=PAGE_SIZE):
+def solo_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SIZE):
     """Host restatement of how the tensor-core kernel's solo variant cuts one KV head's work.
 
     The sequences' pages are concatenated (no empty units).  CTA c takes pages [c * share,
-    (c + 1) * share) with share = warps * block, block = ceil(max(ceil(total / ctas_per_head),
-    ceil(longest / (split_k - 1))) / warps); warp w of the CTA streams pages [w * block,
-    (w + 1) * block) of that share on its own, and what the CTA's warps hold of one sequence is
-    merged at the CTA's end into ONE piece, which goes to split slot (the CTA) - (the CTA that
-    holds the sequence's first page).  Returns (block, pieces), a piece being (cta, sequence,
-    first page within the sequence, pages, split slot)."""
-    if split_k < 2 or ctas_per_head < 1:
-        raise ValueError("the persistent kernels need split_k >= 2 and at least one CTA per head")
-    data = [-(-max(int(t), 0) // unit_tokens) for t in seq_lens]
-    total, longest = sum(data), max(data, default=0)
-    if total == 0:
-        return 0, []
-    block = -(-max(-(-total // ctas_per_head), -(-longest // (split_k - 1))) // warps)
-    share = block * warps
-    pieces, first = [], 0
-    for sequence, count in enumerate(data):
-        position = first
-        while position < first + count:
-            cta = position // share
-            stop = min(first + count, (cta + 1) * share)
-            pieces.append((cta, sequence, position - first, stop - position, cta - first // share))
-            position = stop
-        first += count
-    return block, pieces
+    (c + 1) * share) with share = max(ceil(total / ctas_per_head), ceil(longest / (split_k -
+    1))); its eight warps stream consecutive blocks of share // 8 (the first share % 8 of them
+    one more) pages of that share on their own, and what they hold of one sequence is merged at
+    the CTA's end into ONE piece, which goes to split slot (the CTA) - (the CTA that holds the
+    sequence's first page).  Returns (share, pieces), a piece being (cta, sequence, first page
+    within the sequence, pages, split slot): persistent_schedule without empty units."""
+    return persistent_schedule(seq_lens, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=unit_tokens,
+                               overhead_units=0)
 
 
 def kv_bytes_per_layer(seq_lens, *, kv_heads=KV_HEADS, head_dim=HEAD_DIM, elem_bytes=2):

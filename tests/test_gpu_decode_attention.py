@@ -407,22 +407,32 @@ def test_automatic_choice_runs_persistent_kernel_on_a_wide_batch(package, oracle
     assert_attention_close(_persistent(package, 4, dev, 10), oracle.paged_attention(*host))
 
 
-def test_persistent_timeline(package, cuda_device):
-    """The instrumented tensor-core pass: every CTA with work reports entry <= first
-    tile <= exit and its share; the shares add up to the batch's pages."""
+@pytest.mark.parametrize("mode", [0, 4], ids=["solo", "interleaving"])
+def test_persistent_timeline(package, cuda_device, mode):
+    """The instrumented tensor-core pass (the variant every call runs, and the one whose warps
+    interleave over the pages): every CTA with work reports entry <= first tile <= exit and its
+    share; the shares add up to the batch's pages (plus the interleaving variant's empty units)."""
     generator = torch.Generator().manual_seed(4)
     lengths = torch.randint(1, 900, (64,), generator=generator).tolist()
     (_, dev) = _fast_path_inputs(cuda_device, lengths, seed=29)
-    timeline = package.native_grouped_persistent_timeline(*dev, split_k=10).cpu()
+    package.cabi.set_tuning(force_generic=mode)
+    try:
+        timeline = package.native_grouped_persistent_timeline(*dev, split_k=10).cpu()
+    finally:
+        package.cabi.set_tuning()
     busy = timeline[timeline[:, 5] > 0]
     assert len(busy) >= 2
     for earlier, later in ((0, 1), (1, 2), (2, 3), (3, 4)):
         assert (busy[:, earlier] <= busy[:, later]).all()
-    overhead = package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD  # empty units per sequence, as in the kernel
-    empty = package.kv_layout.sequence_overhead
-    assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) + empty(-(-n // 16), overhead) for n in lengths)
-    _, pieces = package.kv_layout.persistent_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2,
-                                                      overhead_units=overhead)
+    if mode == 4:
+        overhead = package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD  # empty units per sequence, as in the kernel
+        empty = package.kv_layout.sequence_overhead
+        assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) + empty(-(-n // 16), overhead) for n in lengths)
+        _, pieces = package.kv_layout.persistent_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2,
+                                                          overhead_units=overhead)
+    else:
+        assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) for n in lengths)
+        _, pieces = package.kv_layout.solo_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2)
     per_cta = torch.bincount(torch.tensor([piece[0] for piece in pieces]), minlength=len(timeline) // 2)
     seen_by_warp0 = busy[:, 6].reshape(2, -1)  # pieces that held pages of warp 0
     assert (seen_by_warp0 >= 1).all() and (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()

@@ -374,12 +374,12 @@ def test_solo_schedule_covers_every_page_once_within_the_slots(package):
             (2, 74, [2000] + [40] * 30 + [0, 700]),
             (8, 148, [1] * 90),
             (4, 74, [0, 0, 0])):
-        block, pieces = kv_layout.solo_schedule(lengths, split_k=split_k, ctas_per_head=ctas)
+        share, pieces = kv_layout.solo_schedule(lengths, split_k=split_k, ctas_per_head=ctas)
         pages = [-(-n // 16) for n in lengths]
         if sum(pages) == 0:
             assert pieces == []
             continue
-        assert block * 8 * ctas >= sum(pages) and block * 8 * (split_k - 1) >= max(pages)
+        assert share * ctas >= sum(pages) and share * (split_k - 1) >= max(pages)
         seen = [0] * len(lengths)
         next_slot = [0] * len(lengths)
         for number, sequence, first, count, slot in pieces:
@@ -388,5 +388,5 @@ def test_solo_schedule_covers_every_page_once_within_the_slots(package):
             assert slot == next_slot[sequence] < split_k
             next_slot[sequence] += 1
             start = sum(pages[:sequence]) + first
-            assert number * 8 * block <= start and start + count <= (number + 1) * 8 * block
+            assert number * share <= start and start + count <= (number + 1) * share
         assert seen == pages
