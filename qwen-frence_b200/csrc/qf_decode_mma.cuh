@@ -1077,7 +1077,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     __syncthreads();
     if (PROFILE) t_barrier = global_nanoseconds(), t_deposit = t_barrier - t_loop_end;  // warp 0's wait at the barrier
     if (own_chain) {
-      const int seq_first = first_page[chain_seq];
+      const int seq_first = first_data_unit(chain_seq);
       const int chain_end = min(first_page[chain_seq + 1], end);         // unit after the chain's last page
       const int participants = chain_warps;                              // this warp and the ones after it
       // lane = (member m = lane / 4, head pair q): weight of m's deposit, per head
@@ -1167,7 +1167,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         value.x += in ? part[k].x * w : 0.f, value.y += in ? part[k].y * w : 0.f;
         value.z += in ? part[k].z * w : 0.f, value.w += in ? part[k].w * w : 0.f;
       }
-      const int split_slot = cta - first_page[sequence] / share;
+      const int split_slot = cta - first_data_unit(sequence) / share;
       if (split_slot >= 0 && split_slot < p.split_k) {  // holds by the choice of `share`
         const int64_t partial_row =
             (static_cast<int64_t>(sequence) * p.split_k + split_slot) * p.q_heads +
