@@ -222,7 +222,8 @@ struct RopeInputs {
 //
 // SOLO (the variant every call runs): warp w owns the CONSECUTIVE units begin + block_start(w) ..
 // of the CTA's share (eight blocks of share / 8 units, the first share % 8 of them one more)
-// instead of every eighth, and the list has no empty units.  Every
+// instead of every eighth (the list keeps its empty units: they make a block that holds many
+// sequence starts shorter in pages).  Every
 // stretch of one sequence inside a warp's block is a piece the warp computes on its own: one Q
 // tile, its pages, no deposits, arrival counters or polls on the way.  A piece whose sequence
 // neither began in the block of the warp before nor goes on in the block of the warp after is
@@ -239,7 +240,11 @@ template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = fal
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
   static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
-  constexpr int kOverhead = SOLO ? 0 : kPieceOverhead;  // empty units in front of a sequence
+  // empty units in front of a sequence: both variants weigh the shares with them (the solo
+  // variant, where a sequence costs one warp a Q tile and a store, measured per 28-layer step
+  // with 0 / 3 / 6: 64 x U[128, 4096] tokens 0.790 / 0.771 / 0.767 ms, 256 x log-uniform
+  // [64, 8192] 2.072 / 2.005 / 2.012, FP8 128 x 2 048 1.039 / 1.000 / 0.995)
+  constexpr int kOverhead = kPieceOverhead;
   constexpr int kStep = SOLO ? 1 : kMmaWarps;          // distance between a warp's units
   using Ops = MmaOps<typename std::conditional<FP8, __half, T>::type>;
   using Ring = RingShape<FP8>;
@@ -690,7 +695,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     const int seq_first = first_data_unit(piece_seq);  // unit of the sequence's first page
     if (page < seq_first) {
       // empty units: on to this warp's first unit that is a page (maybe of a later sequence)
-      page += ((seq_first - page + kMmaWarps - 1) / kMmaWarps) * kMmaWarps;
+      page += ((seq_first - page + kStep - 1) / kStep) * kStep;
       continue;
     }
     {
@@ -1188,7 +1193,9 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     __syncthreads();  // the CTA's exit time is that of its last warp
     if (p.cycles != nullptr && tid == 0) {
       long long* dst = p.cycles + static_cast<int64_t>(blockIdx.x) * kTimelineColumns;
-      dst[0] = t_entry, dst[1] = t_list, dst[2] = t_ids, dst[3] = t_first, dst[4] = global_nanoseconds();
+      // (warp 0 stamps the first tile; in the solo variant its block may hold empty units only)
+      dst[0] = t_entry, dst[1] = t_list, dst[2] = t_ids, dst[3] = t_first != 0 ? t_first : t_ids;
+      dst[4] = global_nanoseconds();
       dst[5] = count, dst[6] = pieces, dst[7] = t_deposit, dst[8] = t_merge, dst[9] = merges;
     }
   }

@@ -200,15 +200,15 @@ def persistent_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SI
 def solo_schedule(seq_lens, *, split_k, ctas_per_head, unit_tokens=PAGE_SIZE):
     """Host restatement of how the tensor-core kernel's solo variant cuts one KV head's work.
 
-    The sequences' pages are concatenated (no empty units).  CTA c takes pages [c * share,
-    (c + 1) * share) with share = max(ceil(total / ctas_per_head), ceil(longest / (split_k -
-    1))); its eight warps stream consecutive blocks of share // 8 (the first share % 8 of them
-    one more) pages of that share on their own, and what they hold of one sequence is merged at
-    the CTA's end into ONE piece, which goes to split slot (the CTA) - (the CTA that holds the
-    sequence's first page).  Returns (share, pieces), a piece being (cta, sequence, first page
-    within the sequence, pages, split slot): persistent_schedule without empty units."""
+    The unit list and the CTAs' shares are those of persistent_schedule with
+    TENSOR_CORE_PIECE_OVERHEAD empty units per sequence.  Inside a CTA the eight warps stream
+    consecutive blocks of share // 8 (the first share % 8 of them one more) units on their own,
+    and what they hold of one sequence is merged at the CTA's end into ONE piece, which goes to
+    split slot (the CTA) - (the CTA that holds the sequence's first page): the pieces are those
+    of the variant whose warps interleave over the units.  Returns (share, pieces), a piece
+    being (cta, sequence, first page within the sequence, pages, split slot)."""
     return persistent_schedule(seq_lens, split_k=split_k, ctas_per_head=ctas_per_head, unit_tokens=unit_tokens,
-                               overhead_units=0)
+                               overhead_units=TENSOR_CORE_PIECE_OVERHEAD)
 
 
 def kv_bytes_per_layer(seq_lens, *, kv_heads=KV_HEADS, head_dim=HEAD_DIM, elem_bytes=2):

@@ -424,18 +424,17 @@ def test_persistent_timeline(package, cuda_device, mode):
     assert len(busy) >= 2
     for earlier, later in ((0, 1), (1, 2), (2, 3), (3, 4)):
         assert (busy[:, earlier] <= busy[:, later]).all()
-    if mode == 4:
-        overhead = package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD  # empty units per sequence, as in the kernel
-        empty = package.kv_layout.sequence_overhead
-        assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) + empty(-(-n // 16), overhead) for n in lengths)
-        _, pieces = package.kv_layout.persistent_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2,
-                                                          overhead_units=overhead)
-    else:
-        assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) for n in lengths)
-        _, pieces = package.kv_layout.solo_schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2)
+    overhead = package.kv_layout.TENSOR_CORE_PIECE_OVERHEAD  # empty units per sequence, as in the kernel
+    empty = package.kv_layout.sequence_overhead
+    assert busy[:, 5].sum().item() == 2 * sum(-(-n // 16) + empty(-(-n // 16), overhead) for n in lengths)
+    schedule = package.kv_layout.persistent_schedule if mode == 4 else package.kv_layout.solo_schedule
+    extra = dict(overhead_units=overhead) if mode == 4 else {}
+    _, pieces = schedule(lengths, split_k=10, ctas_per_head=len(timeline) // 2, **extra)
     per_cta = torch.bincount(torch.tensor([piece[0] for piece in pieces]), minlength=len(timeline) // 2)
     seen_by_warp0 = busy[:, 6].reshape(2, -1)  # pieces that held pages of warp 0
-    assert (seen_by_warp0 >= 1).all() and (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()
+    # (in the solo variant warp 0's block of a small share may hold empty units only)
+    assert (seen_by_warp0 >= (1 if mode == 4 else 0)).all()
+    assert (seen_by_warp0 <= per_cta[:seen_by_warp0.shape[1]]).all()
     package.cabi.set_tuning(force_generic=2)  # the per-partition kernel has no timeline
     try:
         with pytest.raises(RuntimeError, match="tensor-core persistent kernel"):

@@ -362,8 +362,8 @@ def test_persistent_schedule_respects_split_slots(package):
 
 def test_solo_schedule_covers_every_page_once_within_the_slots(package):
     """Host restatement of the solo variant's cut: every page of every sequence in exactly one
-    piece, a piece inside its CTA's share (eight warp blocks), slots counted from 0 per sequence
-    without gaps and below split_k -- also when the slot limit, not the page count, sets the share."""
+    piece, in order, slots counted from 0 per sequence without gaps and below split_k -- also
+    when the slot limit, not the unit count, sets the share."""
     import random
 
     kv_layout = package.kv_layout
@@ -379,14 +379,15 @@ def test_solo_schedule_covers_every_page_once_within_the_slots(package):
         if sum(pages) == 0:
             assert pieces == []
             continue
-        assert share * ctas >= sum(pages) and share * (split_k - 1) >= max(pages)
+        units = [n + kv_layout.sequence_overhead(n, kv_layout.TENSOR_CORE_PIECE_OVERHEAD) for n in pages]
+        assert share * ctas >= sum(units) and share * (split_k - 1) >= max(units)
         seen = [0] * len(lengths)
         next_slot = [0] * len(lengths)
-        for number, sequence, first, count, slot in pieces:
-            assert count >= 1 and first == seen[sequence]
+        last_cta = -1
+        for cta, sequence, first, count, slot in pieces:
+            assert count >= 1 and first == seen[sequence] and cta >= last_cta
+            last_cta = cta
             seen[sequence] += count
             assert slot == next_slot[sequence] < split_k
             next_slot[sequence] += 1
-            start = sum(pages[:sequence]) + first
-            assert number * share <= start and start + count <= (number + 1) * share
         assert seen == pages
