@@ -241,6 +241,10 @@ def test_plan_split_k_uses_host_bounds_only(package):
     assert plan(4, 32769) == 148         # long, tiny batch: fill the machine
     assert plan(1, 64) == 1              # never shorter than 8 pages per split
     assert plan(8, 513) == 4
+    # many short sequences stay on the persistent kernel (which needs split_k >= 2) ...
+    assert plan(512, 101) == 3 and plan(256, 1024) == 3 and plan(1024, 61) == 3
+    # ... smaller batches and wider tables keep the old plan
+    assert plan(255, 101) == 1 and plan(64, 201) == 1 and plan(256, 1025) == 3
     for batch, context in ((1, 1), (3, 100000), (1024, 16)):
         assert 1 <= plan(batch, context) <= 65535
 
