@@ -80,6 +80,7 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {  # (workload, seed, kernel): (bytes, split_k of
     ("sweep_b256", 0, "decode_mma_kernel"): (409.63e6 + 3.54e6, 3),
     ("long_skew_b4", 0, "decode_mma_kernel (solo)+rope"): (55.17e6 + 0.01e6, 148),  # the partials stay in L2
     ("long_skew_b4", 0, "decode_mma_kernel+rope"): (55.17e6 + 0.01e6, 148),
+    ("fp8_b128", 0, "decode_mma_kernel (solo)+rope"): (135.23e6 + 1.92e6, 5),  # the default: write folded in
     ("fp8_b128", 0, "decode_mma_kernel (solo)"): (135.09e6 + 1.80e6, 5),
     ("fp8_b128", 0, "decode_mma_kernel"): (135.19e6 + 1.92e6, 5),
     ("short_b512", 0, "decode_mma_kernel (solo)+rope"): (54.63e6 + 0.05e6, 3),  # the default; the partials stay in L2
@@ -772,7 +773,7 @@ def partial_pass_leg(package, step, timer, steps, repeats, seed, world):
             source = step.packed[layer].as_strided((workload.batch, 12, 128), (step.packed.stride(1), 128, 1))
             plain_sets.append(splitk.fill_attention_args(
                 cabi, q, step.k_pools[layer], step.v_pools[layer], step.block_table, step.seq_lens,
-                split_k=step.split_k, scale=128 ** -0.5, partials=partials, out=out))
+                split_k=step.split_k, scale=128 ** -0.5, partials=partials, out=out, kv_scales=scales))
         arg_sets.append(splitk.fill_attention_args(
             cabi, source, step.k_pools[layer], step.v_pools[layer], step.block_table, step.seq_lens,
             split_k=step.split_k, scale=128 ** -0.5, partials=partials, out=out, kv_scales=scales))

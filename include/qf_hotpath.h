@@ -467,10 +467,12 @@ int qf_qkv_rope_cache_timeline(const qf_qkv_rope_cache_args* args, int64_t* time
  * started (an earlier step, a prefill).  The kernel relies on it: it requests tiles of
  * those older pages before its dependency wait, while the kernels before it drain.  The
  * newest token's page is only copied after this kernel itself has stored the new row.
- * QF_EUNSUPPORTED unless: 16-bit pools, 12 + 2 heads, split_k >= 2, and arguments for
- * which qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA or its
- * _SOLO variant (the fused step runs the same variant);
- * callers then run qf_rope_kv_write and qf_grouped_splitk_decode_attention.
+ * FP8 pools (args->kv_fp8 with k_scale / v_scale): the new K / V rows are stored as e4m3
+ * bytes at their page's fixed scales, byte for byte what qf_rope_kv_write_fp8 stores.
+ * QF_EUNSUPPORTED unless: 12 + 2 heads, split_k >= 2, and arguments for which
+ * qf_grouped_splitk_decode_attention_plan reports QF_KERNEL_PERSISTENT_MMA_SOLO (or, for
+ * 16-bit pools, QF_KERNEL_PERSISTENT_MMA: the fused step runs the same variant); callers
+ * then run qf_rope_kv_write(_fp8) and qf_grouped_splitk_decode_attention.
  * `stages`: QF_STAGE_PARTIAL | QF_STAGE_COMBINE for the whole step; one of them alone
  * launches only that kernel (timing). */
 int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const void* positions,

@@ -19,7 +19,8 @@ current torch stream; none has a CPU fallback):
     native_grouped_persistent_timeline                     custom_kernels/paged_decode_native_grouped.py
     quantize_kv_pool_e4m3, dequantize_kv_pool_e4m3,
     native_decode_rope_kv_write_fp8, packed_qkv_rope_cache_fp8,
-    grouped_splitk_decode_attention_fp8                    custom_kernels/fp8_paged_kv.py
+    grouped_splitk_decode_attention_fp8,
+    packed_qkv_rope_attention_fp8                          custom_kernels/fp8_paged_kv.py
     advance_decode_state                                   custom_kernels/decode_state.py
     rms_norm, residual_add_rms_norm                        custom_kernels/fused_rms.py
     qkv_rope_cache, qkv_rope_cache_timeline                custom_kernels/fused_gemm.py
@@ -53,6 +54,7 @@ _EXPORTS = {
     "native_decode_rope_kv_write_fp8": "fp8_paged_kv",
     "packed_qkv_rope_cache_fp8": "fp8_paged_kv",
     "grouped_splitk_decode_attention_fp8": "fp8_paged_kv",
+    "packed_qkv_rope_attention_fp8": "fp8_paged_kv",
     "advance_decode_state": "decode_state",
     "rms_norm": "fused_rms",
     "residual_add_rms_norm": "fused_rms",

@@ -979,13 +979,14 @@ int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const 
              "the rotation table must be a 16-byte aligned device buffer of at least one position");
   if (args->batch == 0) return QF_OK;
   // q points at the packed rows: 16 segments of 128, the query heads first
-  if (args->kv_fp8 || args->q_heads != 12 || args->kv_heads != 2 || args->q_stride_h != QF_HEAD_DIM ||
+  const qf::FusedKernel kind = qf::choose_fused_kernel(args);
+  // (FP8 pools: the solo variant only, i.e. not behind qf_set_tuning mode 4)
+  if (args->q_heads != 12 || args->kv_heads != 2 || args->q_stride_h != QF_HEAD_DIM ||
       args->q_stride_b < 16 * QF_HEAD_DIM || args->split_k < 2 ||
-      (qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCore &&
-       qf::choose_fused_kernel(args) != qf::FusedKernel::kTensorCoreSolo)) {
+      (kind != qf::FusedKernel::kTensorCoreSolo && (kind != qf::FusedKernel::kTensorCore || args->kv_fp8))) {
     return qf::fail(QF_EUNSUPPORTED,
-                    "the fused step needs 16-bit pools, the packed 12 + 2 + 2 head layout, split_k >= 2 and a "
-                    "layout the tensor-core kernel takes; run the RoPE / KV write and the attention separately");
+                    "the fused step needs the packed 12 + 2 + 2 head layout, split_k >= 2 and a layout the "
+                    "tensor-core kernel takes; run the RoPE / KV write and the attention separately");
   }
   int* status = qf::status_word_for_current_device();
   QF_REQUIRE(status != nullptr, "could not resolve the device status word");
@@ -997,7 +998,10 @@ int qf_packed_rope_decode_attention(const qf_decode_attention_args* args, const 
   rope.table = reinterpret_cast<const float2*>(rope_table), rope.table_positions = table_positions;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (stages & QF_STAGE_PARTIAL) {
-    if (qf::choose_fused_kernel(args) == qf::FusedKernel::kTensorCoreSolo) {
+    if (args->kv_fp8) {
+      rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, true, false, true, true>(p, s, rope)
+                                       : qf::launch_mma<__nv_bfloat16, true, false, true, true>(p, s, rope);
+    } else if (kind == qf::FusedKernel::kTensorCoreSolo) {
       rc = args->dtype == QF_DTYPE_F16 ? qf::launch_mma<__half, false, false, true, true>(p, s, rope)
                                        : qf::launch_mma<__nv_bfloat16, false, false, true, true>(p, s, rope);
     } else {

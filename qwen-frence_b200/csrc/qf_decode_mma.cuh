@@ -81,7 +81,9 @@ template <bool FP8>
 struct RingShape {
   static constexpr int kRowBytes = FP8 ? QF_HEAD_DIM : 2 * QF_HEAD_DIM;
   static constexpr int kTileBytes = QF_PAGE_SIZE * kRowBytes;
-  static constexpr int kSlotBytes = FP8 ? kTileBytes + 64 : kTileBytes;
+  // (FP8: the tile's scale rides behind it; the fused step's Q tile and its cos / sin row,
+  // 1 632 + 512 bytes, need the slot a little larger than a tile as well)
+  static constexpr int kSlotBytes = FP8 ? kTileBytes + 128 : kTileBytes;
   static constexpr int kSlots = FP8 ? 3 : 5;
   static constexpr int kCtasPerSm = FP8 ? 2 : 1;
   static constexpr int kAhead = kSlots - 1;
@@ -239,7 +241,8 @@ struct RopeInputs {
 template <typename T, bool FP8, bool PROFILE, bool ROPE = false, bool SOLO = false>
 __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     decode_mma_kernel(const StreamParams sp, const __grid_constant__ RopeInputs rope) {
-  static_assert(!(ROPE && FP8), "the fused RoPE / KV write is built for 16-bit pools");
+  static_assert(!(ROPE && FP8) || SOLO, "the fused RoPE / KV write on FP8 pools is built for the solo variant");
+  static_assert(kQTileBytes + (ROPE ? 512 : 0) <= RingShape<FP8>::kSlotBytes, "the Q tile must fit a ring slot");
   // empty units in front of a sequence: both variants weigh the shares with them (the solo
   // variant, where a sequence costs one warp a Q tile and a store, measured per 28-layer step
   // with 0 / 3 / 6: 64 x U[128, 4096] tokens 0.790 / 0.771 / 0.767 ms, 256 x log-uniform
@@ -398,6 +401,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     float x1, x2, y1, y2;
     uint4 v_bits;
     int64_t row;  // byte offset of the pool row (the same in both pools)
+    float k_scale, v_scale;  // FP8 pools: the page's scales, by which the new row is divided
     bool write;   // false: the sequence's length was cut to the table's capacity
   };
   auto load_new_row = [&](int sequence, int id, int rows, int position) {
@@ -419,10 +423,38 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     r.y1 = to_float(from[lane + 32]), r.y2 = to_float(from[lane + 96]);
     r.v_bits = make_uint4(0u, 0u, 0u, 0u);
     if (lane < 16) r.v_bits = reinterpret_cast<const uint4*>(row_in + (14 + kv_head) * QF_HEAD_DIM * 2)[lane];
+    r.k_scale = r.v_scale = 1.f;
+    if constexpr (FP8) {
+      r.k_scale = p.k_scale[static_cast<int64_t>(id) * p.kv_heads + kv_head];
+      r.v_scale = p.v_scale[static_cast<int64_t>(id) * p.kv_heads + kv_head];
+    }
     return r;
   };
   auto finish_new_row = [&](const NewRow& r) {
     if (!r.write) return;  // the same for every lane
+    if constexpr (FP8) {
+      // e4m3 bytes at the page's fixed scales: clamp(x / scale, +-448), round to nearest even,
+      // saturating -- the expressions of the RoPE / KV-write kernel, so the same bytes
+      auto encode = [](float x, float scale) {
+        const float y = fminf(fmaxf(__fdiv_rn(x, scale), -448.f), 448.f);
+        return static_cast<unsigned char>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+      };
+      unsigned char* to = const_cast<unsigned char*>(p.k_pool) + r.row;
+      to[lane] = encode(__fsub_rn(__fmul_rn(r.x1, r.cs_lo.x), __fmul_rn(r.x2, r.cs_lo.y)), r.k_scale);
+      to[lane + 64] = encode(__fadd_rn(__fmul_rn(r.x2, r.cs_lo.x), __fmul_rn(r.x1, r.cs_lo.y)), r.k_scale);
+      to[lane + 32] = encode(__fsub_rn(__fmul_rn(r.y1, r.cs_hi.x), __fmul_rn(r.y2, r.cs_hi.y)), r.k_scale);
+      to[lane + 96] = encode(__fadd_rn(__fmul_rn(r.y2, r.cs_hi.x), __fmul_rn(r.y1, r.cs_hi.y)), r.k_scale);
+      if (lane < 16) {
+        const float2 a = unpack2<T>(r.v_bits.x), b = unpack2<T>(r.v_bits.y), c = unpack2<T>(r.v_bits.z),
+                     d = unpack2<T>(r.v_bits.w);
+        __align__(8) unsigned char bytes[8] = {encode(a.x, r.v_scale), encode(a.y, r.v_scale), encode(b.x, r.v_scale),
+                                               encode(b.y, r.v_scale), encode(c.x, r.v_scale), encode(c.y, r.v_scale),
+                                               encode(d.x, r.v_scale), encode(d.y, r.v_scale)};
+        reinterpret_cast<uint2*>(const_cast<unsigned char*>(p.v_pool) + r.row)[lane] = *reinterpret_cast<const uint2*>(bytes);
+      }
+      __syncwarp();  // the lanes' stores are ordered before the lanes' copies of the rows
+      return;
+    }
     T* to = reinterpret_cast<T*>(const_cast<unsigned char*>(p.k_pool) + r.row);
     to[lane] = from_float<T>(__fsub_rn(__fmul_rn(r.x1, r.cs_lo.x), __fmul_rn(r.x2, r.cs_lo.y)));
     to[lane + 64] = from_float<T>(__fadd_rn(__fmul_rn(r.x2, r.cs_lo.x), __fmul_rn(r.x1, r.cs_lo.y)));

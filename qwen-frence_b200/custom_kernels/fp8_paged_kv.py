@@ -224,3 +224,68 @@ def grouped_splitk_decode_attention_fp8(
         cabi.check(cabi.library().qf_grouped_splitk_decode_attention(
             ctypes.byref(args), cabi.stream_pointer(q.device)))
     return out
+
+
+def packed_qkv_rope_attention_fp8(
+    packed, positions, slot_mapping, k8_pool, v8_pool, k_scale, v_scale, block_table, seq_lens,
+    *, split_k, scale=None, base=1_000_000.0, partials=None, rope_table=None, require_fused=False,
+):
+    """The decode step on FP8 pools in two launches: packed_qkv_rope_attention (RoPE + KV write
+    folded into the attention partial pass, then the combine) with the new K / V rows quantised
+    at their page's scales, byte for byte what packed_qkv_rope_cache_fp8 stores.  Same contract
+    as the 16-bit call: `slot_mapping[b]` names token seq_lens[b] - 1 of sequence b in
+    `block_table` and is not read, every older token is already in the pools; positions are
+    int32 / int64; `rope_table` from build_rope_table (default: a cached table as long as the
+    block table can hold).  Falls back to the two operators when the fused kernel does not apply
+    (`require_fused=True`: raises instead)."""
+    import ctypes
+
+    import torch
+
+    fused = _sibling("fused_decode_step")
+    if packed.ndim == 3:
+        _require(packed.shape[1] == 1, "packed QKV must have one decode token per row")
+        packed = packed[:, 0, :]
+    _require(packed.ndim == 2 and packed.shape[1] == 2048, "expected packed QKV shape (batch, 2048)")
+    batch = packed.shape[0]
+    _require(tuple(positions.shape) == (batch,) and tuple(slot_mapping.shape) == (batch,) and
+             tuple(seq_lens.shape) == (batch,), "positions, slot_mapping and seq_lens must hold one entry per row")
+    _check_fp8_pools(torch, k8_pool, v8_pool, k_scale, v_scale)
+    _require(packed.dtype in (torch.float16, torch.bfloat16), "packed QKV must be float16 or bfloat16")
+
+    def pair():
+        if require_fused:
+            raise RuntimeError("the fused step does not apply to these arguments")
+        q = packed_qkv_rope_cache_fp8(packed, positions, slot_mapping, k8_pool, v8_pool, k_scale, v_scale, base=base)
+        return grouped_splitk_decode_attention_fp8(q, k8_pool, v8_pool, k_scale, v_scale, block_table, seq_lens,
+                                                   split_k=split_k, scale=scale, partials=partials)
+
+    fused_ok = (batch > 0 and int(split_k) >= 2 and packed.stride(1) == 1
+                and tuple(k8_pool.shape[1:]) == (16, 2, 128) and block_table.ndim == 2 and block_table.shape[1] > 0
+                and positions.dtype in (torch.int32, torch.int64))
+    if not fused_ok:
+        return pair()
+    cabi = _cabi()
+    splitk = _sibling("paged_decode_grouped_splitk")
+    q_view = packed.as_strided((batch, 12, 128), (packed.stride(0), 128, 1))
+    out = torch.empty((batch, 12, 128), dtype=packed.dtype, device=packed.device)
+    if partials is None:
+        shape = (batch, int(split_k), 12, 128)
+        partials = (torch.empty(shape, dtype=torch.float32, device=packed.device),
+                    torch.empty(shape[:3], dtype=torch.float32, device=packed.device),
+                    torch.empty(shape[:3], dtype=torch.float32, device=packed.device))
+    args = splitk.fill_attention_args(
+        cabi, q_view, _as_bytes(torch, k8_pool), _as_bytes(torch, v8_pool), block_table, seq_lens,
+        split_k=int(split_k), scale=128 ** -0.5 if scale is None else scale, partials=partials, out=out,
+        kv_scales=(k_scale, v_scale))
+    if cabi.fused_kernel_plan(args)[0] != "decode_mma_kernel (solo)":
+        return pair()
+    positions = positions.contiguous()
+    if rope_table is None:
+        rope_table = fused.build_rope_table(block_table.shape[1] * 16, base=base, device=packed.device)
+    with cabi.device_of(packed):
+        cabi.check(cabi.library().qf_packed_rope_decode_attention(
+            ctypes.byref(args), positions.data_ptr(), cabi.torch_index_code(positions.dtype),
+            1, rope_table.data_ptr(), rope_table.shape[0], cabi.STAGE_PARTIAL | cabi.STAGE_COMBINE,
+            cabi.stream_pointer(packed.device)))
+    return out

@@ -46,7 +46,7 @@ class DecodeStep:
             sm_count=torch.cuda.get_device_properties(self.device).multi_processor_count)
         # fused_write: RoPE + KV write inside the attention partial pass (two launches per layer
         # instead of three) where the tensor-core kernel applies
-        self.fused_write = (bool(fused_write) and not self.fp8 and self.split_k > 1
+        self.fused_write = (bool(fused_write) and self.split_k > 1
                             and (fused_write == "always" or self.batch <= self.FUSED_WRITE_MAX_BATCH))
         self.kernel_launches_per_step = self.layers * (2 if self.split_k == 1 or self.fused_write else 3)
         self.rope_table = None
@@ -153,7 +153,12 @@ class DecodeStep:
     def layer(self, index):
         """RoPE + KV write, then attention, for one layer, on the current stream."""
         pkg = self.package
-        if self.fp8:
+        if self.fp8 and self.fused_write:
+            out = pkg.packed_qkv_rope_attention_fp8(
+                self.packed[index], self.positions, self.slot_mapping, self.k_pools[index], self.v_pools[index],
+                self.k_scales[index], self.v_scales[index], self.block_table, self.seq_lens, split_k=self.split_k,
+                partials=self._fp8_partials(), rope_table=self.rope_table, require_fused=True)
+        elif self.fp8:
             q = pkg.packed_qkv_rope_cache_fp8(
                 self.packed[index], self.positions, self.slot_mapping, self.k_pools[index],
                 self.v_pools[index], self.k_scales[index], self.v_scales[index])

@@ -165,3 +165,41 @@ def test_fp8_tensor_core_long_share(package, oracle, cuda_device):
             q.to(dev), k8, v8, ks, vs, table.to(dev), lens.to(dev), split_k=split_k)
         assert_attention_close(out, expected)
     assert package.cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fp8_fused_step_equals_the_two_operators(package, oracle, cuda_device, dtype):
+    """The decode step on FP8 pools in two launches (RoPE + KV write inside the partial pass):
+    the pools' bytes -- new rows quantised at their page's scales, everything else untouched --
+    and the attention output are those of packed_qkv_rope_cache_fp8 followed by
+    grouped_splitk_decode_attention_fp8, bit for bit; new token first / last in its page,
+    one-token sequences, sequences over several CTAs, many short ones."""
+    generator = torch.Generator().manual_seed(5)
+    for lengths, split_k in (([1, 16, 17, 32, 33, 100, 2049, 4000], 8),
+                             (torch.randint(1, 300, (200,), generator=generator).tolist(), 3),
+                             ([700, 9, 31, 1500, 64, 65, 3, 48, 1024, 1025, 250, 16] * 4, 6)):
+        q, k, v, table, lens = make_paged_inputs(lengths, seed=len(lengths), value_scale=0.5, dtype=dtype)
+        dev = cuda_device
+        k8, ks = package.quantize_kv_pool_e4m3(k.to(dev))
+        v8, vs = package.quantize_kv_pool_e4m3(v.to(dev))
+        batch = len(lengths)
+        packed = (torch.randn((batch, 2048), generator=generator) * 0.5).to(dtype).to(dev)
+        positions = (lens - 1).to(dev)
+        rows = torch.arange(batch)
+        slots = (table[rows, ((lens - 1) // 16).long()].long() * 16 + ((lens - 1) % 16).long()).to(dev)
+        table_dev, lens_dev = table.to(dev), lens.to(dev)
+        # poison the new rows: both paths must overwrite them
+        for pool in (k8, v8):
+            pool.view(-1, 2, 128)[slots] = 0x7F
+        k_pair, v_pair = k8.clone(), v8.clone()
+        q_pair = package.packed_qkv_rope_cache_fp8(packed, positions, slots, k_pair, v_pair, ks, vs)
+        want = package.grouped_splitk_decode_attention_fp8(q_pair, k_pair, v_pair, ks, vs, table_dev, lens_dev,
+                                                           split_k=split_k)
+        k_fused, v_fused = k8.clone(), v8.clone()
+        got = package.packed_qkv_rope_attention_fp8(packed, positions, slots, k_fused, v_fused, ks, vs, table_dev,
+                                                    lens_dev, split_k=split_k, require_fused=True)
+        assert package.cabi.device_status() == 0
+        assert torch.equal(k_fused, k_pair) and torch.equal(v_fused, v_pair)
+        assert not bool((k_fused.view(-1, 2, 128)[slots] == 0x7F).all())
+        assert torch.equal(got, want)
+        assert torch.isfinite(got.float()).all()
