@@ -1033,7 +1033,8 @@ def main():
         layers=args.layers or None)
     package.cabi.set_tuning(force_generic=KERNEL_MODES[args.kernel])  # read at launch (and capture) time
     step = package.decode_step.DecodeStep(workload, device, split_k=args.split_k or None, package=package,
-                                          fused_write=not args.unfused_write and args.kernel in ("auto", "persistent_mma", "persistent_mma_solo"))
+                                          fused_write=(not args.unfused_write and args.kernel in ("auto", "persistent_mma", "persistent_mma_solo")
+                                                       and not (workload.fp8 and args.kernel == "persistent_mma")))  # FP8: folded in the solo variant only
     step.load_packed_rows()
 
     # ---- parity gate: nothing is timed unless the timed call gives the oracle's answers ----
