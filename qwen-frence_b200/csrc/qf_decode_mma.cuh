@@ -518,6 +518,7 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
                    : "memory");
     }
   };
+  bool new_rows_described = false;  // ROPE: the descriptors just fetched may hold new rows to store
   bool plain_v_pending = false;  // the last call issued the K tile of a plain page; its V tile is next
   int64_t plain_page_offset = 0;
   int plain_id = 0;
@@ -558,7 +559,12 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
         describe((fill_page >> 5) + 1, id_next, rows_next, q_next, last_next, pos_next);
         if constexpr (FP8) plain_next = plain_units(id_next, rows_next, q_next);
         // ROPE: the new rows of the 32 units just described, well before their pages are copied
-        if constexpr (ROPE) store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
+        // (which happens after the next 32 units have been issued).  FP8 pools: at the top of the
+        // next page instead, in one place -- this code is inlined wherever a tile is issued, and
+        // with the quantisation in every copy that instantiation grew to 145 KB (120 KB so; the
+        // step of 128 x 2 048 tokens 0.944 -> 0.924 ms)
+        if constexpr (ROPE && !FP8) store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
+        if constexpr (ROPE && FP8) new_rows_described = true;
       }
       id = __shfl_sync(kFull, id_now, fill_page & 31);
       if (id != -3) break;
@@ -632,9 +638,13 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
   // (the caller's promise, see StreamParams::early_tiles) start their trip to shared memory
   // while the kernels before this one drain.
   int issued = 0;
-  if (sp.early_tiles) {
+  if constexpr (ROPE && !FP8) {
+    // (not for FP8 pools: one early tile per warp is all their ring has room for, and the copy
+    // of the tile-issue code it needs makes the largest instantiation of the family larger still)
+    if (sp.early_tiles) {
 #pragma unroll 1
-    while (issued < kAhead - 1 && issue_tile(true)) ++issued;
+      while (issued < kAhead - 1 && issue_tile(true)) ++issued;
+    }
   }
   bool first_tiles_out_of_order = issued > 0;  // groups: early tiles first, then the Q tile
   // From here on the kernel reads what the RoPE / KV-write kernel stored (Q rows, the
@@ -788,6 +798,12 @@ __global__ void __launch_bounds__(kFastThreads, RingShape<FP8>::kCtasPerSm)
     const int done_seq = piece_seq, done_rank = rank;
 
     for (; page < piece_end; page += kStep) {
+      if constexpr (ROPE && FP8) {
+        if (new_rows_described) {
+          store_new_rows_of(id_next, rows_next, last_next, pos_next, kFull);
+          new_rows_described = false;
+        }
+      }
       // ---- scores S^T = K Q^T ----
       wait_tiles_ahead<kAhead>();
       __syncwarp();
